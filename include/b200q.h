@@ -1,0 +1,149 @@
+/*
+ * b200q — C ABI of the B200 (sm_100a) quantized-linear hot path.
+ *
+ * This is the drop-in boundary: a maintainer of Torch-TensorRT binds these entry points
+ * (ctypes, a torch.library C++ shim, or a TensorRT plugin `enqueue`) in place of the
+ * TensorRT layers / third-party eager kernels the reference uses for the same step.
+ *
+ * Conventions for every compute entry point
+ *   - all buffers are caller-owned DEVICE pointers, row-major, contiguous;
+ *   - nothing is allocated or freed, nothing synchronises: work is enqueued on `stream`
+ *     (a `cudaStream_t` passed as `void*`; NULL = the legacy default stream);
+ *   - the return value is B200Q_OK (0) or a negative B200Q_ERR_* code; nothing throws;
+ *   - `dtype` is one of B200Q_F32 / B200Q_F16 / B200Q_BF16 and names the element type of
+ *     the floating-point tensor `x` / `out`.
+ *
+ * Reference citations are paths inside the pytorch/TensorRT tree.
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200Q_OK 0
+#define B200Q_ERR_INVALID (-1)   /* bad shape / null pointer / unsupported dtype      */
+#define B200Q_ERR_ALIGN (-2)     /* pointer or leading dimension not aligned as needed */
+#define B200Q_ERR_ARCH (-3)      /* device is not compute capability 10.x              */
+#define B200Q_ERR_CUDA (-4)      /* a CUDA runtime / driver call failed                */
+#define B200Q_ERR_WORKSPACE (-5) /* workspace missing or too small                     */
+#define B200Q_ERR_TIMEOUT (-6)   /* a bounded device-side wait gave up                 */
+
+#define B200Q_F32 0
+#define B200Q_F16 1
+#define B200Q_BF16 2
+
+typedef void* b200q_stream_t;
+
+/* Library identification. */
+int b200q_version(void);
+const char* b200q_status_string(int status);
+
+/* ------------------------------------------------------------------ abs-max reductions
+ * The `amax` operand of both quantize ops is an input the caller supplies
+ * (tests/py/dynamo/models/test_models_export.py:789 passes it explicitly); these produce
+ * it on the device for dynamic quantization.
+ *
+ * b200q_amax: max(|x|) over n elements -> amax_out[0].  Needs a workspace of
+ * b200q_amax_workspace_bytes() bytes (per-block partial maxima and a ticket counter);
+ * the workspace must be zero the first time it is used and is left zero again on return,
+ * so one memset at allocation is enough.  Calls sharing a workspace must not overlap.
+ * b200q_row_amax: max(|x|) per row -> amax_out[rows].
+ */
+size_t b200q_amax_workspace_bytes(void);
+int b200q_amax(const void* x, int dtype, int64_t n, float* amax_out, void* workspace,
+               size_t workspace_bytes, b200q_stream_t stream);
+int b200q_row_amax(const void* x, int dtype, int64_t rows, int64_t cols, float* amax_out,
+                   b200q_stream_t stream);
+
+/* ------------------------------------------------------------------ FP8 E4M3
+ * Replaces the Q half of the IQuantizeLayer/IDequantizeLayer pair built by
+ * py/torch_tensorrt/dynamo/conversion/impl/quantize.py:73-134 (scale = amax / 448,
+ * round to nearest even, saturate), producing real codes for the FP8 GEMM.
+ *
+ * amax_numel selects the scaling granularity:
+ *   1      per-tensor: amax[0]                       (what impl/quantize.py:96-100 accepts)
+ *   rows   one amax per row: amax[r]                 (per-token / per-channel extension)
+ *   0      dynamic per-row: the row abs-max is reduced inside the kernel, amax is ignored
+ * scales_out receives max(amax_numel, 1) fp32 scales (rows of them when amax_numel == 0);
+ * it may be NULL when amax_numel == 1.  cols must be a multiple of 16.
+ */
+int b200q_fp8_quantize(const void* x, int dtype, int64_t rows, int64_t cols, const float* amax,
+                       int64_t amax_numel, uint8_t* codes_out, float* scales_out,
+                       b200q_stream_t stream);
+
+/* Eager semantics of `tensorrt::quantize_op(input, amax, 8, 4, unsigned, narrow_range)`:
+ * quantize then dequantize back to the input dtype (impl/quantize.py:126-138).  Same
+ * amax_numel convention as above.  cols must be a multiple of 8. */
+int b200q_fp8_fake_quantize(const void* x, int dtype, int64_t rows, int64_t cols,
+                            const float* amax, int64_t amax_numel, void* out,
+                            b200q_stream_t stream);
+
+/* codes * scale -> out (dtype).  scales_numel is 1 or rows. */
+int b200q_fp8_dequantize(const uint8_t* codes, const float* scales, int64_t scales_numel,
+                         int64_t rows, int64_t cols, void* out, int dtype, b200q_stream_t stream);
+
+/* ------------------------------------------------------------------ NVFP4 (E2M1 codes, block 16, E4M3 block scales)
+ * Replaces IDynamicQuantizeLayer (impl/dynamic_block_quantize.py:149-156) for activations
+ * and the offline weight quantization (impl/dynamic_block_quantize.py:248-270) for weights.
+ *   global scale = (amax[0] / 6) / 448, zero -> 1     (impl/dynamic_block_quantize.py:299-308)
+ *   codes_out    [rows, cols/2] bytes, element 2i in the low nibble
+ *   scales_out   b200q_nvfp4_scale_bytes(rows, cols) bytes in the 128x4 swizzled layout
+ *                (rows padded to 128, scale columns to 4; tile (rt, ct) at
+ *                (rt * n_col_tiles + ct) * 512; row r, column c inside a tile at
+ *                (r % 32) * 16 + (r / 32) * 4 + c); padding is written as zero
+ *   global_scale_out  one fp32 (may be NULL)
+ * cols must be a multiple of 16.
+ */
+size_t b200q_nvfp4_scale_bytes(int64_t rows, int64_t cols);
+int b200q_nvfp4_quantize(const void* x, int dtype, int64_t rows, int64_t cols, const float* amax,
+                         uint8_t* codes_out, uint8_t* scales_out, float* global_scale_out,
+                         b200q_stream_t stream);
+
+/* Eager semantics of `tensorrt::dynamic_block_quantize_op(input, 16, amax, 4, 2, 8, 4)`:
+ * quantize then double-dequantize, x_hat = e2m1 * (e4m3 * global), back to the input dtype
+ * (impl/dynamic_block_quantize.py:201-221). */
+int b200q_nvfp4_fake_quantize(const void* x, int dtype, int64_t rows, int64_t cols,
+                              const float* amax, void* out, b200q_stream_t stream);
+
+int b200q_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales_swizzled,
+                           const float* global_scale, int64_t rows, int64_t cols, void* out,
+                           int dtype, b200q_stream_t stream);
+
+/* ------------------------------------------------------------------ quantized GEMMs (tcgen05)
+ * Replace the IMatrixMultiplyLayer (+ bias add) TensorRT fuses with its Q/DQ neighbours
+ * (impl/linear.py:40-67, impl/matmul.py:62-64):   out[m, n] = sum_k a[m,k] * b[n,k]  (+ bias[n])
+ * with a, b the dequantized operands.  out is bf16 [M, N]; bias is bf16 [N] or NULL.
+ *
+ * FP8: a_codes [M, K], b_codes [N, K] E4M3; a_scales has a_scales_numel (1 or M) fp32
+ * entries, b_scales has b_scales_numel (1 or N).  K must be a multiple of 16.
+ *
+ * NVFP4: a_codes [M, K/2], b_codes [N, K/2]; block scales in the swizzled layout above;
+ * a_global / b_global point at one fp32 each.  K must be a multiple of 32.
+ */
+int b200q_fp8_gemm(const uint8_t* a_codes, const float* a_scales, int64_t a_scales_numel,
+                   const uint8_t* b_codes, const float* b_scales, int64_t b_scales_numel,
+                   const void* bias, void* out, int64_t M, int64_t N, int64_t K,
+                   b200q_stream_t stream);
+int b200q_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_scales, const float* a_global,
+                     const uint8_t* b_codes, const uint8_t* b_scales, const float* b_global,
+                     const void* bias, void* out, int64_t M, int64_t N, int64_t K,
+                     b200q_stream_t stream);
+
+/* Tile width of the GEMM kernels: 0 = chosen per problem (default), 128 or 256 = forced.
+ * Process-wide tuning knob; results do not depend on it beyond fp32 summation order. */
+int b200q_gemm_set_tile_n(int bn);
+
+/* The GEMM kernels bound every device-side wait; a wait that gives up records it in a
+ * device status word instead of hanging.  This call synchronises with the device, returns
+ * B200Q_OK or B200Q_ERR_TIMEOUT, and clears the word when `reset` is non-zero. */
+int b200q_device_status(int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

@@ -1,0 +1,208 @@
+"""Python calls straight through the C ABI (include/b200q.h) on torch CUDA tensors.
+
+torch is used for device memory and streams only; every function below hands raw device
+pointers to `libb200q.so`.  These are the calls the GPU parity tests exercise.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import check, load
+
+_DTYPE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def _dt(x: torch.Tensor) -> int:
+    try:
+        return _DTYPE[x.dtype]
+    except KeyError:
+        raise ValueError(f"received an input of {x.dtype} type. Supported types: float32 | float16 | bfloat16") from None
+
+
+def _stream(x: torch.Tensor) -> int:
+    return torch.cuda.current_stream(x.device).cuda_stream
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("b200q operates on CUDA tensors only; there is no CPU implementation")
+
+
+def _rows_cols(x: torch.Tensor):
+    cols = x.shape[-1]
+    return (x.numel() // cols if cols else 0), cols
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+_amax_ws: dict = {}
+
+
+def amax_workspace(device) -> torch.Tensor:
+    """Zero-initialised workspace for b200q_amax, one per (device, stream)."""
+    key = (torch.device(device).index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _amax_ws.get(key)
+    if ws is None:
+        ws = torch.zeros(load().b200q_amax_workspace_bytes(), dtype=torch.uint8, device=device)
+        _amax_ws[key] = ws
+    return ws
+
+
+def amax(x: torch.Tensor) -> torch.Tensor:
+    _need_cuda(x)
+    x = x.contiguous()
+    out = torch.zeros((), dtype=torch.float32, device=x.device)
+    if x.numel() == 0:
+        return out
+    ws = amax_workspace(x.device)
+    with torch.cuda.device(x.device):
+        check(load().b200q_amax(x.data_ptr(), _dt(x), x.numel(), out.data_ptr(), ws.data_ptr(), ws.numel(), _stream(x)),
+              "b200q_amax")
+    return out
+
+
+def row_amax(x: torch.Tensor) -> torch.Tensor:
+    _need_cuda(x)
+    x = x.contiguous()
+    rows, cols = _rows_cols(x)
+    out = torch.empty(rows, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(load().b200q_row_amax(x.data_ptr(), _dt(x), rows, cols, out.data_ptr(), _stream(x)), "b200q_row_amax")
+    return out.view(*x.shape[:-1], 1)
+
+
+def _amax_arg(x, amax_t, rows):
+    if amax_t is None:
+        return None, 0
+    a = amax_t.to(device=x.device, dtype=torch.float32).contiguous()
+    n = a.numel()
+    if n != 1 and n != rows:
+        raise ValueError(f"amax must hold one value or one per row ({rows}), got shape {tuple(amax_t.shape)}")
+    return a, n
+
+
+def fp8_quantize(x: torch.Tensor, amax_t: torch.Tensor | None = None):
+    """-> (codes uint8 like x, scales fp32 [1] or [rows]).  amax_t None = dynamic per-row."""
+    _need_cuda(x, amax_t)
+    x = x.contiguous()
+    rows, cols = _rows_cols(x)
+    a, n = _amax_arg(x, amax_t, rows)
+    codes = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    scales = torch.empty(1 if n == 1 else rows, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(load().b200q_fp8_quantize(x.data_ptr(), _dt(x), rows, cols, _ptr(a), n, codes.data_ptr(), scales.data_ptr(),
+                                        _stream(x)), "b200q_fp8_quantize")
+    return codes, scales
+
+
+def fp8_fake_quantize(x: torch.Tensor, amax_t: torch.Tensor | None = None) -> torch.Tensor:
+    _need_cuda(x, amax_t)
+    x = x.contiguous()
+    rows, cols = _rows_cols(x)
+    a, n = _amax_arg(x, amax_t, rows)
+    out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        check(load().b200q_fp8_fake_quantize(x.data_ptr(), _dt(x), rows, cols, _ptr(a), n, out.data_ptr(), _stream(x)),
+              "b200q_fp8_fake_quantize")
+    return out
+
+
+def fp8_dequantize(codes: torch.Tensor, scales: torch.Tensor, dtype=torch.float32) -> torch.Tensor:
+    _need_cuda(codes, scales)
+    codes = codes.contiguous()
+    rows, cols = _rows_cols(codes)
+    out = torch.empty(codes.shape, dtype=dtype, device=codes.device)
+    with torch.cuda.device(codes.device):
+        check(load().b200q_fp8_dequantize(codes.data_ptr(), scales.data_ptr(), scales.numel(), rows, cols, out.data_ptr(),
+                                          _DTYPE[dtype], _stream(codes)), "b200q_fp8_dequantize")
+    return out
+
+
+def nvfp4_scale_bytes(rows: int, cols: int) -> int:
+    return load().b200q_nvfp4_scale_bytes(rows, cols)
+
+
+def nvfp4_quantize(x: torch.Tensor, amax_t: torch.Tensor):
+    """-> (packed codes uint8 [.., cols/2], swizzled E4M3 block scales uint8 [bytes], global scale fp32 0-dim)."""
+    _need_cuda(x, amax_t)
+    x = x.contiguous()
+    rows, cols = _rows_cols(x)
+    if cols % 16:
+        raise ValueError(f"last dimension ({cols}) must be a multiple of the block size 16")
+    a = amax_t.to(device=x.device, dtype=torch.float32).reshape(1)
+    codes = torch.empty(*x.shape[:-1], cols // 2, dtype=torch.uint8, device=x.device)
+    scales = torch.empty(nvfp4_scale_bytes(rows, cols), dtype=torch.uint8, device=x.device)
+    g = torch.empty((), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(load().b200q_nvfp4_quantize(x.data_ptr(), _dt(x), rows, cols, a.data_ptr(), codes.data_ptr(),
+                                          scales.data_ptr(), g.data_ptr(), _stream(x)), "b200q_nvfp4_quantize")
+    return codes, scales, g
+
+
+def nvfp4_fake_quantize(x: torch.Tensor, amax_t: torch.Tensor) -> torch.Tensor:
+    _need_cuda(x, amax_t)
+    x = x.contiguous()
+    rows, cols = _rows_cols(x)
+    if cols % 16:
+        raise ValueError(f"last dimension ({cols}) must be a multiple of the block size 16")
+    a = amax_t.to(device=x.device, dtype=torch.float32).reshape(1)
+    out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        check(load().b200q_nvfp4_fake_quantize(x.data_ptr(), _dt(x), rows, cols, a.data_ptr(), out.data_ptr(), _stream(x)),
+              "b200q_nvfp4_fake_quantize")
+    return out
+
+
+def nvfp4_dequantize(codes, scales, g, dtype=torch.float32) -> torch.Tensor:
+    _need_cuda(codes, scales, g)
+    codes = codes.contiguous()
+    rows, half = _rows_cols(codes)
+    out = torch.empty(*codes.shape[:-1], half * 2, dtype=dtype, device=codes.device)
+    with torch.cuda.device(codes.device):
+        check(load().b200q_nvfp4_dequantize(codes.data_ptr(), scales.data_ptr(), g.data_ptr(), rows, half * 2,
+                                            out.data_ptr(), _DTYPE[dtype], _stream(codes)), "b200q_nvfp4_dequantize")
+    return out
+
+
+def fp8_gemm(a_codes, a_scales, b_codes, b_scales, bias=None) -> torch.Tensor:
+    """bf16 [.., N] = dequant(a [.., K]) @ dequant(b [N, K])^T + bias."""
+    _need_cuda(a_codes, a_scales, b_codes, b_scales, bias)
+    a_codes, b_codes = a_codes.contiguous(), b_codes.contiguous()
+    N, K = b_codes.shape
+    M = a_codes.numel() // K
+    out = torch.empty(*a_codes.shape[:-1], N, dtype=torch.bfloat16, device=a_codes.device)
+    if bias is not None:
+        bias = bias.to(torch.bfloat16).contiguous()
+    with torch.cuda.device(a_codes.device):
+        check(load().b200q_fp8_gemm(a_codes.data_ptr(), a_scales.data_ptr(), a_scales.numel(), b_codes.data_ptr(),
+                                    b_scales.data_ptr(), b_scales.numel(), _ptr(bias), out.data_ptr(), M, N, K,
+                                    _stream(a_codes)), "b200q_fp8_gemm")
+    return out
+
+
+def nvfp4_gemm(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias=None) -> torch.Tensor:
+    _need_cuda(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias)
+    a_codes, b_codes = a_codes.contiguous(), b_codes.contiguous()
+    N, half = b_codes.shape
+    K = half * 2
+    M = a_codes.numel() // half
+    out = torch.empty(*a_codes.shape[:-1], N, dtype=torch.bfloat16, device=a_codes.device)
+    if bias is not None:
+        bias = bias.to(torch.bfloat16).contiguous()
+    with torch.cuda.device(a_codes.device):
+        check(load().b200q_nvfp4_gemm(a_codes.data_ptr(), a_scales.data_ptr(), a_global.data_ptr(), b_codes.data_ptr(),
+                                      b_scales.data_ptr(), b_global.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
+                                      _stream(a_codes)), "b200q_nvfp4_gemm")
+    return out
+
+
+def set_gemm_tile_n(bn: int) -> None:
+    check(load().b200q_gemm_set_tile_n(bn), "b200q_gemm_set_tile_n")
+
+
+def device_status(reset: bool = True) -> int:
+    """0, or B200Q_ERR_TIMEOUT (-6) when a GEMM's bounded device-side wait gave up."""
+    return load().b200q_device_status(1 if reset else 0)

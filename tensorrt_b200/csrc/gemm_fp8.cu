@@ -1,0 +1,93 @@
+// FP8 E4M3 x E4M3 GEMM entry point (tcgen05 kind::f8f6f4) and the pieces shared by both
+// quantized GEMMs: the TMA descriptor encoder lookup, the device status word and the
+// tile-width override.
+#include <atomic>
+#include <mutex>
+
+#include "gemm_host.cuh"
+
+namespace b200q {
+namespace gemm {
+
+namespace {
+__device__ int g_device_status = 0;
+std::atomic<int> g_force_bn{0};
+std::mutex g_mu;
+int* g_status_addr[64] = {};
+}  // namespace
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+int* device_status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_status_addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+    g_status_addr[dev] = static_cast<int*>(p);
+  }
+  return g_status_addr[dev];
+}
+
+int forced_bn() { return g_force_bn.load(); }
+
+}  // namespace gemm
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int b200q_gemm_set_tile_n(int bn) {
+  if (bn != 0 && bn != 128 && bn != 256) return B200Q_ERR_INVALID;
+  gemm::g_force_bn.store(bn);
+  return B200Q_OK;
+}
+
+int b200q_device_status(int reset) {
+  int* w = gemm::device_status_word();
+  if (w == nullptr) return B200Q_ERR_CUDA;
+  int v = 0;
+  if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return B200Q_ERR_CUDA;
+  if (reset && v != 0) {
+    const int zero = 0;
+    if (cudaMemcpy(w, &zero, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) return B200Q_ERR_CUDA;
+  }
+  return v == 0 ? B200Q_OK : B200Q_ERR_TIMEOUT;
+}
+
+int b200q_fp8_gemm(const uint8_t* a_codes, const float* a_scales, int64_t a_scales_numel, const uint8_t* b_codes,
+                   const float* b_scales, int64_t b_scales_numel, const void* bias, void* out, int64_t M, int64_t N,
+                   int64_t K, b200q_stream_t stream) {
+  if (a_codes == nullptr || b_codes == nullptr || a_scales == nullptr || b_scales == nullptr || out == nullptr)
+    return B200Q_ERR_INVALID;
+  if (M < 0 || N < 0 || K <= 0 || M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200Q_ERR_INVALID;
+  if (K % 16 != 0) return B200Q_ERR_INVALID;
+  if ((a_scales_numel != 1 && a_scales_numel != M) || (b_scales_numel != 1 && b_scales_numel != N)) return B200Q_ERR_INVALID;
+  if (!aligned(a_codes, 16) || !aligned(b_codes, 16) || !aligned(out, 16)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  if (M == 0 || N == 0) return B200Q_OK;
+  gemm::Params p{};
+  p.a_scales = a_scales;
+  p.b_scales = b_scales;
+  p.a_scale_stride = a_scales_numel == 1 ? 0 : 1;
+  p.b_scale_stride = b_scales_numel == 1 ? 0 : 1;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.k_bytes = static_cast<int>(K);
+  return gemm::launch<false>(a_codes, b_codes, p, static_cast<cudaStream_t>(stream), gemm::forced_bn());
+}
+
+}  // extern "C"

@@ -1,0 +1,74 @@
+// Host side of the tcgen05 GEMMs: TMA tensor maps, tile-shape choice, launch.
+#pragma once
+
+#include <cuda.h>
+
+#include "gemm_kernel.cuh"
+
+namespace b200q {
+namespace gemm {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled resolved through the runtime, so the library has no link-time
+// dependency on libcuda.
+EncodeTiledFn encode_tiled();
+
+// Device status word shared by all GEMM launches of this process on the current device.
+int* device_status_word();
+
+// Row-major byte matrix [rows, row_bytes] -> tiles of box_rows x 128 bytes, 128-byte swizzle,
+// out-of-bounds bytes read as zero.
+inline int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t row_bytes, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) return B200Q_ERR_CUDA;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBKBytes), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200Q_OK : B200Q_ERR_CUDA;
+}
+
+template <bool NVF4, int BN>
+int launch_tile(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st) {
+  using C = Cfg<NVF4, BN>;
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200Q_ERR_CUDA;
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(gemm_kernel<NVF4, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+      return B200Q_ERR_CUDA;
+    configured[dev] = true;
+  }
+  CUtensorMap ta, tb;
+  if (int rc = make_operand_map(&ta, a, p.M, p.k_bytes, kBM)) return rc;
+  if (int rc = make_operand_map(&tb, b, p.N, p.k_bytes, BN)) return rc;
+  const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_kernel<NVF4, BN><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, p);
+  return check_launch();
+}
+
+// Tile width: 256 when that still gives every SM a tile, else 128.  `force_bn` (128 / 256)
+// overrides the choice (used by tests to cover both instantiations).
+template <bool NVF4>
+int launch(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, int force_bn) {
+  p.status = device_status_word();
+  if (p.status == nullptr) return B200Q_ERR_CUDA;
+  int bn = force_bn;
+  if (bn != 128 && bn != 256) {
+    const int64_t tiles256 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 255) / 256);
+    bn = (tiles256 >= sm_count()) ? 256 : 128;
+  }
+  return bn == 256 ? launch_tile<NVF4, 256>(a, b, p, st) : launch_tile<NVF4, 128>(a, b, p, st);
+}
+
+int forced_bn();  // from the environment variable B200Q_GEMM_BN (0 when unset)
+
+}  // namespace gemm
+}  // namespace b200q

@@ -1,0 +1,329 @@
+// Persistent, warp-specialised tcgen05 GEMM for quantized operands (sm_100a).
+//
+//   out[m, n] = epilogue( sum_k A[m, k] * B[n, k] )            A: [M, K], B: [N, K], both K-major
+//
+// FP8  (NVF4 = false): tcgen05.mma kind::f8f6f4, E4M3 x E4M3 -> fp32 in tensor memory;
+//                      epilogue  acc * sa[m] * sb[n] + bias[n] -> bf16.
+// NVFP4 (NVF4 = true): tcgen05.mma kind::mxf4nvf4.block_scale (block 16, UE4M3 scales);
+//                      the 128x4 swizzled scale tiles are bulk-copied to shared memory and
+//                      moved to tensor memory with tcgen05.cp before the MMAs of a K tile;
+//                      epilogue  acc * (ga * gb) + bias[n] -> bf16.
+//
+// One CTA (192 threads) per SM walks over output tiles of 128 x BN:
+//   warp 0      TMA producer: operand (and scale) tiles into a STAGES-deep shared-memory ring
+//   warp 1      allocates tensor memory, issues the MMAs (one lane), commits to mbarriers
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp its own 32-lane quarter),
+//               scale, add bias, convert, store; overlaps the next tile's main loop when
+//               the accumulator is double-buffered in tensor memory
+// No TMA multicast is used anywhere.  Every mbarrier wait is bounded; a wait that gives up
+// raises a flag in global memory, the CTA drains and leaves, and the host reports
+// B200Q_ERR_TIMEOUT from b200q_device_status().
+#pragma once
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace b200q {
+namespace gemm {
+
+constexpr int kBM = 128;
+constexpr int kBKBytes = 128;       // one 128-byte swizzle row of K per stage: 128 FP8 or 256 FP4 elements
+constexpr int kMmaKBytes = 32;      // K bytes consumed by one tcgen05.mma (32 FP8 / 64 FP4 elements)
+constexpr int kThreads = 192;
+constexpr int kSmemLimit = 232448;  // 227 KiB
+
+template <bool NVF4, int BN>
+struct Cfg {
+  static constexpr int kABytes = kBM * kBKBytes;
+  static constexpr int kBBytes = BN * kBKBytes;
+  static constexpr int kSfaBytes = NVF4 ? 2048 : 0;                 // 4 atoms of 512 B (128 rows x 16 scales)
+  static constexpr int kSfbBytes = NVF4 ? (BN / 128) * 2048 : 0;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kAccStages = (NVF4 && BN == 256) ? 1 : 2;
+  static constexpr int kSfCols = NVF4 ? (16 + 4 * (BN / 32)) : 0;  // tensor-memory columns holding one K tile of scales
+  static constexpr int kColsNeeded = kAccStages * BN + kSfCols;
+  static constexpr int kTmemCols = kColsNeeded <= 256 ? 256 : 512;
+  static constexpr int kTailBytes = 2048;                           // barriers, tmem pointer, epilogue vectors
+  static constexpr int kEpiBytes = 2 * 2 * BN * 4;                  // 2 buffers x (col scale, bias) x BN floats
+  static constexpr int kStagesRaw = (kSmemLimit - 1024 - kTailBytes - kEpiBytes) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiBytes + kTailBytes;
+  static_assert(kStages >= 3, "pipeline too shallow");
+  static_assert(kColsNeeded <= 512, "tensor memory overflow");
+};
+
+struct Params {
+  const float* a_scales;   // FP8: [M] or [1]; NVFP4: pointer to the global scale of A
+  const float* b_scales;   // FP8: [N] or [1]; NVFP4: pointer to the global scale of B
+  int a_scale_stride;      // FP8: 1 (per row) or 0 (per tensor)
+  int b_scale_stride;
+  const uint8_t* sfa;      // NVFP4: swizzled block scales of A / B
+  const uint8_t* sfb;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* out;
+  int M, N;
+  int k_bytes;             // bytes per operand row (K for FP8, K/2 for NVFP4)
+  int sf_col_tiles;        // NVFP4: number of 4-scale column tiles per row tile (ceil(K/64))
+  int* status;             // device status word (0 = ok)
+};
+
+__device__ __forceinline__ void raise_timeout(int* status, int where) { atomicCAS(status, 0, where); }
+
+template <bool NVF4, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+  using C = Cfg<NVF4, BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* tail = smem + C::kStages * C::kStageBytes + C::kEpiBytes;
+  float* epi = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);
+  uint64_t* empty_bar = full_bar + C::kStages;
+  uint64_t* acc_full = empty_bar + C::kStages;
+  uint64_t* acc_empty = acc_full + C::kAccStages;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + C::kAccStages);
+  volatile uint32_t* abort_flag = tmem_holder + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_blocks = (p.M + kBM - 1) / kBM, n_blocks = (p.N + BN - 1) / BN;
+  const int num_tiles = m_blocks * n_blocks;
+  const int k_tiles = (p.k_bytes + kBKBytes - 1) / kBKBytes;
+  constexpr int kGroupM = 16;
+
+  auto tile_coord = [&](int t, int& mb, int& nb) {
+    const int per_group = kGroupM * n_blocks;
+    const int g = t / per_group, r = t - g * per_group;
+    const int rows_in_group = min(kGroupM, m_blocks - g * kGroupM);
+    nb = r / rows_in_group;
+    mb = g * kGroupM + (r - nb * rows_in_group);
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      ptx::mbar_init(full_bar + s, 1);
+      ptx::mbar_init(empty_bar + s, 1);
+    }
+    for (int s = 0; s < C::kAccStages; ++s) {
+      ptx::mbar_init(acc_full + s, 1);
+      ptx::mbar_init(acc_empty + s, 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tmap(&tmap_a);
+    ptx::prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<1>(tmem_holder, C::kTmemCols);
+    ptx::tmem_relinquish<1>();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mb, nb;
+        tile_coord(t, mb, nb);
+        for (int kt = 0; kt < k_tiles; ++kt) {
+          if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1u)) {
+            raise_timeout(p.status, 1);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * C::kStageBytes;
+          uint8_t* sb = sa + C::kABytes;
+          uint32_t tx = C::kABytes + C::kBBytes;
+          int atoms = 0;
+          if constexpr (NVF4) {
+            atoms = min(4, p.sf_col_tiles - kt * 4);
+            tx += atoms * 512;
+            for (int j = 0; j < BN / 128; ++j)
+              if ((nb * (BN / 128) + j) * 128 < p.N) tx += atoms * 512;
+          }
+          ptx::mbar_arrive_expect_tx(full_bar + stage, tx);
+          ptx::tma_load_2d(sa, &tmap_a, full_bar + stage, kt * kBKBytes, mb * kBM);
+          ptx::tma_load_2d(sb, &tmap_b, full_bar + stage, kt * kBKBytes, nb * BN);
+          if constexpr (NVF4) {
+            uint8_t* ssfa = sb + C::kBBytes;
+            uint8_t* ssfb = ssfa + C::kSfaBytes;
+            ptx::bulk_load(ssfa, p.sfa + (static_cast<int64_t>(mb) * p.sf_col_tiles + kt * 4) * 512, atoms * 512, full_bar + stage);
+            for (int j = 0; j < BN / 128; ++j) {
+              const int rt = nb * (BN / 128) + j;
+              if (rt * 128 < p.N)
+                ptx::bulk_load(ssfb + j * 2048, p.sfb + (static_cast<int64_t>(rt) * p.sf_col_tiles + kt * 4) * 512, atoms * 512,
+                               full_bar + stage);
+            }
+          }
+          if (++stage == C::kStages) stage = 0, phase ^= 1u;
+        }
+      }
+      // Drain: every load issued above must have landed before this CTA's shared memory is
+      // released.  The consumer arrives on `empty` only after `full` completed, so waiting
+      // for the ring to become empty again (bounded) covers all loads in flight.
+      for (int s = 0; s < C::kStages; ++s) {
+        const int st = (stage + s) % C::kStages;
+        const uint32_t ph = (st >= stage) ? phase : (phase ^ 1u);
+        if (!ptx::mbar_wait(empty_bar + st, ph ^ 1u)) {
+          raise_timeout(p.status, 2);
+          break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = NVF4 ? ptx::idesc_nvf4(kBM, BN) : ptx::idesc_f8(kBM, BN);
+      const uint32_t tmem_sfa = tmem_base + C::kAccStages * BN;
+      const uint32_t tmem_sfb = tmem_sfa + 16;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!ptx::mbar_wait(acc_empty + acc, acc_phase ^ 1u)) {
+          raise_timeout(p.status, 3);
+          *abort_flag = 1;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kt = 0; kt < k_tiles; ++kt) {
+          if (!ptx::mbar_wait(full_bar + stage, phase)) {
+            raise_timeout(p.status, 4);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = ptx::smem_u32(smem + stage * C::kStageBytes);
+          const uint32_t sb = sa + C::kABytes;
+          int kblocks = kBKBytes / kMmaKBytes;
+          if constexpr (NVF4) {
+            kblocks = min(4, p.sf_col_tiles - kt * 4);
+            const uint32_t ssfa = sb + C::kBBytes;
+            const uint32_t ssfb = ssfa + C::kSfaBytes;
+            for (int kb = 0; kb < kblocks; ++kb) {
+              ptx::tmem_cp_sf<1>(tmem_sfa + kb * 4, ptx::smem_desc_sf(ssfa + kb * 512));
+              for (int j = 0; j < BN / 128; ++j)
+                ptx::tmem_cp_sf<1>(tmem_sfb + kb * (BN / 32) + j * 4, ptx::smem_desc_sf(ssfb + j * 2048 + kb * 512));
+            }
+          }
+          const uint64_t da = ptx::smem_desc_sw128(sa), db = ptx::smem_desc_sw128(sb);
+          for (int kb = 0; kb < kblocks; ++kb) {
+            const uint32_t accum = (kt > 0 || kb > 0) ? 1u : 0u;
+            const uint64_t adv = static_cast<uint64_t>((kb * kMmaKBytes) >> 4);
+            if constexpr (NVF4)
+              ptx::mma_nvf4<1>(tmem_d, da + adv, db + adv, idesc, accum, tmem_sfa + kb * 4, tmem_sfb + kb * (BN / 32));
+            else
+              ptx::mma_f8<1>(tmem_d, da + adv, db + adv, idesc, accum);
+          }
+          ptx::tc_commit<1>(empty_bar + stage);  // stage reusable once these MMAs (and copies) retire
+          if (++stage == C::kStages) stage = 0, phase ^= 1u;
+        }
+        if (ok) ptx::tc_commit<1>(acc_full + acc);  // accumulator complete
+        if (++acc == C::kAccStages) acc = 0, acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    const int et = threadIdx.x - 64;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int buf = 0;
+    bool dead = false;
+    float gscale = 1.0f;
+    if constexpr (NVF4) gscale = __fmul_rn(__ldg(p.a_scales), __ldg(p.b_scales));
+    const bool vec_ok = (p.N % 8) == 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int mb, nb;
+      tile_coord(t, mb, nb);
+      const int n0 = nb * BN;
+      float* colscale = epi + buf * 2 * BN;
+      float* colbias = colscale + BN;
+      for (int i = et; i < BN; i += 128) {
+        const int n = n0 + i;
+        float s = 1.0f, b = 0.0f;
+        if (n < p.N) {
+          if constexpr (!NVF4) s = __ldg(p.b_scales + static_cast<int64_t>(n) * p.b_scale_stride);
+          if (p.bias != nullptr) b = __bfloat162float(p.bias[n]);
+        }
+        colscale[i] = s;
+        colbias[i] = b;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      buf ^= 1;
+
+      // A warp whose wait gave up keeps walking the tile list (so the named barrier above
+      // stays matched) but touches neither tensor memory nor the output again.
+      if (dead) continue;
+      if (!ptx::mbar_wait(acc_full + acc, acc_phase)) {
+        raise_timeout(p.status, 5);
+        dead = true;
+        continue;
+      }
+      ptx::tc_fence_after();
+      const int row = mb * kBM + q * 32 + lane;
+      float rscale = gscale;
+      if constexpr (!NVF4) rscale = (row < p.M) ? __ldg(p.a_scales + static_cast<int64_t>(row) * p.a_scale_stride) : 0.0f;
+      __nv_bfloat16* orow = p.out + static_cast<int64_t>(row) * p.N + n0;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr + c * 32, r);
+        ptx::tmem_ld_wait();
+        if (row < p.M) {
+          const int cbase = n0 + c * 32;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int i0 = c * 32 + v * 8 + 2 * j;
+              const float x0 = fmaf(__uint_as_float(r[v * 8 + 2 * j]) * rscale, colscale[i0], colbias[i0]);
+              const float x1 = fmaf(__uint_as_float(r[v * 8 + 2 * j + 1]) * rscale, colscale[i0 + 1], colbias[i0 + 1]);
+              __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+              w[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            const int col = cbase + v * 8;
+            if (vec_ok && col + 8 <= p.N) {
+              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (col + j < p.N) {
+                  const uint32_t word = w[j >> 1];
+                  const uint16_t hbits = (j & 1) ? static_cast<uint16_t>(word >> 16) : static_cast<uint16_t>(word & 0xffffu);
+                  reinterpret_cast<uint16_t*>(orow)[c * 32 + v * 8 + j] = hbits;
+                }
+              }
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(acc_empty + acc);
+      if (++acc == C::kAccStages) acc = 0, acc_phase ^= 1u;
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc<1>(tmem_base, C::kTmemCols);
+  }
+}
+
+}  // namespace gemm
+}  // namespace b200q

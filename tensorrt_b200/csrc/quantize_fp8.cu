@@ -1,0 +1,355 @@
+// FP8 E4M3 quantize / fake-quantize / dequantize and the abs-max reductions.
+//
+// All kernels are HBM-bound streaming kernels: 128-bit coalesced loads, warp-shuffle
+// abs-max reductions, the row kept in registers between the amax pass and the quantize
+// pass so that every input byte is read from DRAM once.
+//
+// Arithmetic contract (identical to the CPU restatement the tests compare against):
+//   scale = amax / 448 (fp32 division; 0 -> 1)
+//   code  = e4m3_rne_sat(x_fp32 / scale)
+//   fake-quant output = fp32(code) * scale, rounded (RNE) to the input dtype.
+#include "common.cuh"
+
+namespace b200q {
+
+namespace {
+
+constexpr int kRowThreads = 256;
+constexpr int kMaxItems = 8;  // 8-element groups a thread keeps in registers between the two passes
+
+// ---------------------------------------------------------------- block reduce
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* smem) {
+  v = warp_max(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float r = (lane < THREADS / 32) ? smem[lane] : 0.0f;
+  r = warp_max(r);
+  __syncthreads();
+  return r;
+}
+
+// ---------------------------------------------------------------- row kernels
+enum class Out { Codes, Fake };
+
+// One CTA per row.  ITEMS groups of 8 elements per thread stay in registers when the row
+// fits (cols <= THREADS * 8 * ITEMS); otherwise (ITEMS == 0) the row is streamed twice and
+// the second pass hits L2.
+//   AMAX_MODE 0: dynamic (reduce the row), 1: amax[0], 2: amax[row]
+template <typename T, int ITEMS, int AMAX_MODE, Out OUT>
+__global__ void __launch_bounds__(kRowThreads)
+fp8_rows_kernel(const T* __restrict__ x, const float* __restrict__ amax, uint8_t* __restrict__ codes,
+                T* __restrict__ fake, float* __restrict__ scales, int64_t rows, int64_t cols) {
+  __shared__ float red[kRowThreads / 32];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * cols;
+  const int groups = static_cast<int>(cols >> 3);
+
+  float v[ITEMS > 0 ? ITEMS : 1][8];
+  float local = 0.0f;
+  if constexpr (ITEMS > 0) {
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const int g = threadIdx.x + i * kRowThreads;
+      if (g < groups) {
+        Elem<T>::load8(xr + (int64_t)g * 8, v[i]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+      }
+    }
+    if constexpr (AMAX_MODE == 0) {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) local = fmaxf(local, fabsf(v[i][j]));
+    }
+  } else if constexpr (AMAX_MODE == 0) {
+    for (int g = threadIdx.x; g < groups; g += kRowThreads) {
+      float t[8];
+      Elem<T>::load8(xr + (int64_t)g * 8, t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) local = fmaxf(local, fabsf(t[j]));
+    }
+  }
+
+  float a;
+  if constexpr (AMAX_MODE == 0) {
+    a = block_max<kRowThreads>(local, red);
+  } else if constexpr (AMAX_MODE == 1) {
+    a = __ldg(amax);
+  } else {
+    a = __ldg(amax + row);
+  }
+  const float scale = fp8_scale_from_amax(a);
+  if (threadIdx.x == 0 && scales != nullptr && (AMAX_MODE != 1 || row == 0)) scales[AMAX_MODE == 1 ? 0 : row] = scale;
+
+  const SharedDivisor dv(scale);
+  const float lim = __fmul_rn(scale, 512.0f);
+
+  auto emit = [&](int g, const float* t) {
+    uint32_t lo = f32x2_to_e4m3x2(dv.div(t[0], lim), dv.div(t[1], lim)) |
+                  (f32x2_to_e4m3x2(dv.div(t[2], lim), dv.div(t[3], lim)) << 16);
+    uint32_t hi = f32x2_to_e4m3x2(dv.div(t[4], lim), dv.div(t[5], lim)) |
+                  (f32x2_to_e4m3x2(dv.div(t[6], lim), dv.div(t[7], lim)) << 16);
+    if constexpr (OUT == Out::Codes) {
+      *reinterpret_cast<uint2*>(codes + row * cols + (int64_t)g * 8) = make_uint2(lo, hi);
+    } else {
+      float o[8];
+      float2 p;
+      p = e4m3x2_to_f32x2(lo), o[0] = __fmul_rn(p.x, scale), o[1] = __fmul_rn(p.y, scale);
+      p = e4m3x2_to_f32x2(lo >> 16), o[2] = __fmul_rn(p.x, scale), o[3] = __fmul_rn(p.y, scale);
+      p = e4m3x2_to_f32x2(hi), o[4] = __fmul_rn(p.x, scale), o[5] = __fmul_rn(p.y, scale);
+      p = e4m3x2_to_f32x2(hi >> 16), o[6] = __fmul_rn(p.x, scale), o[7] = __fmul_rn(p.y, scale);
+      Elem<T>::store8(fake + row * cols + (int64_t)g * 8, o);
+    }
+  };
+
+  if constexpr (ITEMS > 0) {
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const int g = threadIdx.x + i * kRowThreads;
+      if (g < groups) emit(g, v[i]);
+    }
+  } else {
+    for (int g = threadIdx.x; g < groups; g += kRowThreads) {
+      float t[8];
+      Elem<T>::load8(xr + (int64_t)g * 8, t);
+      emit(g, t);
+    }
+  }
+}
+
+template <typename T, int AMAX_MODE, Out OUT>
+int launch_rows_items(const T* x, const float* amax, uint8_t* codes, T* fake, float* scales, int64_t rows,
+                      int64_t cols, cudaStream_t st) {
+  const int64_t groups = cols >> 3;
+  const int items = static_cast<int>((groups + kRowThreads - 1) / kRowThreads);
+  dim3 grid(static_cast<unsigned>(rows)), block(kRowThreads);
+#define B200Q_ROWS(I) fp8_rows_kernel<T, I, AMAX_MODE, OUT><<<grid, block, 0, st>>>(x, amax, codes, fake, scales, rows, cols)
+  if (items <= 1) B200Q_ROWS(1);
+  else if (items <= 2) B200Q_ROWS(2);
+  else if (items <= 4) B200Q_ROWS(4);
+  else if (items <= kMaxItems) B200Q_ROWS(8);
+  else B200Q_ROWS(0);
+#undef B200Q_ROWS
+  return check_launch();
+}
+
+template <typename T, Out OUT>
+int launch_rows(const void* x, const float* amax, int64_t amax_numel, uint8_t* codes, void* fake, float* scales,
+                int64_t rows, int64_t cols, cudaStream_t st) {
+  const T* xt = static_cast<const T*>(x);
+  T* ft = static_cast<T*>(fake);
+  if (amax_numel == 0) return launch_rows_items<T, 0, OUT>(xt, amax, codes, ft, scales, rows, cols, st);
+  if (amax_numel == 1) return launch_rows_items<T, 1, OUT>(xt, amax, codes, ft, scales, rows, cols, st);
+  return launch_rows_items<T, 2, OUT>(xt, amax, codes, ft, scales, rows, cols, st);
+}
+
+int validate_rows(const void* x, int dtype, int64_t rows, int64_t cols, const float* amax, int64_t amax_numel,
+                  const void* out, int64_t col_multiple) {
+  if (x == nullptr || out == nullptr || rows < 0 || cols < 0) return B200Q_ERR_INVALID;
+  if (dtype != B200Q_F32 && dtype != B200Q_F16 && dtype != B200Q_BF16) return B200Q_ERR_INVALID;
+  if (amax_numel != 0 && amax_numel != 1 && amax_numel != rows) return B200Q_ERR_INVALID;
+  if (amax_numel != 0 && amax == nullptr) return B200Q_ERR_INVALID;
+  if (cols % col_multiple != 0) return B200Q_ERR_INVALID;
+  if (rows > 0x7fffffffLL) return B200Q_ERR_INVALID;
+  if (!aligned(x, 16) || !aligned(out, 16)) return B200Q_ERR_ALIGN;
+  return B200Q_OK;
+}
+
+// ---------------------------------------------------------------- dequantize
+template <typename T>
+__global__ void __launch_bounds__(256)
+fp8_dequant_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ scales, int per_row, T* __restrict__ out,
+                   int64_t rows, int64_t cols) {
+  const int64_t groups_per_row = cols >> 3;
+  const int64_t total = rows * groups_per_row;
+  for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = g / groups_per_row;
+    const float s = __ldg(scales + (per_row ? row : 0));
+    const uint2 c = *reinterpret_cast<const uint2*>(codes + g * 8);
+    float o[8];
+    float2 p;
+    p = e4m3x2_to_f32x2(c.x), o[0] = __fmul_rn(p.x, s), o[1] = __fmul_rn(p.y, s);
+    p = e4m3x2_to_f32x2(c.x >> 16), o[2] = __fmul_rn(p.x, s), o[3] = __fmul_rn(p.y, s);
+    p = e4m3x2_to_f32x2(c.y), o[4] = __fmul_rn(p.x, s), o[5] = __fmul_rn(p.y, s);
+    p = e4m3x2_to_f32x2(c.y >> 16), o[6] = __fmul_rn(p.x, s), o[7] = __fmul_rn(p.y, s);
+    Elem<T>::store8(out + g * 8, o);
+  }
+}
+
+// ---------------------------------------------------------------- amax reductions
+constexpr int kAmaxBlocks = 148 * 8;
+constexpr int kAmaxThreads = 256;
+
+// Single-pass tensor abs-max.  Every CTA writes its partial maximum to `partials`, takes a
+// ticket; the last CTA to arrive reduces the partials, writes the result and re-arms the
+// ticket counter (so the workspace is zero again when the kernel ends).
+template <typename T>
+__global__ void __launch_bounds__(kAmaxThreads)
+amax_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ out, float* __restrict__ partials,
+            unsigned int* __restrict__ ticket) {
+  __shared__ float red[kAmaxThreads / 32];
+  __shared__ bool last;
+  float local = 0.0f;
+  const int64_t groups = n >> 3;
+  for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < groups; g += (int64_t)gridDim.x * blockDim.x) {
+    float t[8];
+    Elem<T>::load8(x + g * 8, t);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) local = fmaxf(local, fabsf(t[j]));
+  }
+  if (blockIdx.x == 0) {  // ragged tail (n % 8 elements), scalar
+    for (int64_t i = (groups << 3) + threadIdx.x; i < n; i += blockDim.x) local = fmaxf(local, fabsf(static_cast<float>(x[i])));
+  }
+  const float m = block_max<kAmaxThreads>(local, red);
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = m;
+    __threadfence();
+    const unsigned int t = atomicAdd(ticket, 1u);
+    last = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (last) {
+    __threadfence();
+    float r = 0.0f;
+    for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) r = fmaxf(r, __ldcg(partials + i));
+    r = block_max<kAmaxThreads>(r, red);
+    if (threadIdx.x == 0) {
+      out[0] = r;
+      *ticket = 0u;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+row_amax_kernel(const T* __restrict__ x, float* __restrict__ out, int64_t rows, int64_t cols) {
+  __shared__ float red[kRowThreads / 32];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * cols;
+  const int groups = static_cast<int>(cols >> 3);
+  float local = 0.0f;
+  for (int g = threadIdx.x; g < groups; g += kRowThreads) {
+    float t[8];
+    Elem<T>::load8(xr + (int64_t)g * 8, t);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) local = fmaxf(local, fabsf(t[j]));
+  }
+  const float m = block_max<kRowThreads>(local, red);
+  if (threadIdx.x == 0) out[row] = m;
+}
+
+}  // namespace
+
+// launcher used by the entry points below and by the no-scratch variants elsewhere
+int launch_amax(const void* x, int dtype, int64_t n, float* out, float* partials, unsigned int* ticket,
+                cudaStream_t st) {
+  const int64_t groups = n >> 3;
+  int blocks = static_cast<int>(groups / kAmaxThreads);
+  blocks = blocks < 1 ? 1 : (blocks > kAmaxBlocks ? kAmaxBlocks : blocks);
+  switch (dtype) {
+    case B200Q_BF16:
+      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), n, out, partials, ticket);
+      break;
+    case B200Q_F16:
+      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __half*>(x), n, out, partials, ticket);
+      break;
+    case B200Q_F32:
+      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const float*>(x), n, out, partials, ticket);
+      break;
+    default:
+      return B200Q_ERR_INVALID;
+  }
+  return check_launch();
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+size_t b200q_amax_workspace_bytes(void) { return (kAmaxBlocks + 64) * sizeof(float); }
+
+int b200q_amax(const void* x, int dtype, int64_t n, float* amax_out, void* workspace, size_t workspace_bytes,
+               b200q_stream_t stream) {
+  if (x == nullptr || amax_out == nullptr || n < 0) return B200Q_ERR_INVALID;
+  if (workspace == nullptr || workspace_bytes < b200q_amax_workspace_bytes()) return B200Q_ERR_WORKSPACE;
+  if (!aligned(x, 16) || !aligned(workspace, 16)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  // layout: [0, 64) floats reserved for the ticket counter (first word), then the partials
+  unsigned int* ticket = static_cast<unsigned int*>(workspace);
+  float* partials = static_cast<float*>(workspace) + 64;
+  return launch_amax(x, dtype, n, amax_out, partials, ticket, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_row_amax(const void* x, int dtype, int64_t rows, int64_t cols, float* amax_out, b200q_stream_t stream) {
+  if (x == nullptr || amax_out == nullptr || rows < 0 || cols < 0 || cols % 8 != 0 || rows > 0x7fffffffLL)
+    return B200Q_ERR_INVALID;
+  if (!aligned(x, 16)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  if (rows == 0) return B200Q_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(static_cast<unsigned>(rows)), block(kRowThreads);
+  switch (dtype) {
+    case B200Q_BF16: row_amax_kernel<<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16*>(x), amax_out, rows, cols); break;
+    case B200Q_F16: row_amax_kernel<<<grid, block, 0, st>>>(static_cast<const __half*>(x), amax_out, rows, cols); break;
+    case B200Q_F32: row_amax_kernel<<<grid, block, 0, st>>>(static_cast<const float*>(x), amax_out, rows, cols); break;
+    default: return B200Q_ERR_INVALID;
+  }
+  return check_launch();
+}
+
+int b200q_fp8_quantize(const void* x, int dtype, int64_t rows, int64_t cols, const float* amax, int64_t amax_numel,
+                       uint8_t* codes_out, float* scales_out, b200q_stream_t stream) {
+  if (int rc = validate_rows(x, dtype, rows, cols, amax, amax_numel, codes_out, 16)) return rc;
+  if (amax_numel != 1 && scales_out == nullptr) return B200Q_ERR_INVALID;
+  if (int rc = check_arch()) return rc;
+  if (rows == 0 || cols == 0) return B200Q_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case B200Q_BF16: return launch_rows<__nv_bfloat16, Out::Codes>(x, amax, amax_numel, codes_out, nullptr, scales_out, rows, cols, st);
+    case B200Q_F16: return launch_rows<__half, Out::Codes>(x, amax, amax_numel, codes_out, nullptr, scales_out, rows, cols, st);
+    default: return launch_rows<float, Out::Codes>(x, amax, amax_numel, codes_out, nullptr, scales_out, rows, cols, st);
+  }
+}
+
+int b200q_fp8_fake_quantize(const void* x, int dtype, int64_t rows, int64_t cols, const float* amax,
+                            int64_t amax_numel, void* out, b200q_stream_t stream) {
+  if (int rc = validate_rows(x, dtype, rows, cols, amax, amax_numel, out, 8)) return rc;
+  if (int rc = check_arch()) return rc;
+  if (rows == 0 || cols == 0) return B200Q_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case B200Q_BF16: return launch_rows<__nv_bfloat16, Out::Fake>(x, amax, amax_numel, nullptr, out, nullptr, rows, cols, st);
+    case B200Q_F16: return launch_rows<__half, Out::Fake>(x, amax, amax_numel, nullptr, out, nullptr, rows, cols, st);
+    default: return launch_rows<float, Out::Fake>(x, amax, amax_numel, nullptr, out, nullptr, rows, cols, st);
+  }
+}
+
+int b200q_fp8_dequantize(const uint8_t* codes, const float* scales, int64_t scales_numel, int64_t rows, int64_t cols,
+                         void* out, int dtype, b200q_stream_t stream) {
+  if (codes == nullptr || scales == nullptr || out == nullptr || rows < 0 || cols < 0 || cols % 8 != 0)
+    return B200Q_ERR_INVALID;
+  if (scales_numel != 1 && scales_numel != rows) return B200Q_ERR_INVALID;
+  if (!aligned(codes, 8) || !aligned(out, 16)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  if (rows == 0 || cols == 0) return B200Q_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t total = rows * (cols >> 3);
+  int blocks = static_cast<int>((total + 255) / 256);
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+  const int per_row = (scales_numel == rows && scales_numel != 1) ? 1 : 0;
+  switch (dtype) {
+    case B200Q_BF16: fp8_dequant_kernel<<<blocks, 256, 0, st>>>(codes, scales, per_row, static_cast<__nv_bfloat16*>(out), rows, cols); break;
+    case B200Q_F16: fp8_dequant_kernel<<<blocks, 256, 0, st>>>(codes, scales, per_row, static_cast<__half*>(out), rows, cols); break;
+    case B200Q_F32: fp8_dequant_kernel<<<blocks, 256, 0, st>>>(codes, scales, per_row, static_cast<float*>(out), rows, cols); break;
+    default: return B200Q_ERR_INVALID;
+  }
+  return check_launch();
+}
+
+}  // extern "C"
