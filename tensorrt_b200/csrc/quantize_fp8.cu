@@ -149,7 +149,9 @@ int launch_rows(const void* x, const float* amax, int64_t amax_numel, uint8_t* c
 
 int validate_rows(const void* x, int dtype, int64_t rows, int64_t cols, const float* amax, int64_t amax_numel,
                   const void* out, int64_t col_multiple) {
-  if (x == nullptr || out == nullptr || rows < 0 || cols < 0) return B200Q_ERR_INVALID;
+  if (rows < 0 || cols < 0) return B200Q_ERR_INVALID;
+  if (rows == 0 || cols == 0) return B200Q_OK;  // empty tensors are a valid no-op, whatever the pointers
+  if (x == nullptr || out == nullptr) return B200Q_ERR_INVALID;
   if (dtype != B200Q_F32 && dtype != B200Q_F16 && dtype != B200Q_BF16) return B200Q_ERR_INVALID;
   if (amax_numel != 0 && amax_numel != 1 && amax_numel != rows) return B200Q_ERR_INVALID;
   if (amax_numel != 0 && amax == nullptr) return B200Q_ERR_INVALID;
@@ -306,9 +308,9 @@ int b200q_row_amax(const void* x, int dtype, int64_t rows, int64_t cols, float* 
 int b200q_fp8_quantize(const void* x, int dtype, int64_t rows, int64_t cols, const float* amax, int64_t amax_numel,
                        uint8_t* codes_out, float* scales_out, b200q_stream_t stream) {
   if (int rc = validate_rows(x, dtype, rows, cols, amax, amax_numel, codes_out, 16)) return rc;
+  if (rows == 0 || cols == 0) return B200Q_OK;
   if (amax_numel != 1 && scales_out == nullptr) return B200Q_ERR_INVALID;
   if (int rc = check_arch()) return rc;
-  if (rows == 0 || cols == 0) return B200Q_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case B200Q_BF16: return launch_rows<__nv_bfloat16, Out::Codes>(x, amax, amax_numel, codes_out, nullptr, scales_out, rows, cols, st);
@@ -320,8 +322,8 @@ int b200q_fp8_quantize(const void* x, int dtype, int64_t rows, int64_t cols, con
 int b200q_fp8_fake_quantize(const void* x, int dtype, int64_t rows, int64_t cols, const float* amax,
                             int64_t amax_numel, void* out, b200q_stream_t stream) {
   if (int rc = validate_rows(x, dtype, rows, cols, amax, amax_numel, out, 8)) return rc;
-  if (int rc = check_arch()) return rc;
   if (rows == 0 || cols == 0) return B200Q_OK;
+  if (int rc = check_arch()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case B200Q_BF16: return launch_rows<__nv_bfloat16, Out::Fake>(x, amax, amax_numel, nullptr, out, nullptr, rows, cols, st);

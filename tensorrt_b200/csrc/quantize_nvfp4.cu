@@ -194,7 +194,9 @@ int launch(const void* x, const float* amax, uint8_t* codes, uint8_t* sf, void* 
 }
 
 int validate(const void* x, int dtype, int64_t rows, int64_t cols, const float* amax) {
-  if (x == nullptr || amax == nullptr || rows < 0 || cols < 0) return B200Q_ERR_INVALID;
+  if (rows < 0 || cols < 0) return B200Q_ERR_INVALID;
+  if (rows == 0 || cols == 0) return B200Q_OK;  // empty tensors are a valid no-op, whatever the pointers
+  if (x == nullptr || amax == nullptr) return B200Q_ERR_INVALID;
   if (dtype != B200Q_F32 && dtype != B200Q_F16 && dtype != B200Q_BF16) return B200Q_ERR_INVALID;
   if (cols % 16 != 0) return B200Q_ERR_INVALID;
   if (!aligned(x, 32)) return B200Q_ERR_ALIGN;
@@ -217,6 +219,7 @@ size_t b200q_nvfp4_scale_bytes(int64_t rows, int64_t cols) {
 int b200q_nvfp4_quantize(const void* x, int dtype, int64_t rows, int64_t cols, const float* amax, uint8_t* codes_out,
                          uint8_t* scales_out, float* global_scale_out, b200q_stream_t stream) {
   if (int rc = validate(x, dtype, rows, cols, amax)) return rc;
+  if (rows == 0 || cols == 0) return B200Q_OK;
   if (codes_out == nullptr || scales_out == nullptr) return B200Q_ERR_INVALID;
   if (!aligned(codes_out, 8) || !aligned(scales_out, 16)) return B200Q_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
@@ -239,6 +242,7 @@ int b200q_nvfp4_quantize(const void* x, int dtype, int64_t rows, int64_t cols, c
 int b200q_nvfp4_fake_quantize(const void* x, int dtype, int64_t rows, int64_t cols, const float* amax, void* out,
                               b200q_stream_t stream) {
   if (int rc = validate(x, dtype, rows, cols, amax)) return rc;
+  if (rows == 0 || cols == 0) return B200Q_OK;
   if (out == nullptr) return B200Q_ERR_INVALID;
   if (!aligned(out, 32)) return B200Q_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
