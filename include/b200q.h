@@ -32,6 +32,7 @@ extern "C" {
 #define B200Q_ERR_CUDA (-4)      /* a CUDA runtime / driver call failed                */
 #define B200Q_ERR_WORKSPACE (-5) /* workspace missing or too small                     */
 #define B200Q_ERR_TIMEOUT (-6)   /* a bounded device-side wait gave up                 */
+#define B200Q_ERR_TOO_LARGE (-7) /* size beyond what a fixed built-in scratch can serve    */
 
 #define B200Q_F32 0
 #define B200Q_F16 1
@@ -59,6 +60,26 @@ int b200q_amax(const void* x, int dtype, int64_t n, float* amax_out, void* works
                size_t workspace_bytes, b200q_stream_t stream);
 int b200q_row_amax(const void* x, int dtype, int64_t rows, int64_t cols, float* amax_out,
                    b200q_stream_t stream);
+
+/* b200q_amax_static: the same tensor abs-max for callers that have no way to provide a
+ * workspace.  No counterpart in the reference; it exists because some hosts of this library
+ * must not allocate device memory at the point where they call it: a TensorRT plugin's
+ * enqueue() only gets the workspace TensorRT sized at build time, a stream being captured
+ * into a CUDA graph rejects cudaMalloc, and a serving process may have handed all device
+ * memory to its own pool.  The per-CTA partial maxima and the ticket counter live in a
+ * 4352-byte array compiled into the library (every GPU that loads the library holds it
+ * until the process exits), so nothing is allocated or freed here, by this library or by
+ * any library it calls.
+ *   - n may be at most b200q_amax_static_max_elements() (2^28: one partial per 2^18-element
+ *     chunk, 1024 partials); larger n returns B200Q_ERR_TOO_LARGE and launches nothing.
+ *   - The first call on each device looks up the array's device address (a host-side
+ *     runtime query); make that first call outside any stream capture.
+ *   - All calls on a device share the one array: calls that can overlap on the GPU (two
+ *     streams, two host threads) race with each other and give wrong results; serialise
+ *     them or use b200q_amax with separate workspaces.
+ * Results are identical to b200q_amax. */
+int64_t b200q_amax_static_max_elements(void);
+int b200q_amax_static(const void* x, int dtype, int64_t n, float* amax_out, b200q_stream_t stream);
 
 /* ------------------------------------------------------------------ FP8 E4M3
  * Replaces the Q half of the IQuantizeLayer/IDequantizeLayer pair built by

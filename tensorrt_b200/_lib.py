@@ -23,6 +23,8 @@ SIGNATURES = {
     "b200q_amax_workspace_bytes": (_c.c_size_t, []),
     "b200q_amax": (_c.c_int, [_p, _c.c_int, _i64, _p, _p, _c.c_size_t, _p]),
     "b200q_row_amax": (_c.c_int, [_p, _c.c_int, _i64, _i64, _p, _p]),
+    "b200q_amax_static_max_elements": (_i64, []),
+    "b200q_amax_static": (_c.c_int, [_p, _c.c_int, _i64, _p, _p]),
     "b200q_fp8_quantize": (_c.c_int, [_p, _c.c_int, _i64, _i64, _p, _i64, _p, _p, _p]),
     "b200q_fp8_fake_quantize": (_c.c_int, [_p, _c.c_int, _i64, _i64, _p, _i64, _p, _p]),
     "b200q_fp8_dequantize": (_c.c_int, [_p, _p, _i64, _i64, _i64, _p, _c.c_int, _p]),

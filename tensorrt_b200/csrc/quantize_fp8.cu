@@ -8,6 +8,8 @@
 //   scale = amax / 448 (fp32 division; 0 -> 1)
 //   code  = e4m3_rne_sat(x_fp32 / scale)
 //   fake-quant output = fp32(code) * scale, rounded (RNE) to the input dtype.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200q {
@@ -268,6 +270,57 @@ int launch_amax(const void* x, int dtype, int64_t n, float* out, float* partials
   return check_launch();
 }
 
+// ---------------------------------------------------------------- abs-max without a caller workspace
+// Scratch of b200q_amax_static: the ticket counter lives in the first 256 bytes, one partial
+// maximum per CTA follows.  Zero at module load; the kernel re-arms the ticket when it ends
+// and every partial that is read was written by the same launch.
+constexpr int kStaticAmaxMaxBlocks = 1024;
+constexpr int64_t kStaticAmaxElemsPerBlock = 1 << 18;
+static __device__ __align__(256) unsigned char g_amax_static_scratch[256 + kStaticAmaxMaxBlocks * sizeof(float)];
+
+namespace {
+std::mutex g_static_mu;
+unsigned char* g_static_scratch_addr[64] = {};
+
+// Device address of the scratch array on the current device.  In host code the array's name
+// is only a handle for the runtime, so the address is asked for once per device.
+int static_scratch_address(unsigned char** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200Q_ERR_CUDA;
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    unsigned char* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_amax_static_scratch) != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return B200Q_ERR_CUDA;
+    }
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return B200Q_OK;
+}
+
+int launch_amax_static(const void* x, int dtype, int64_t n, float* out, float* partials, unsigned int* ticket,
+                       cudaStream_t st) {
+  int blocks = static_cast<int>((n + kStaticAmaxElemsPerBlock - 1) / kStaticAmaxElemsPerBlock);
+  if (blocks < 1) blocks = 1;
+  switch (dtype) {
+    case B200Q_BF16:
+      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), n, out, partials, ticket);
+      break;
+    case B200Q_F16:
+      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __half*>(x), n, out, partials, ticket);
+      break;
+    case B200Q_F32:
+      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const float*>(x), n, out, partials, ticket);
+      break;
+    default:
+      return B200Q_ERR_INVALID;
+  }
+  return check_launch();
+}
+}  // namespace
+
 }  // namespace b200q
 
 using namespace b200q;
@@ -352,6 +405,21 @@ int b200q_fp8_dequantize(const uint8_t* codes, const float* scales, int64_t scal
     default: return B200Q_ERR_INVALID;
   }
   return check_launch();
+}
+
+int64_t b200q_amax_static_max_elements(void) { return kStaticAmaxMaxBlocks * kStaticAmaxElemsPerBlock; }
+
+int b200q_amax_static(const void* x, int dtype, int64_t n, float* amax_out, b200q_stream_t stream) {
+  if (x == nullptr || amax_out == nullptr || n < 0) return B200Q_ERR_INVALID;
+  if (dtype != B200Q_F32 && dtype != B200Q_F16 && dtype != B200Q_BF16) return B200Q_ERR_INVALID;
+  if (n > b200q_amax_static_max_elements()) return B200Q_ERR_TOO_LARGE;
+  if (!aligned(x, 16)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  unsigned char* scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch)) return rc;
+  unsigned int* ticket = reinterpret_cast<unsigned int*>(scratch);
+  float* partials = reinterpret_cast<float*>(scratch + 256);
+  return launch_amax_static(x, dtype, n, amax_out, partials, ticket, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -54,6 +54,7 @@ const char* b200q_status_string(int status) {
     case B200Q_ERR_CUDA: return "CUDA runtime or driver call failed";
     case B200Q_ERR_WORKSPACE: return "workspace missing or too small";
     case B200Q_ERR_TIMEOUT: return "device-side bounded wait timed out";
+    case B200Q_ERR_TOO_LARGE: return "size exceeds the capacity of the built-in scratch of this entry point";
     default: return "unknown status";
   }
 }
