@@ -258,6 +258,36 @@ def gemm_extras(capi, peaks, quick=True):
     return out
 
 
+def quantize_extras(capi):
+    """Device-timed GB/s of the other memory-bound kernels on inputs larger than L2."""
+    out = {}
+
+    def time_it(fn, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    for rows, cols in ((16384, 4096), (8192, 8192), (16384, 14336)):
+        xs = [torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16) for _ in range(3)]
+        n = rows * cols
+        ms = time_it(lambda i=0: capi.fp8_quantize(xs[i % 3], None))
+        out[f"fp8_per_token_quantize_{rows}x{cols}"] = {"ms": round(ms, 4), "GBps": round((3 * n + 4 * rows) / ms / 1e6, 1)}
+        ms = time_it(lambda i=0: capi.amax(xs[i % 3]))
+        out[f"amax_{rows}x{cols}"] = {"ms": round(ms, 4), "GBps": round(2 * n / ms / 1e6, 1)}
+        am = capi.amax(xs[0])
+        ms = time_it(lambda i=0: capi.nvfp4_quantize(xs[i % 3], am))
+        out[f"nvfp4_quantize_{rows}x{cols}"] = {"ms": round(ms, 4), "GBps": round(ALG_BYTES_PER_ELEM * n / ms / 1e6, 1)}
+        del xs
+    return out
+
+
 # ----------------------------------------------------------------------------- main arm
 def run_b200(args):
     rank, world, local = dist_setup(args.gpus)
@@ -328,6 +358,7 @@ def run_b200(args):
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
         if not args.no_extras:
             line["extras"] = gemm_extras(capi, peaks)
+            line["extras"]["quantize"] = quantize_extras(capi)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -337,8 +368,8 @@ def run_b200(args):
 
 
 # DRAM bytes (read + write) per launch of the quantize kernel on this workload, from the
-# committed ncu capture (profiles/); None until a capture exists.
-NCU_TRAFFIC_BYTES = None
+# committed ncu capture (profiles/nvfp4_quantize_kernel_bf16_8192x8192.md).
+NCU_TRAFFIC_BYTES = 155_108_352
 
 
 def main():

@@ -160,19 +160,25 @@ __device__ __forceinline__ float with_sign_of(float mag, float src) {
   return __uint_as_float((__float_as_uint(mag) & 0x7fffffffu) | (__float_as_uint(src) & 0x80000000u));
 }
 
-// Divider by a fixed positive divisor; bit-identical to IEEE `a / d` for the codes.
-struct SharedDivisor {
-  float d, y;
-  bool fast;
-  __device__ __forceinline__ explicit SharedDivisor(float d_) : d(d_), y(b200q_rcp_rn(d_)), fast(b200q_div_fast_ok(d_)) {}
-  // |x| / d with the sign of x.  `lim` (>= any quotient that is not already saturated,
-  // times d) bounds the numerator so the fast path cannot overflow.
-  __device__ __forceinline__ float div(float x, float lim) const {
-    float a = fminf(fabsf(x), lim);
-    float q = fast ? b200q_div_by_shared(a, d, y) : __fdiv_rn(a, d);
-    return with_sign_of(q, x);
+// Quotient x / d by one of three routes, all bit-identical to IEEE division wherever the
+// result can influence a code:
+//   kDivFast     shared-divisor sequence on the signed numerator; needs b200q_div_fast_ok(d)
+//                and a quotient that cannot overflow (|x| bounded by a multiple of d)
+//   kDivClamped  same, on |x| clamped to `lim` (any value whose quotient already saturates),
+//                sign restored afterwards; for numerators that may be arbitrarily large
+//   kDivTrue     IEEE division on the clamped numerator; for extreme divisors
+enum DivPath { kDivFast = 0, kDivClamped = 1, kDivTrue = 2 };
+
+template <int PATH>
+__device__ __forceinline__ float div_path(float x, float d, float y, float lim) {
+  if constexpr (PATH == kDivFast) {
+    return b200q_div_by_shared(x, d, y);
+  } else if constexpr (PATH == kDivClamped) {
+    return with_sign_of(b200q_div_by_shared(fminf(fabsf(x), lim), d, y), x);
+  } else {
+    return with_sign_of(__fdiv_rn(fminf(fabsf(x), lim), d), x);
   }
-};
+}
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

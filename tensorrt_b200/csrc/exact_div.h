@@ -5,7 +5,7 @@
  * tensor or a 16-element block.  IEEE division per element costs ~10 instructions; the
  * quantize kernels are HBM-bound only if the per-element instruction count stays low.
  * With y = RN(1/d) computed once per divisor, the quotient is recovered as
- *     q0 = RN(a * y);  r = fma(-d, q0, a)  (exact);  q = fma(r, y, q0)
+ *     q0 = RN(a * y);  r = fma(d, q0, -a)  (exact);  q = fma(-r, y, q0)
  * which equals RN(a / d) whenever no intermediate under/overflows (Markstein's
  * correction step).  `b200q_div_fast_ok` states the divisor range where that holds for
  * every quotient that can influence an E4M3 / E2M1 code (|q| >= 2^-10); outside it the
@@ -52,16 +52,21 @@ B200Q_HD float b200q_rcp_rn(float d) {
 #endif
 }
 
-/* a >= 0 finite, d > 0 with b200q_div_fast_ok(d), y = b200q_rcp_rn(d), a / d < 2^127. */
+/* a finite (either sign, zeros included), d > 0 with b200q_div_fast_ok(d), y = b200q_rcp_rn(d),
+ * |a / d| < 2^127.  The residual is formed as r = d*q0 - a and subtracted again, which is the
+ * same arithmetic as the textbook a - d*q0 but keeps the sign of a zero numerator:
+ * a = -0 gives q0 = -0, r = +0, q = (-0)*y + (-0) = -0. */
 B200Q_HD float b200q_div_by_shared(float a, float d, float y) {
 #if defined(__CUDA_ARCH__)
   float q0 = __fmul_rn(a, y);
-  float r = __fmaf_rn(-d, q0, a);
-  return __fmaf_rn(r, y, q0);
+  float r = __fmaf_rn(d, q0, -a);
+  return __fmaf_rn(-r, y, q0);
 #else
   float q0 = a * y;
-  float r = fmaf(-d, q0, a);
-  return fmaf(r, y, q0);
+  volatile float r = fmaf(d, q0, -a); /* volatile: keeps the host compiler from folding the
+                                         negation below into the fma above, which would lose
+                                         the sign of a zero numerator */
+  return fmaf(-r, y, q0);
 #endif
 }
 

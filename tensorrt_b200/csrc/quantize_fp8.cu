@@ -9,6 +9,7 @@
 //   code  = e4m3_rne_sat(x_fp32 / scale)
 //   fake-quant output = fp32(code) * scale, rounded (RNE) to the input dtype.
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -87,14 +88,19 @@ fp8_rows_kernel(const T* __restrict__ x, const float* __restrict__ amax, uint8_t
   const float scale = fp8_scale_from_amax(a);
   if (threadIdx.x == 0 && scales != nullptr && (AMAX_MODE != 1 || row == 0)) scales[AMAX_MODE == 1 ? 0 : row] = scale;
 
-  const SharedDivisor dv(scale);
-  const float lim = __fmul_rn(scale, 512.0f);
+  const float y = b200q_rcp_rn(scale);
+  const float lim = __fmul_rn(scale, 512.0f);  // |x| >= 512 * scale saturates to 448 anyway
+  // With the amax reduced in this kernel every quotient is <= 448 (1 + 2^-23) and the plain
+  // sequence is safe; a supplied amax may lie below the data, so the numerator is clamped.
+  const int path = !b200q_div_fast_ok(scale) ? kDivTrue : (AMAX_MODE == 0 ? kDivFast : kDivClamped);
 
-  auto emit = [&](int g, const float* t) {
-    uint32_t lo = f32x2_to_e4m3x2(dv.div(t[0], lim), dv.div(t[1], lim)) |
-                  (f32x2_to_e4m3x2(dv.div(t[2], lim), dv.div(t[3], lim)) << 16);
-    uint32_t hi = f32x2_to_e4m3x2(dv.div(t[4], lim), dv.div(t[5], lim)) |
-                  (f32x2_to_e4m3x2(dv.div(t[6], lim), dv.div(t[7], lim)) << 16);
+  auto emit = [&](int g, const float* t, auto path_tag) {
+    constexpr int P = decltype(path_tag)::value;
+    float q[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q[j] = div_path<P>(t[j], scale, y, lim);
+    uint32_t lo = f32x2_to_e4m3x2(q[0], q[1]) | (f32x2_to_e4m3x2(q[2], q[3]) << 16);
+    uint32_t hi = f32x2_to_e4m3x2(q[4], q[5]) | (f32x2_to_e4m3x2(q[6], q[7]) << 16);
     if constexpr (OUT == Out::Codes) {
       *reinterpret_cast<uint2*>(codes + row * cols + (int64_t)g * 8) = make_uint2(lo, hi);
     } else {
@@ -108,19 +114,25 @@ fp8_rows_kernel(const T* __restrict__ x, const float* __restrict__ amax, uint8_t
     }
   };
 
-  if constexpr (ITEMS > 0) {
+  auto emit_all = [&](auto path_tag) {
+    if constexpr (ITEMS > 0) {
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-      const int g = threadIdx.x + i * kRowThreads;
-      if (g < groups) emit(g, v[i]);
+      for (int i = 0; i < ITEMS; ++i) {
+        const int g = threadIdx.x + i * kRowThreads;
+        if (g < groups) emit(g, v[i], path_tag);
+      }
+    } else {
+      for (int g = threadIdx.x; g < groups; g += kRowThreads) {
+        float t[8];
+        Elem<T>::load8(xr + (int64_t)g * 8, t);
+        emit(g, t, path_tag);
+      }
     }
-  } else {
-    for (int g = threadIdx.x; g < groups; g += kRowThreads) {
-      float t[8];
-      Elem<T>::load8(xr + (int64_t)g * 8, t);
-      emit(g, t);
-    }
-  }
+  };
+
+  if (path == kDivFast) emit_all(std::integral_constant<int, kDivFast>{});
+  else if (path == kDivClamped) emit_all(std::integral_constant<int, kDivClamped>{});
+  else emit_all(std::integral_constant<int, kDivTrue>{});
 }
 
 template <typename T, int AMAX_MODE, Out OUT>

@@ -32,9 +32,11 @@ int main(int argc, char** argv){
       ma &= 0x7f0000; a = bits((ea << 23) | ma);
     }
     if (!b200q_div_fast_ok(d)) continue;
+    if (ra & 0x80000000u) a = -a;              /* both signs */
+    if ((i & 0xfffff) == 0) a = (i & 0x100000) ? -0.0f : 0.0f;   /* signed zeros */
     float y = b200q_rcp_rn(d);
     float q = b200q_div_by_shared(a, d, y);
-    if (q != a / d) { if (bad < 5) printf("mismatch a=%a d=%a got=%a want=%a\n", a, d, q, a / d); ++bad; }
+    if (b200q_f32_bits(q) != b200q_f32_bits(a / d)) { if (bad < 5) printf("mismatch a=%a d=%a got=%a want=%a\n", a, d, q, a / d); ++bad; }
   }
   printf("bad=%ld\n", bad);
   return bad != 0;
