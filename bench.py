@@ -380,6 +380,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="nvfp4_quantize")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--shape", default="", help="M,N,K for the GEMM workloads (default: the whole sweep)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

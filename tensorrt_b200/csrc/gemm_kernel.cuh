@@ -41,13 +41,15 @@ struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kAccStages = (NVF4 && BN == 256) ? 1 : 2;
   static constexpr int kSfCols = NVF4 ? (16 + 4 * (BN / 32)) : 0;  // tensor-memory columns holding one K tile of scales
-  static constexpr int kColsNeeded = kAccStages * BN + kSfCols;
-  static constexpr int kTmemCols = kColsNeeded <= 256 ? 256 : 512;
   static constexpr int kTailBytes = 2048;                           // barriers, tmem pointer, epilogue vectors
   static constexpr int kEpiBytes = 2 * 2 * BN * 4;                  // 2 buffers x (col scale, bias) x BN floats
   static constexpr int kStagesRaw = (kSmemLimit - 1024 - kTailBytes - kEpiBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiBytes + kTailBytes;
+  // Each shared-memory stage owns its own scale-factor columns in tensor memory, so the
+  // tcgen05.cp of K tile i+1 never has to wait for the MMAs of K tile i to finish reading.
+  static constexpr int kColsNeeded = kAccStages * BN + kStages * kSfCols;
+  static constexpr int kTmemCols = kColsNeeded <= 256 ? 256 : 512;
   static_assert(kStages >= 3, "pipeline too shallow");
   static_assert(kColsNeeded <= 512, "tensor memory overflow");
 };
@@ -130,6 +132,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int mb, nb;
         tile_coord(t, mb, nb);
+        // per-tile constants of the scale-factor loads
+        const uint8_t* sfa_src = nullptr;
+        const uint8_t* sfb_src[2] = {nullptr, nullptr};
+        uint32_t sf_copies = 0;  // bulk copies per K tile: SFA + the live row tiles of SFB
+        if constexpr (NVF4) {
+          sfa_src = p.sfa + static_cast<int64_t>(mb) * p.sf_col_tiles * 512;
+          sf_copies = 1;
+          for (int j = 0; j < BN / 128; ++j) {
+            const int rt = nb * (BN / 128) + j;
+            if (rt * 128 < p.N) {
+              sfb_src[j] = p.sfb + static_cast<int64_t>(rt) * p.sf_col_tiles * 512;
+              ++sf_copies;
+            }
+          }
+        }
+        const int32_t m0 = mb * kBM, n0 = nb * BN;
         for (int kt = 0; kt < k_tiles; ++kt) {
           if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1u)) {
             raise_timeout(p.status, 1);
@@ -139,27 +157,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
           uint8_t* sa = smem + stage * C::kStageBytes;
           uint8_t* sb = sa + C::kABytes;
-          uint32_t tx = C::kABytes + C::kBBytes;
-          int atoms = 0;
-          if constexpr (NVF4) {
-            atoms = min(4, p.sf_col_tiles - kt * 4);
-            tx += atoms * 512;
-            for (int j = 0; j < BN / 128; ++j)
-              if ((nb * (BN / 128) + j) * 128 < p.N) tx += atoms * 512;
-          }
-          ptx::mbar_arrive_expect_tx(full_bar + stage, tx);
-          ptx::tma_load_2d(sa, &tmap_a, full_bar + stage, kt * kBKBytes, mb * kBM);
-          ptx::tma_load_2d(sb, &tmap_b, full_bar + stage, kt * kBKBytes, nb * BN);
+          uint32_t sf_bytes = 0;
+          if constexpr (NVF4) sf_bytes = static_cast<uint32_t>(min(4, p.sf_col_tiles - kt * 4)) * 512u;
+          ptx::mbar_arrive_expect_tx(full_bar + stage, C::kABytes + C::kBBytes + sf_copies * sf_bytes);
+          ptx::tma_load_2d(sa, &tmap_a, full_bar + stage, kt * kBKBytes, m0);
+          ptx::tma_load_2d(sb, &tmap_b, full_bar + stage, kt * kBKBytes, n0);
           if constexpr (NVF4) {
             uint8_t* ssfa = sb + C::kBBytes;
             uint8_t* ssfb = ssfa + C::kSfaBytes;
-            ptx::bulk_load(ssfa, p.sfa + (static_cast<int64_t>(mb) * p.sf_col_tiles + kt * 4) * 512, atoms * 512, full_bar + stage);
-            for (int j = 0; j < BN / 128; ++j) {
-              const int rt = nb * (BN / 128) + j;
-              if (rt * 128 < p.N)
-                ptx::bulk_load(ssfb + j * 2048, p.sfb + (static_cast<int64_t>(rt) * p.sf_col_tiles + kt * 4) * 512, atoms * 512,
-                               full_bar + stage);
-            }
+            ptx::bulk_load(ssfa, sfa_src + kt * 2048, sf_bytes, full_bar + stage);
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)
+              if (sfb_src[j] != nullptr) ptx::bulk_load(ssfb + j * 2048, sfb_src[j] + kt * 2048, sf_bytes, full_bar + stage);
           }
           if (++stage == C::kStages) stage = 0, phase ^= 1u;
         }
@@ -179,9 +188,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      // This single thread feeds the tensor pipe; its instruction stream per K tile has to
+      // stay well below the ~512 cycles the four MMAs of a K tile take.  Descriptors are
+      // kept as 32-bit low halves that advance by immediates, and the full-K-tile path is
+      // completely unrolled.
       constexpr uint32_t idesc = NVF4 ? ptx::idesc_nvf4(kBM, BN) : ptx::idesc_f8(kBM, BN);
-      const uint32_t tmem_sfa = tmem_base + C::kAccStages * BN;
-      const uint32_t tmem_sfb = tmem_sfa + 16;
+      constexpr uint32_t kStageStep = C::kStageBytes >> 4;
+      const uint32_t smem_u = ptx::smem_u32(smem);
+      const uint32_t a_lo0 = ptx::desc_lo_sw128(smem_u);
+      const uint32_t tmem_sf0 = tmem_base + C::kAccStages * BN;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -203,27 +218,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             break;
           }
           ptx::tc_fence_after();
-          const uint32_t sa = ptx::smem_u32(smem + stage * C::kStageBytes);
-          const uint32_t sb = sa + C::kABytes;
+          const uint32_t a_lo = a_lo0 + stage * kStageStep;          // A tile; B follows at +kABytes
+          const uint32_t b_lo = a_lo + (C::kABytes >> 4);
+          const uint32_t tmem_sfa = tmem_sf0 + stage * C::kSfCols;
+          const uint32_t tmem_sfb = tmem_sfa + 16;
           int kblocks = kBKBytes / kMmaKBytes;
-          if constexpr (NVF4) {
-            kblocks = min(4, p.sf_col_tiles - kt * 4);
-            const uint32_t ssfa = sb + C::kBBytes;
-            const uint32_t ssfb = ssfa + C::kSfaBytes;
-            for (int kb = 0; kb < kblocks; ++kb) {
-              ptx::tmem_cp_sf<1>(tmem_sfa + kb * 4, ptx::smem_desc_sf(ssfa + kb * 512));
-              for (int j = 0; j < BN / 128; ++j)
-                ptx::tmem_cp_sf<1>(tmem_sfb + kb * (BN / 32) + j * 4, ptx::smem_desc_sf(ssfb + j * 2048 + kb * 512));
+          if constexpr (NVF4) kblocks = min(4, p.sf_col_tiles - kt * 4);
+          if (kblocks == 4) {
+            if constexpr (NVF4) {
+              const uint32_t sfa_lo = (b_lo & 0x3fffu) + (C::kBBytes >> 4);   // plain address field, no flags
+              const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
+#pragma unroll
+              for (int kb = 0; kb < 4; ++kb) {
+                ptx::tmem_cp_sf<1>(tmem_sfa + kb * 4, ptx::desc_join(sfa_lo + kb * 32, ptx::kDescHiSf));
+#pragma unroll
+                for (int j = 0; j < BN / 128; ++j)
+                  ptx::tmem_cp_sf<1>(tmem_sfb + kb * (BN / 32) + j * 4, ptx::desc_join(sfb_lo + j * 128 + kb * 32, ptx::kDescHiSf));
+              }
             }
-          }
-          const uint64_t da = ptx::smem_desc_sw128(sa), db = ptx::smem_desc_sw128(sb);
-          for (int kb = 0; kb < kblocks; ++kb) {
-            const uint32_t accum = (kt > 0 || kb > 0) ? 1u : 0u;
-            const uint64_t adv = static_cast<uint64_t>((kb * kMmaKBytes) >> 4);
-            if constexpr (NVF4)
-              ptx::mma_nvf4<1>(tmem_d, da + adv, db + adv, idesc, accum, tmem_sfa + kb * 4, tmem_sfb + kb * (BN / 32));
-            else
-              ptx::mma_f8<1>(tmem_d, da + adv, db + adv, idesc, accum);
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+              const uint32_t accum = (kt > 0 || kb > 0) ? 1u : 0u;
+              const uint64_t da = ptx::desc_join(a_lo + kb * 2, ptx::kDescHiSw128);
+              const uint64_t db = ptx::desc_join(b_lo + kb * 2, ptx::kDescHiSw128);
+              if constexpr (NVF4)
+                ptx::mma_nvf4<1>(tmem_d, da, db, idesc, accum, tmem_sfa + kb * 4, tmem_sfb + kb * (BN / 32));
+              else
+                ptx::mma_f8<1>(tmem_d, da, db, idesc, accum);
+            }
+          } else {
+            // last, partial K tile of an NVFP4 problem whose K is not a multiple of 256
+            const uint32_t sfa_lo = (b_lo & 0x3fffu) + (C::kBBytes >> 4);
+            const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
+            for (int kb = 0; kb < kblocks; ++kb) {
+              ptx::tmem_cp_sf<1>(tmem_sfa + kb * 4, ptx::desc_join(sfa_lo + kb * 32, ptx::kDescHiSf));
+              for (int j = 0; j < BN / 128; ++j)
+                ptx::tmem_cp_sf<1>(tmem_sfb + kb * (BN / 32) + j * 4, ptx::desc_join(sfb_lo + j * 128 + kb * 32, ptx::kDescHiSf));
+            }
+            for (int kb = 0; kb < kblocks; ++kb) {
+              const uint32_t accum = (kt > 0 || kb > 0) ? 1u : 0u;
+              const uint64_t da = ptx::desc_join(a_lo + kb * 2, ptx::kDescHiSw128);
+              const uint64_t db = ptx::desc_join(b_lo + kb * 2, ptx::kDescHiSw128);
+              ptx::mma_nvf4<1>(tmem_d, da, db, idesc, accum, tmem_sfa + kb * 4, tmem_sfb + kb * (BN / 32));
+            }
           }
           ptx::tc_commit<1>(empty_bar + stage);  // stage reusable once these MMAs (and copies) retire
           if (++stage == C::kStages) stage = 0, phase ^= 1u;

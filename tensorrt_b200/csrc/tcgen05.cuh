@@ -135,6 +135,18 @@ __device__ __forceinline__ uint64_t smem_desc_sf(uint32_t saddr) {
   return d;
 }
 
+// The same descriptors split into 32-bit halves: the upper half is a constant, the lower
+// half is (address >> 4) plus flags, so stepping through a tile is one 32-bit add.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);
+__device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t saddr) { return ((saddr >> 4) & 0x3fffu) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_sf(uint32_t saddr) { return (saddr >> 4) & 0x3fffu; }
+__device__ __forceinline__ uint64_t desc_join(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 // Instruction descriptors (upper 32 bits of the tcgen05.mma "idesc" operand).
 // kind::f8f6f4, A = B = E4M3, fp32 accumulate, both operands K-major.
 __host__ __device__ constexpr uint32_t idesc_f8(int m, int n) {
