@@ -155,6 +155,25 @@ int b200q_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_scales, const floa
                      const void* bias, void* out, int64_t M, int64_t N, int64_t K,
                      b200q_stream_t stream);
 
+/* ------------------------------------------------------------------ glue of the decoder linear stack
+ * The benchmark workloads wrap the quantized linears in a Llama-shaped decoder layer
+ * (RMSNorm -> QKV -> attention replaced by identity on V -> O -> residual -> RMSNorm ->
+ * gate/up -> silu(gate)*up -> down -> residual).  The reference lowers these to TensorRT
+ * elementwise layers (RMSNorm: lowering/passes/replace_fused_rms_norm.py:12-92); here they are
+ * plain streaming kernels over bf16 so that the stack runs without any library kernel.
+ *   b200q_rms_norm      out = x * rsqrt(mean(x^2) + eps) * weight, per row; cols % 8 == 0
+ *   b200q_silu_mul      out[t, j] = silu(gu[t, j]) * gu[t, f + j], gu is [rows, 2f]; f % 8 == 0
+ *   b200q_add           out = a + b over n elements (n % 8 == 0)
+ *   b200q_expand_heads  out[t, h*hd + d] = src[t*src_stride + src_col0 + (h / rep)*hd + d]
+ *                       (every kv head repeated `rep` times: grouped-query V -> query width)
+ */
+int b200q_rms_norm(const void* x, const void* weight, void* out, int64_t rows, int64_t cols, float eps,
+                   b200q_stream_t stream);
+int b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t f, b200q_stream_t stream);
+int b200q_add(const void* a, const void* b, void* out, int64_t n, b200q_stream_t stream);
+int b200q_expand_heads(const void* src, int64_t src_stride, int64_t src_col0, void* out, int64_t rows,
+                       int heads_out, int rep, int head_dim, b200q_stream_t stream);
+
 /* Tile width of the GEMM kernels: 0 = chosen per problem (default), 128 or 256 = forced.
  * Process-wide tuning knob; results do not depend on it beyond fp32 summation order. */
 int b200q_gemm_set_tile_n(int bn);

@@ -34,6 +34,10 @@ SIGNATURES = {
     "b200q_nvfp4_dequantize": (_c.c_int, [_p, _p, _p, _i64, _i64, _p, _c.c_int, _p]),
     "b200q_fp8_gemm": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _p]),
     "b200q_nvfp4_gemm": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
+    "b200q_rms_norm": (_c.c_int, [_p, _p, _p, _i64, _i64, _c.c_float, _p]),
+    "b200q_silu_mul": (_c.c_int, [_p, _p, _i64, _i64, _p]),
+    "b200q_add": (_c.c_int, [_p, _p, _p, _i64, _p]),
+    "b200q_expand_heads": (_c.c_int, [_p, _i64, _i64, _p, _i64, _c.c_int, _c.c_int, _c.c_int, _p]),
     "b200q_gemm_set_tile_n": (_c.c_int, [_c.c_int]),
     "b200q_device_status": (_c.c_int, [_c.c_int]),
 }

@@ -199,6 +199,58 @@ def nvfp4_gemm(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias=No
     return out
 
 
+def _bf16(*ts):
+    for t in ts:
+        if t.dtype != torch.bfloat16:
+            raise ValueError(f"expected bfloat16, got {t.dtype}")
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    _need_cuda(x, weight)
+    _bf16(x, weight)
+    x = x.contiguous()
+    rows, cols = _rows_cols(x)
+    out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        check(load().b200q_rms_norm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, eps, _stream(x)), "b200q_rms_norm")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """[.., 2F] (gate columns first) -> [.., F] = silu(gate) * up."""
+    _need_cuda(gate_up)
+    _bf16(gate_up)
+    gate_up = gate_up.contiguous()
+    rows, two_f = _rows_cols(gate_up)
+    out = torch.empty(*gate_up.shape[:-1], two_f // 2, dtype=torch.bfloat16, device=gate_up.device)
+    with torch.cuda.device(gate_up.device):
+        check(load().b200q_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, two_f // 2, _stream(gate_up)), "b200q_silu_mul")
+    return out
+
+
+def add(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _need_cuda(a, b)
+    _bf16(a, b)
+    a, b = a.contiguous(), b.contiguous()
+    out = torch.empty_like(a) if out is None else out
+    with torch.cuda.device(a.device):
+        check(load().b200q_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), _stream(a)), "b200q_add")
+    return out
+
+
+def expand_heads(src: torch.Tensor, col0: int, heads_out: int, rep: int, head_dim: int) -> torch.Tensor:
+    """src [.., W] bf16 -> [.., heads_out*head_dim]: head h is src[.., col0 + (h // rep)*head_dim : +head_dim]."""
+    _need_cuda(src)
+    _bf16(src)
+    src = src.contiguous()
+    rows, width = _rows_cols(src)
+    out = torch.empty(*src.shape[:-1], heads_out * head_dim, dtype=torch.bfloat16, device=src.device)
+    with torch.cuda.device(src.device):
+        check(load().b200q_expand_heads(src.data_ptr(), width, col0, out.data_ptr(), rows, heads_out, rep, head_dim, _stream(src)),
+              "b200q_expand_heads")
+    return out
+
+
 def set_gemm_tile_n(bn: int) -> None:
     check(load().b200q_gemm_set_tile_n(bn), "b200q_gemm_set_tile_n")
 

@@ -1,0 +1,193 @@
+// Elementwise / row-wise kernels either side of the quantized linears in the decoder
+// linear stack: RMSNorm, silu(gate) * up, residual add, and the "attention = identity on V"
+// head expansion.  All are HBM-bound streaming kernels over bf16 with 128-bit accesses.
+#include "common.cuh"
+
+namespace b200q {
+namespace {
+
+constexpr int kThreads = 256;
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* smem) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float r = (lane < THREADS / 32) ? smem[lane] : 0.0f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  __syncthreads();
+  return r;
+}
+
+// y = x * rsqrt(mean(x^2) + eps) * w, fp32 math, bf16 in/out; one CTA per row, the row stays
+// in registers (ITEMS groups of 8 per thread) or is re-read (ITEMS == 0).
+template <int ITEMS>
+__global__ void __launch_bounds__(kThreads)
+rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                int64_t cols, float eps) {
+  __shared__ float red[kThreads / 32];
+  const int64_t row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * cols;
+  __nv_bfloat16* yr = y + row * cols;
+  const int groups = static_cast<int>(cols >> 3);
+  float v[ITEMS > 0 ? ITEMS : 1][8];
+  float ss = 0.0f;
+  if constexpr (ITEMS > 0) {
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const int g = threadIdx.x + i * kThreads;
+      if (g < groups) {
+        Elem<__nv_bfloat16>::load8(xr + (int64_t)g * 8, v[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
+      }
+    }
+  } else {
+    for (int g = threadIdx.x; g < groups; g += kThreads) {
+      float t[8];
+      Elem<__nv_bfloat16>::load8(xr + (int64_t)g * 8, t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(t[j], t[j], ss);
+    }
+  }
+  const float total = block_sum<kThreads>(ss, red);
+  const float inv = rsqrtf(total / static_cast<float>(cols) + eps);
+  auto emit = [&](int g, const float* t) {
+    float wv[8], o[8];
+    Elem<__nv_bfloat16>::load8(w + (int64_t)g * 8, wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = t[j] * inv * wv[j];
+    Elem<__nv_bfloat16>::store8(yr + (int64_t)g * 8, o);
+  };
+  if constexpr (ITEMS > 0) {
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const int g = threadIdx.x + i * kThreads;
+      if (g < groups) emit(g, v[i]);
+    }
+  } else {
+    for (int g = threadIdx.x; g < groups; g += kThreads) {
+      float t[8];
+      Elem<__nv_bfloat16>::load8(xr + (int64_t)g * 8, t);
+      emit(g, t);
+    }
+  }
+}
+
+// act[t, j] = silu(gu[t, j]) * gu[t, F + j], gu is [T, 2F] (gate columns first)
+__global__ void __launch_bounds__(kThreads)
+silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int64_t rows, int64_t f) {
+  const int64_t groups_per_row = f >> 3;
+  const int64_t total = rows * groups_per_row;
+  for (int64_t g = blockIdx.x * (int64_t)kThreads + threadIdx.x; g < total; g += (int64_t)gridDim.x * kThreads) {
+    const int64_t row = g / groups_per_row, c = (g - row * groups_per_row) * 8;
+    float a[8], b[8], o[8];
+    Elem<__nv_bfloat16>::load8(gu + row * 2 * f + c, a);
+    Elem<__nv_bfloat16>::load8(gu + row * 2 * f + f + c, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = a[j] / (1.0f + __expf(-a[j])) * b[j];
+    Elem<__nv_bfloat16>::store8(act + row * f + c, o);
+  }
+}
+
+// out = a + b (bf16, fp32 add)
+__global__ void __launch_bounds__(kThreads)
+add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ out, int64_t n) {
+  const int64_t groups = n >> 3;
+  for (int64_t g = blockIdx.x * (int64_t)kThreads + threadIdx.x; g < groups; g += (int64_t)gridDim.x * kThreads) {
+    float x[8], y[8];
+    Elem<__nv_bfloat16>::load8(a + g * 8, x);
+    Elem<__nv_bfloat16>::load8(b + g * 8, y);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] += y[j];
+    Elem<__nv_bfloat16>::store8(out + g * 8, x);
+  }
+}
+
+// out[t, h * hd + d] = src[t, src_col0 + (h / rep) * hd + d]: every kv head repeated `rep` times
+__global__ void __launch_bounds__(kThreads)
+expand_heads_kernel(const __nv_bfloat16* __restrict__ src, int64_t src_stride, int64_t src_col0, __nv_bfloat16* __restrict__ out,
+                    int64_t rows, int heads_out, int rep, int head_dim) {
+  const int64_t groups_per_head = head_dim >> 3;
+  const int64_t groups_per_row = heads_out * groups_per_head;
+  const int64_t total = rows * groups_per_row;
+  for (int64_t g = blockIdx.x * (int64_t)kThreads + threadIdx.x; g < total; g += (int64_t)gridDim.x * kThreads) {
+    const int64_t row = g / groups_per_row, r = g - row * groups_per_row;
+    const int64_t h = r / groups_per_head, d = (r - h * groups_per_head) * 8;
+    const uint4 v = *reinterpret_cast<const uint4*>(src + row * src_stride + src_col0 + (h / rep) * head_dim + d);
+    *reinterpret_cast<uint4*>(out + row * groups_per_row * 8 + h * head_dim + d) = v;
+  }
+}
+
+int grid_for(int64_t work_items) {
+  int64_t ctas = (work_items + kThreads - 1) / kThreads;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  return static_cast<int>(ctas < 1 ? 1 : (ctas > cap ? cap : ctas));
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int b200q_rms_norm(const void* x, const void* weight, void* out, int64_t rows, int64_t cols, float eps, b200q_stream_t stream) {
+  if (rows < 0 || cols < 0 || cols % 8 != 0 || rows > 0x7fffffffLL) return B200Q_ERR_INVALID;
+  if (rows == 0 || cols == 0) return B200Q_OK;
+  if (x == nullptr || weight == nullptr || out == nullptr) return B200Q_ERR_INVALID;
+  if (!aligned(x, 16) || !aligned(weight, 16) || !aligned(out, 16)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const auto* xp = static_cast<const __nv_bfloat16*>(x);
+  const auto* wp = static_cast<const __nv_bfloat16*>(weight);
+  auto* yp = static_cast<__nv_bfloat16*>(out);
+  const int items = static_cast<int>(((cols >> 3) + kThreads - 1) / kThreads);
+  dim3 grid(static_cast<unsigned>(rows));
+  if (items <= 1) rms_norm_kernel<1><<<grid, kThreads, 0, st>>>(xp, wp, yp, cols, eps);
+  else if (items <= 2) rms_norm_kernel<2><<<grid, kThreads, 0, st>>>(xp, wp, yp, cols, eps);
+  else if (items <= 4) rms_norm_kernel<4><<<grid, kThreads, 0, st>>>(xp, wp, yp, cols, eps);
+  else rms_norm_kernel<0><<<grid, kThreads, 0, st>>>(xp, wp, yp, cols, eps);
+  return check_launch();
+}
+
+int b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t f, b200q_stream_t stream) {
+  if (rows < 0 || f < 0 || f % 8 != 0) return B200Q_ERR_INVALID;
+  if (rows == 0 || f == 0) return B200Q_OK;
+  if (gate_up == nullptr || out == nullptr) return B200Q_ERR_INVALID;
+  if (!aligned(gate_up, 16) || !aligned(out, 16)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  silu_mul_kernel<<<grid_for(rows * (f >> 3)), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, f);
+  return check_launch();
+}
+
+int b200q_add(const void* a, const void* b, void* out, int64_t n, b200q_stream_t stream) {
+  if (n < 0 || n % 8 != 0) return B200Q_ERR_INVALID;
+  if (n == 0) return B200Q_OK;
+  if (a == nullptr || b == nullptr || out == nullptr) return B200Q_ERR_INVALID;
+  if (!aligned(a, 16) || !aligned(b, 16) || !aligned(out, 16)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  add_kernel<<<grid_for(n >> 3), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), static_cast<__nv_bfloat16*>(out), n);
+  return check_launch();
+}
+
+int b200q_expand_heads(const void* src, int64_t src_stride, int64_t src_col0, void* out, int64_t rows, int heads_out, int rep,
+                       int head_dim, b200q_stream_t stream) {
+  if (rows < 0 || heads_out <= 0 || rep <= 0 || head_dim <= 0 || head_dim % 8 != 0 || heads_out % rep != 0 || src_stride % 8 != 0 ||
+      src_col0 % 8 != 0)
+    return B200Q_ERR_INVALID;
+  if (rows == 0) return B200Q_OK;
+  if (src == nullptr || out == nullptr) return B200Q_ERR_INVALID;
+  if (!aligned(src, 16) || !aligned(out, 16)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  expand_heads_kernel<<<grid_for(rows * heads_out * (head_dim >> 3)), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), src_stride, src_col0, static_cast<__nv_bfloat16*>(out), rows, heads_out, rep, head_dim);
+  return check_launch();
+}
+
+}  // extern "C"

@@ -1,0 +1,221 @@
+"""Llama-shaped decoder *linear* stack with quantized linears, optionally tensor-parallel.
+
+One layer:  h -> RMSNorm -> QKV linear -> "attention" (identity on the V slice, every kv head
+repeated n_q/n_kv times up to the query width) -> O linear -> (all-reduce) -> residual ->
+RMSNorm -> gate/up linear -> silu(gate) * up -> down linear -> (all-reduce) -> residual.
+
+Tensor parallelism follows the reference's plan (tools/llm/tensor_parallel_llama_llm.py:134-157;
+manual-slicing twin tools/llm/tensor_parallel_llama_export.py:109-190): q/k/v/gate/up are
+column-parallel (weight rows sliced, no communication), o/down row-parallel (weight columns
+sliced, partial outputs summed by `tensorrt::fused_nccl_all_reduce` semantics).  Each rank
+quantizes the activation slice it owns (per-token amax over the local slice for FP8, a
+tensor amax of the local slice for NVFP4).
+
+The numerical work is done by a `backend` object.  `CudaBackend` (the product) calls the b200q
+kernels through the C ABI; tests drive the same layer logic on CPU/gloo ranks with a backend
+built from the CPU oracle.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import capi
+
+
+@dataclass(frozen=True)
+class StackConfig:
+    hidden: int
+    n_q: int
+    n_kv: int
+    head_dim: int
+    ffn: int
+    layers: int
+    mode: str = "fp8"          # "fp8" (per-token activations x per-channel weights) or "nvfp4" (W4A4)
+    eps: float = 1e-5
+
+    @property
+    def q_width(self):
+        return self.n_q * self.head_dim
+
+    @property
+    def kv_width(self):
+        return self.n_kv * self.head_dim
+
+    def check(self, world: int = 1):
+        if self.mode not in ("fp8", "nvfp4"):
+            raise ValueError(f"mode must be 'fp8' or 'nvfp4', got {self.mode!r}")
+        if self.n_q % self.n_kv:
+            raise ValueError("n_q must be a multiple of n_kv")
+        if self.n_q % world or self.n_kv % world or self.ffn % world:
+            raise ValueError(f"heads ({self.n_q}/{self.n_kv}) and ffn ({self.ffn}) must divide by the TP size {world}")
+
+    def weights_per_layer(self):
+        return self.hidden * (self.q_width + 2 * self.kv_width) + self.hidden * self.q_width + 3 * self.hidden * self.ffn
+
+    def flops_per_token(self):
+        return 2 * self.weights_per_layer() * self.layers
+
+
+LLAMA3_8B = StackConfig(hidden=4096, n_q=32, n_kv=8, head_dim=128, ffn=14336, layers=32, mode="nvfp4")
+LLAMA3_70B = StackConfig(hidden=8192, n_q=64, n_kv=8, head_dim=128, ffn=28672, layers=80, mode="fp8")
+
+
+# ----------------------------------------------------------------------------- sharding
+def shard_layer_weights(layer: dict, cfg: StackConfig, rank: int, world: int) -> dict:
+    """Full-precision layer weights -> this rank's slices.  `wqkv` rows are
+    [q heads | k heads | v heads], `wgu` rows are [gate | up]."""
+    q, kv = cfg.q_width, cfg.kv_width
+    qs, kvs, fs = q // world, kv // world, cfg.ffn // world
+    wq, wk, wv = layer["wqkv"][:q], layer["wqkv"][q:q + kv], layer["wqkv"][q + kv:]
+    gate, up = layer["wgu"][:cfg.ffn], layer["wgu"][cfg.ffn:]
+    return {
+        "norm1": layer["norm1"], "norm2": layer["norm2"],
+        "wqkv": torch.cat([wq[rank * qs:(rank + 1) * qs], wk[rank * kvs:(rank + 1) * kvs], wv[rank * kvs:(rank + 1) * kvs]]).contiguous(),
+        "wo": layer["wo"][:, rank * qs:(rank + 1) * qs].contiguous(),
+        "wgu": torch.cat([gate[rank * fs:(rank + 1) * fs], up[rank * fs:(rank + 1) * fs]]).contiguous(),
+        "wdown": layer["wdown"][:, rank * fs:(rank + 1) * fs].contiguous(),
+    }
+
+
+# ----------------------------------------------------------------------------- backends
+class CudaBackend:
+    """b200q kernels through the C ABI."""
+
+    def __init__(self, mode: str):
+        self.mode = mode
+
+    def prepare_weight(self, w: torch.Tensor):
+        if self.mode == "fp8":
+            return capi.fp8_quantize(w, capi.row_amax(w))
+        return capi.nvfp4_quantize(w, capi.amax(w))
+
+    def linear(self, x: torch.Tensor, qw) -> torch.Tensor:
+        if self.mode == "fp8":
+            xc, xs = capi.fp8_quantize(x, None)
+            return capi.fp8_gemm(xc, xs, qw[0], qw[1], None)
+        xc, xs, xg = capi.nvfp4_quantize(x, capi.amax(x))
+        return capi.nvfp4_gemm(xc, xs, xg, qw[0], qw[1], qw[2], None)
+
+    rms_norm = staticmethod(capi.rms_norm)
+    silu_mul = staticmethod(capi.silu_mul)
+    add = staticmethod(capi.add)
+    expand_heads = staticmethod(capi.expand_heads)
+
+
+# ----------------------------------------------------------------------------- collectives
+class AllReduce:
+    """Row-parallel sum over the TP group; `slabs` > 1 splits the rows so that the collective of
+    one slab overlaps the caller's work on the next (the caller passes a generator of slabs)."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+
+    def __call__(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+
+class OverlappedRowParallel:
+    """Row-parallel linear + all-reduce with the collective of slab i running on a side stream
+    while the GEMM of slab i+1 runs on the compute stream (CUDA only)."""
+
+    def __init__(self, backend, reduce: AllReduce, slabs: int):
+        self.backend, self.reduce, self.slabs = backend, reduce, max(1, slabs)
+        self.comm_stream = torch.cuda.Stream() if torch.cuda.is_available() and reduce.world > 1 else None
+
+    def __call__(self, x: torch.Tensor, qw) -> torch.Tensor:
+        if self.reduce.world == 1:
+            return self.backend.linear(x, qw)
+        rows = x.shape[0]
+        slabs = min(self.slabs, max(1, rows // 128))
+        if slabs == 1 or self.comm_stream is None:
+            return self.reduce(self.backend.linear(x, qw))
+        bounds = [rows * i // slabs for i in range(slabs + 1)]
+        outs = []
+        main = torch.cuda.current_stream()
+        for i in range(slabs):
+            part = self.backend.linear(x[bounds[i]:bounds[i + 1]], qw)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ev)
+                self.reduce(part)
+                part.record_stream(self.comm_stream)
+            outs.append(part)
+        main.wait_stream(self.comm_stream)
+        return torch.cat(outs, dim=0)
+
+
+# ----------------------------------------------------------------------------- the stack
+class DecoderLayer:
+    def __init__(self, cfg: StackConfig, weights: dict, backend, world: int = 1, row_parallel=None):
+        self.cfg, self.backend, self.world = cfg, backend, world
+        self.norm1, self.norm2 = weights["norm1"], weights["norm2"]
+        self.wqkv = backend.prepare_weight(weights["wqkv"])
+        self.wo = backend.prepare_weight(weights["wo"])
+        self.wgu = backend.prepare_weight(weights["wgu"])
+        self.wdown = backend.prepare_weight(weights["wdown"])
+        self.row_parallel = row_parallel or (lambda x, qw: backend.linear(x, qw))
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        """h: [tokens, hidden] bf16."""
+        cfg, be, w = self.cfg, self.backend, self.world
+        x = be.rms_norm(h, self.norm1, cfg.eps)
+        qkv = be.linear(x, self.wqkv)                                   # [T, (q + 2 kv) / W]
+        q_local, kv_local = cfg.q_width // w, cfg.kv_width // w
+        attn = be.expand_heads(qkv, q_local + kv_local, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
+        h = be.add(h, self.row_parallel(attn, self.wo))
+        x = be.rms_norm(h, self.norm2, cfg.eps)
+        act = be.silu_mul(self.gate_up(x))
+        return be.add(h, self.row_parallel(act, self.wdown))
+
+    def gate_up(self, x):
+        return self.backend.linear(x, self.wgu)
+
+
+class DecoderStack:
+    """`layers` decoder layers sharing one TP group.  `weights` is an iterable of per-layer dicts
+    of full (unsharded) bf16 weights; each is sharded, quantized and dropped."""
+
+    def __init__(self, cfg: StackConfig, weights, backend=None, rank: int = 0, world: int = 1, group=None, slabs: int = 1):
+        cfg.check(world)
+        self.cfg, self.rank, self.world = cfg, rank, world
+        self.backend = backend or CudaBackend(cfg.mode)
+        reduce = AllReduce(group) if world > 1 else None
+        row_parallel = None
+        if world > 1:
+            if slabs > 1:
+                row_parallel = OverlappedRowParallel(self.backend, reduce, slabs)
+            else:
+                be = self.backend
+                row_parallel = lambda x, qw: reduce(be.linear(x, qw))  # noqa: E731
+        self.layers = [DecoderLayer(cfg, shard_layer_weights(w, cfg, rank, world) if world > 1 else w, self.backend, world,
+                                    row_parallel) for w in weights]
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        shape = h.shape
+        h = h.reshape(-1, shape[-1])
+        for layer in self.layers:
+            h = layer.forward(h)
+        return h.view(shape)
+
+    __call__ = forward
+
+
+def random_layer_weights(cfg: StackConfig, seed: int, device="cuda", dtype=torch.bfloat16):
+    """Generator of per-layer full weights ~ N(0, 0.02), RMSNorm weights = 1 (same values on
+    every rank for the same seed)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    for _ in range(cfg.layers):
+        def rnd(r, c):
+            return (torch.randn(r, c, device=device, dtype=torch.float32, generator=g) * 0.02).to(dtype)
+        yield {
+            "norm1": torch.ones(cfg.hidden, device=device, dtype=dtype), "norm2": torch.ones(cfg.hidden, device=device, dtype=dtype),
+            "wqkv": rnd(cfg.q_width + 2 * cfg.kv_width, cfg.hidden), "wo": rnd(cfg.hidden, cfg.q_width),
+            "wgu": rnd(2 * cfg.ffn, cfg.hidden), "wdown": rnd(cfg.hidden, cfg.ffn),
+        }

@@ -1,0 +1,102 @@
+"""`bench.py --workload nvfp4_stack | tp_stack`: decoder linear stacks end to end.
+
+nvfp4_stack  NVFP4 W4A4, Llama-3-8B shape (hidden 4096, 32 q / 8 kv heads of 128, FFN 14336,
+             32 layers), prefill of 8 x 2048 tokens, seed 3; one GPU.
+tp_stack     FP8 (per-token activations, per-channel weights), Llama-3-70B shape (hidden 8192,
+             64 q / 8 kv heads, FFN 28672, 80 layers), tensor parallel over --gpus ranks
+             (column-parallel QKV / gate-up, row-parallel O / down + all-reduce), prefill of
+             32 x 1024 tokens plus single-token decode steps of batch 64, seed 4.
+value = prefill tokens/s of the whole job (strong scaling: the token count is fixed as the TP
+size grows); decode tokens/s is reported beside it.
+"""
+from __future__ import annotations
+
+import json
+import time
+
+import torch
+
+
+def _fwd_time(fn, steps, warmup, world, bench):
+    return bench.timed(lambda i: fn(), steps, warmup, world)
+
+
+def run(args):
+    import bench
+    from tensorrt_b200 import capi
+    from tensorrt_b200.stack import LLAMA3_8B, LLAMA3_70B, DecoderStack, random_layer_weights
+
+    rank, world, local = bench.dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    tp = args.workload == "tp_stack"
+    cfg = LLAMA3_70B if tp else LLAMA3_8B
+    if not tp and world > 1:
+        raise SystemExit("nvfp4_stack is a single-GPU workload; use tp_stack for --gpus > 1")
+    seed = 4 if tp else 3
+    group = None
+    t0 = time.time()
+    stack = DecoderStack(cfg, random_layer_weights(cfg, seed, device=dev), rank=rank, world=world, group=group,
+                         slabs=args.slabs if world > 1 else 1)
+    torch.cuda.synchronize()
+    build_s = time.time() - t0
+
+    g = torch.Generator().manual_seed(seed)
+    batch, seq = (32, 1024) if tp else (8, 2048)
+    h_host = torch.randn(batch, seq, cfg.hidden, generator=g).bfloat16().pin_memory()
+    h = h_host.to(dev)
+    tokens = batch * seq
+    steps, warmup = max(1, args.steps), max(1, min(args.warmup, 3))
+
+    with bench.ClockSampler(local) as clocks:
+        ms = _fwd_time(lambda: stack(h), steps, warmup, world, bench)
+    status = capi.device_status()
+    prefill_tps = tokens * steps / (ms * 1e-3)
+
+    def e2e():
+        x = h_host.to(dev, non_blocking=True)
+        y = stack(x)
+        return float(y.float().abs().mean().item())  # device -> host read of a scalar of the result
+
+    e2e_ms = _fwd_time(e2e, max(1, min(steps, 3)), 1, world, bench)
+    e2e_steps = max(1, min(steps, 3))
+
+    decode = None
+    if tp:
+        hd = torch.randn(64, 1, cfg.hidden, generator=g).bfloat16().to(dev)
+        dsteps = 20
+        dms = _fwd_time(lambda: stack(hd), dsteps, 3, world, bench)
+        decode = {"tokens_per_s": 64 * dsteps / (dms * 1e-3), "ms_per_step": dms / dsteps, "batch": 64,
+                  "weight_bytes_per_rank": cfg.weights_per_layer() * cfg.layers // world,
+                  "weight_stream_GBps_per_rank": cfg.weights_per_layer() * cfg.layers / world / (dms / dsteps * 1e-3) / 1e9}
+
+    peaks = bench.measured_peaks()
+    flops = cfg.flops_per_token() * tokens
+    scale = 2.0 if cfg.mode == "fp8" else 4.0
+    tflops = flops / (ms / steps * 1e-3) / 1e12
+    line = {
+        "metric": "tp_decoder_stack_prefill_throughput" if tp else "nvfp4_decoder_stack_prefill_throughput",
+        "value": prefill_tps, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "e4m3" if cfg.mode == "fp8" else "e2m1 (nvfp4)", "data": "synthetic",
+        "config": {"workload": f"{cfg.mode} decoder linear stack hidden {cfg.hidden}, {cfg.n_q}q/{cfg.n_kv}kv x {cfg.head_dim}, "
+                               f"ffn {cfg.ffn}, {cfg.layers} layers; prefill {batch} x {seq} tokens; random-init weights N(0, 0.02); "
+                               "attention core = identity on the V slice (kv heads repeated to the query width)",
+                   "parallelism": f"tp{world}", "slabs": args.slabs if world > 1 else 1,
+                   "l2": "weights + activations per forward far exceed the 126 MB L2"},
+        "clocks": clocks.summary(), "build_seconds": round(build_s, 1), "device_status": status,
+        "e2e": {"value": tokens * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h_host.numel() * 2,
+                "d2h_bytes_per_step": 4, "steps": e2e_steps},
+        "model_tflops": tflops,
+        "roofline": {"bound": "tensor", "achieved": tflops / world, "peak": peaks["bf16_tflops_sustained"] * scale, "unit": "TFLOP/s",
+                     "frac": tflops / world / (peaks["bf16_tflops_sustained"] * scale),
+                     "peak_source": f"{peaks['source']} sustained cuBLAS bf16 x{int(scale)} per GPU; GEMM flops only, per GPU",
+                     "traffic": None},
+    }
+    if decode:
+        line["decode"] = decode
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()

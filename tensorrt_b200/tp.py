@@ -61,3 +61,20 @@ def shard_cols(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
         raise ValueError(f"cannot split {w.shape[1]} input features over {world} ranks")
     c = w.shape[1] // world
     return w[:, rank * c:(rank + 1) * c].contiguous()
+
+
+class ShapeMismatchError(RuntimeError):
+    pass
+
+
+def check_same_shape(t: torch.Tensor, group=None) -> None:
+    """Host-side guard for a collective: every rank contributes (shape, dtype) through an
+    object all-gather and raises the same error on all ranks when they differ, instead of
+    letting mismatched all-reduce calls hang or corrupt memory on the device."""
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    mine = (tuple(t.shape), str(t.dtype))
+    seen = [None] * dist.get_world_size(group)
+    dist.all_gather_object(seen, mine, group=group)
+    if any(s != seen[0] for s in seen):
+        raise ShapeMismatchError(f"all-reduce operands differ across ranks: {seen}")

@@ -1,0 +1,176 @@
+"""Tensor-parallel host logic on CPU: two gloo ranks (spawned processes, FileStore rendezvous on
+127.0.0.1-free file paths) run the stack's layer logic with a backend made of the CPU oracle, the
+`tensorrt::fused_nccl_all_reduce` op is checked against its known answer, and host-side failure
+detection (shape mismatch across ranks, a rank that never joins) is exercised without any GPU."""
+import os
+import sys
+import tempfile
+from datetime import timedelta
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+class OracleBackend:
+    """CPU stand-in for the device kernels, built from the oracle (tests only)."""
+
+    def __init__(self, mode):
+        import oracle as o
+
+        self.o, self.mode = o, mode
+
+    def prepare_weight(self, w):
+        return w
+
+    def linear(self, x, w):
+        o = self.o
+        y = o.fp8_linear_ref(x, w) if self.mode == "fp8" else o.nvfp4_linear_ref(x, w)
+        return y.to(x.dtype)
+
+    def rms_norm(self, x, w, eps):
+        return self.o.rms_norm_ref(x, w, eps)
+
+    def silu_mul(self, gu):
+        f = gu.shape[-1] // 2
+        return (torch.nn.functional.silu(gu[..., :f].float()) * gu[..., f:].float()).to(gu.dtype)
+
+    def add(self, a, b):
+        return a + b
+
+    def expand_heads(self, src, col0, heads_out, rep, head_dim):
+        v = src[..., col0:col0 + (heads_out // rep) * head_dim]
+        return v.reshape(*v.shape[:-1], heads_out // rep, 1, head_dim).expand(
+            *v.shape[:-1], heads_out // rep, rep, head_dim).reshape(*v.shape[:-1], -1).contiguous()
+
+
+def _layer_weights(cfg, seed):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(cfg.layers):
+        rnd = lambda r, c: (torch.randn(r, c, generator=g) * 0.02).bfloat16()  # noqa: E731
+        out.append({"norm1": torch.ones(cfg.hidden).bfloat16(), "norm2": torch.ones(cfg.hidden).bfloat16(),
+                    "wqkv": rnd(cfg.q_width + 2 * cfg.kv_width, cfg.hidden), "wo": rnd(cfg.hidden, cfg.q_width),
+                    "wgu": rnd(2 * cfg.ffn, cfg.hidden), "wdown": rnd(cfg.hidden, cfg.ffn)})
+    return out
+
+
+def _init(rank, world, store_path, timeout_s=60):
+    sys.path.insert(0, ROOT)
+    store = dist.FileStore(store_path, world)
+    dist.init_process_group("gloo", store=store, rank=rank, world_size=world, timeout=timedelta(seconds=timeout_s))
+
+
+def _worker_stack(rank, world, store_path, mode, out_path):
+    _init(rank, world, store_path)
+    import oracle as o
+    import tensorrt_b200  # registers tensorrt::fused_nccl_all_reduce
+    from tensorrt_b200.stack import DecoderStack, StackConfig
+    from tensorrt_b200.tp import group_name_of
+
+    # 1. the op, known answer: sum(fill(rank + 1)) == W (W + 1) / 2
+    t = torch.full((1, 4), float(rank + 1))
+    r = torch.ops.tensorrt.fused_nccl_all_reduce(t, "sum", group_name_of())
+    assert torch.allclose(r, torch.full((1, 4), world * (world + 1) / 2), atol=1e-3, rtol=1e-3)
+    assert torch.equal(t, torch.full((1, 4), float(rank + 1))), "the op must not modify its input"
+    r = torch.ops.tensorrt.fused_nccl_all_reduce(t, "max", group_name_of())
+    assert torch.equal(r, torch.full((1, 4), float(world)))
+
+    # 2. the TP stack against the oracle's TP restatement (same arithmetic -> identical) and
+    #    against the unsharded layer (different summation order / activation slices -> close)
+    cfg = StackConfig(hidden=256, n_q=4, n_kv=2, head_dim=64, ffn=512, layers=2, mode=mode)
+    weights = _layer_weights(cfg, seed=4)
+    g = torch.Generator().manual_seed(40)
+    h = torch.randn(2, 8, cfg.hidden, generator=g).bfloat16()
+    stack = DecoderStack(cfg, weights, backend=OracleBackend(mode), rank=rank, world=world)
+    y = stack(h)
+    ref_tp, ref_1 = h, h
+    for w in weights:
+        ref_tp = o.decoder_layer_ref(ref_tp, w, cfg.n_q, cfg.n_kv, cfg.head_dim, mode, world=world)
+        ref_1 = o.decoder_layer_ref(ref_1, w, cfg.n_q, cfg.n_kv, cfg.head_dim, mode, world=1)
+    assert torch.equal(y, ref_tp), o.rel_l2(y.float(), ref_tp.float())
+    assert o.rel_l2(y.float(), ref_1.float()) < (3e-2 if mode == "fp8" else 1e-1)
+    if rank == 0:
+        torch.save(y, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _worker_mismatch(rank, world, store_path):
+    _init(rank, world, store_path)
+    from tensorrt_b200.tp import ShapeMismatchError, check_same_shape
+
+    check_same_shape(torch.zeros(4, 8))                      # same everywhere: passes
+    bad = torch.zeros(4, 8 if rank == 0 else 16)
+    try:
+        check_same_shape(bad)
+    except ShapeMismatchError as e:
+        assert "differ across ranks" in str(e)
+    else:
+        raise AssertionError("mismatch not detected")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _worker_missing_peer(rank, world, store_path):
+    # rank 1 never joins: rank 0's rendezvous must end with an error within its timeout
+    if rank == 1:
+        return
+    try:
+        _init(rank, world, store_path, timeout_s=3)
+        dist.barrier()
+    except Exception as e:  # DistStoreError / RuntimeError depending on where it times out
+        assert "imeout" in str(e) or "timed out" in str(e).lower() or "store" in str(e).lower(), str(e)
+    else:
+        raise AssertionError("rendezvous with a missing peer did not fail")
+
+
+def _spawn(fn, world, *args):
+    with tempfile.TemporaryDirectory() as d:
+        store = os.path.join(d, "store")
+        mp.spawn(fn, args=(world, store, *args), nprocs=world, join=True)
+
+
+@pytest.mark.parametrize("mode", ["fp8", "nvfp4"])
+def test_two_rank_stack_and_all_reduce_op(mode, tmp_path):
+    out = str(tmp_path / "y.pt")
+    _spawn(_worker_stack, 2, mode, out)
+    assert torch.load(out).shape == (2, 8, 256)
+
+
+def test_shape_mismatch_is_detected_on_the_host():
+    _spawn(_worker_mismatch, 2)
+
+
+def test_missing_peer_times_out_on_the_host():
+    _spawn(_worker_missing_peer, 2)
+
+
+def test_single_process_all_reduce_is_identity(b200):
+    t = torch.arange(8.0)
+    r = torch.ops.tensorrt.fused_nccl_all_reduce(t, "sum", "default")
+    assert torch.equal(r, t) and r.data_ptr() != t.data_ptr()
+    with pytest.raises(ValueError):
+        torch.ops.tensorrt.fused_nccl_all_reduce(t, "xor", "default")
+
+
+def test_sharding_helpers():
+    from tensorrt_b200.stack import StackConfig, shard_layer_weights
+    from tensorrt_b200.tp import shard_cols, shard_rows
+
+    w = torch.arange(8 * 6.0).view(8, 6)
+    assert torch.equal(torch.cat([shard_rows(w, r, 4) for r in range(4)]), w)
+    assert torch.equal(torch.cat([shard_cols(w, r, 3) for r in range(3)], dim=1), w)
+    with pytest.raises(ValueError):
+        shard_rows(w, 0, 3)
+    cfg = StackConfig(hidden=256, n_q=4, n_kv=2, head_dim=64, ffn=512, layers=1)
+    lw = _layer_weights(cfg, 1)[0]
+    parts = [shard_layer_weights(lw, cfg, r, 2) for r in range(2)]
+    assert parts[0]["wqkv"].shape == (256, 256) and parts[0]["wo"].shape == (256, 128)
+    assert parts[0]["wgu"].shape == (512, 256) and parts[0]["wdown"].shape == (256, 256)
+    assert torch.equal(torch.cat([p["wo"] for p in parts], dim=1), lw["wo"])
+    with pytest.raises(ValueError):
+        cfg.check(world=4)          # 2 kv heads do not split over 4 ranks
