@@ -34,6 +34,20 @@ inline int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, in
   return r == CUDA_SUCCESS ? B200Q_OK : B200Q_ERR_CUDA;
 }
 
+// bf16 output [M, N] -> boxes of 32 rows x 64 columns (128 bytes), 128-byte swizzle.
+inline int make_output_map(CUtensorMap* map, const void* base, int64_t M, int64_t N) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) return B200Q_ERR_CUDA;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * 2};
+  const cuuint32_t box[2] = {64, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200Q_OK : B200Q_ERR_CUDA;
+}
+
 template <bool NVF4, int BN>
 int launch_tile(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st) {
   using C = Cfg<NVF4, BN>;
@@ -45,12 +59,18 @@ int launch_tile(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st) {
       return B200Q_ERR_CUDA;
     configured[dev] = true;
   }
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tout;
   if (int rc = make_operand_map(&ta, a, p.M, p.k_bytes, kBM)) return rc;
   if (int rc = make_operand_map(&tb, b, p.N, p.k_bytes, BN)) return rc;
+  p.tma_store = (p.N % 8 == 0) ? 1 : 0;
+  if (p.tma_store) {
+    if (int rc = make_output_map(&tout, p.out, p.M, p.N)) return rc;
+  } else {
+    tout = ta;  // unused by the kernel
+  }
   const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_kernel<NVF4, BN><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, p);
+  gemm_kernel<NVF4, BN><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, tout, p);
   return check_launch();
 }
 

@@ -41,11 +41,19 @@ struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kAccStages = (NVF4 && BN == 256) ? 1 : 2;
   static constexpr int kSfCols = NVF4 ? (16 + 4 * (BN / 32)) : 0;  // tensor-memory columns holding one K tile of scales
-  static constexpr int kTailBytes = 2048;                           // barriers, tmem pointer, epilogue vectors
+  static constexpr int kTailBytes = 2048;                           // barriers, tmem pointer
   static constexpr int kEpiBytes = 2 * 2 * BN * 4;                  // 2 buffers x (col scale, bias) x BN floats
-  static constexpr int kStagesRaw = (kSmemLimit - 1024 - kTailBytes - kEpiBytes) / kStageBytes;
+  // Output staging for the TMA store: per epilogue warp kEpiBufs panels of 32 rows x 64 bf16
+  // (4 KiB, 128-byte swizzled).  Two panels per warp unless that costs a pipeline stage.
+  static constexpr int kPanelBytes = 32 * 128;
+  static constexpr int kFixed = 1024 + kTailBytes + kEpiBytes;
+  static constexpr int kStages2 = (kSmemLimit - kFixed - 4 * 2 * kPanelBytes) / kStageBytes;
+  static constexpr int kStages1 = (kSmemLimit - kFixed - 4 * 1 * kPanelBytes) / kStageBytes;
+  static constexpr int kEpiBufs = (kStages2 >= 4 || kStages2 == kStages1) ? 2 : 1;
+  static constexpr int kStoreBytes = 4 * kEpiBufs * kPanelBytes;
+  static constexpr int kStagesRaw = kEpiBufs == 2 ? kStages2 : kStages1;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpiBytes + kTailBytes;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kStoreBytes + kEpiBytes + kTailBytes;
   // Each shared-memory stage owns its own scale-factor columns in tensor memory, so the
   // tcgen05.cp of K tile i+1 never has to wait for the MMAs of K tile i to finish reading.
   static constexpr int kColsNeeded = kAccStages * BN + kStages * kSfCols;
@@ -66,6 +74,7 @@ struct Params {
   int M, N;
   int k_bytes;             // bytes per operand row (K for FP8, K/2 for NVFP4)
   int sf_col_tiles;        // NVFP4: number of 4-scale column tiles per row tile (ceil(K/64))
+  int tma_store;           // 1: output leaves through TMA stores (needs N % 8 == 0), 0: direct stores
   int* status;             // device status word (0 = ok)
 };
 
@@ -73,12 +82,14 @@ __device__ __forceinline__ void raise_timeout(int* status, int where) { atomicCA
 
 template <bool NVF4, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const __grid_constant__ CUtensorMap tmap_out, const Params p) {
   using C = Cfg<NVF4, BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* tail = smem + C::kStages * C::kStageBytes + C::kEpiBytes;
-  float* epi = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);
+  uint8_t* store_stage = smem + C::kStages * C::kStageBytes;  // 1024-byte aligned panels
+  float* epi = reinterpret_cast<float*>(store_stage + C::kStoreBytes);
+  uint8_t* tail = store_stage + C::kStoreBytes + C::kEpiBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);
   uint64_t* empty_bar = full_bar + C::kStages;
   uint64_t* acc_full = empty_bar + C::kStages;
@@ -113,6 +124,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     ptx::fence_barrier_init();
     ptx::prefetch_tmap(&tmap_a);
     ptx::prefetch_tmap(&tmap_b);
+    if (p.tma_store) ptx::prefetch_tmap(&tmap_out);
   }
   if (warp == 1) {
     ptx::tmem_alloc<1>(tmem_holder, C::kTmemCols);
@@ -276,6 +288,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     int acc = 0;
     uint32_t acc_phase = 0;
     int buf = 0;
+    int sbuf = 0;
     bool dead = false;
     float gscale = 1.0f;
     if constexpr (NVF4) gscale = __fmul_rn(__ldg(p.a_scales), __ldg(p.b_scales));
@@ -308,7 +321,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         continue;
       }
       ptx::tc_fence_after();
-      const int row = mb * kBM + q * 32 + lane;
+      const int row0 = mb * kBM + q * 32;
+      const int row = row0 + lane;
       float rscale = gscale;
       if constexpr (!NVF4) rscale = (row < p.M) ? __ldg(p.a_scales + static_cast<int64_t>(row) * p.a_scale_stride) : 0.0f;
       __nv_bfloat16* orow = p.out + static_cast<int64_t>(row) * p.N + n0;
@@ -318,27 +332,58 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         uint32_t r[32];
         ptx::tmem_ld_32x32(taddr + c * 32, r);
         ptx::tmem_ld_wait();
-        if (row < p.M) {
+        if (c == BN / 32 - 1) {
+          // the accumulator is in registers now: hand the tensor-memory buffer back before
+          // the stores of this last chunk
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(acc_empty + acc);
+        }
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int i0 = c * 32 + 2 * j;
+          const float x0 = fmaf(__uint_as_float(r[2 * j]) * rscale, colscale[i0], colbias[i0]);
+          const float x1 = fmaf(__uint_as_float(r[2 * j + 1]) * rscale, colscale[i0 + 1], colbias[i0 + 1]);
+          __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+          w[j] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        if (p.tma_store) {
+          // two 32-column chunks fill one 64-column panel (32 rows x 128 bytes, 128-byte swizzle:
+          // the 16-byte piece j of row r lands at piece j ^ (r & 7)), then one lane stores it
+          const int half = c & 1;
+          uint8_t* panel = store_stage + (q * C::kEpiBufs + sbuf) * C::kPanelBytes;
+          if (half == 0) {
+            if (lane == 0) ptx::bulk_wait_group_read<C::kEpiBufs - 1>();
+            __syncwarp();
+          }
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int piece = (half * 4 + v) ^ (lane & 7);
+            *reinterpret_cast<uint4*>(panel + lane * 128 + piece * 16) = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+          }
+          if (half == 1) {
+            ptx::fence_proxy_async();
+            __syncwarp();
+            const int col0 = n0 + (c >> 1) * 64;
+            if (lane == 0 && row0 < p.M && col0 < p.N) {
+              ptx::tma_store_2d(&tmap_out, panel, col0, row0);
+              ptx::bulk_commit_group();
+            }
+            if (++sbuf == C::kEpiBufs) sbuf = 0;
+          }
+        } else if (row < p.M) {
           const int cbase = n0 + c * 32;
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            uint32_t w[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int i0 = c * 32 + v * 8 + 2 * j;
-              const float x0 = fmaf(__uint_as_float(r[v * 8 + 2 * j]) * rscale, colscale[i0], colbias[i0]);
-              const float x1 = fmaf(__uint_as_float(r[v * 8 + 2 * j + 1]) * rscale, colscale[i0 + 1], colbias[i0 + 1]);
-              __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-              w[j] = *reinterpret_cast<uint32_t*>(&h);
-            }
             const int col = cbase + v * 8;
             if (vec_ok && col + 8 <= p.N) {
-              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
             } else {
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 if (col + j < p.N) {
-                  const uint32_t word = w[j >> 1];
+                  const uint32_t word = w[4 * v + (j >> 1)];
                   const uint16_t hbits = (j & 1) ? static_cast<uint16_t>(word >> 16) : static_cast<uint16_t>(word & 0xffffu);
                   reinterpret_cast<uint16_t*>(orow)[c * 32 + v * 8 + j] = hbits;
                 }
@@ -347,11 +392,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
         }
       }
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(acc_empty + acc);
       if (++acc == C::kAccStages) acc = 0, acc_phase ^= 1u;
     }
+    // shared memory must stay valid until the last store has read it
+    if (lane == 0) ptx::bulk_wait_group_read<0>();
   }
 
   ptx::tc_fence_before();
