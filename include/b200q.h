@@ -174,7 +174,8 @@ int b200q_add(const void* a, const void* b, void* out, int64_t n, b200q_stream_t
 int b200q_expand_heads(const void* src, int64_t src_stride, int64_t src_col0, void* out, int64_t rows,
                        int heads_out, int rep, int head_dim, b200q_stream_t stream);
 
-/* Tile width of the GEMM kernels: 0 = chosen per problem (default), 128 or 256 = forced.
+/* Tile width of the GEMM kernels: 0 = chosen per problem (default), 128 or 256 = forced
+ * single-CTA tiles of 128 x bn, 512 = forced CTA-pair kernel (256 x 256 tiles, cta_group::2).
  * Process-wide tuning knob; results do not depend on it beyond fp32 summation order. */
 int b200q_gemm_set_tile_n(int bn);
 

@@ -49,7 +49,7 @@ using namespace b200q;
 extern "C" {
 
 int b200q_gemm_set_tile_n(int bn) {
-  if (bn != 0 && bn != 128 && bn != 256) return B200Q_ERR_INVALID;
+  if (bn != 0 && bn != 128 && bn != 256 && bn != 512) return B200Q_ERR_INVALID;
   gemm::g_force_bn.store(bn);
   return B200Q_OK;
 }

@@ -3,7 +3,7 @@
 
 #include <cuda.h>
 
-#include "gemm_kernel.cuh"
+#include "gemm_kernel_2cta.cuh"
 
 namespace b200q {
 namespace gemm {
@@ -74,13 +74,80 @@ int launch_tile(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st) {
   return check_launch();
 }
 
+// Swizzled block-scale buffer as a 3-D tensor [128 u32 = one 512-byte tile, column tile, row tile].
+inline int make_scale_map(CUtensorMap* map, const void* base, int64_t row_tiles, int64_t col_tiles, int box_row_tiles) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) return B200Q_ERR_CUDA;
+  const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(col_tiles), static_cast<cuuint64_t>(row_tiles)};
+  const cuuint64_t strides[2] = {512, static_cast<cuuint64_t>(col_tiles) * 512};
+  const cuuint32_t box[3] = {128, 4, static_cast<cuuint32_t>(box_row_tiles)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200Q_OK : B200Q_ERR_CUDA;
+}
+
+// CTA-pair kernel: clusters of two CTAs, one cluster per 256 x 256 output tile.
+template <bool NVF4>
+int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st) {
+  using C = Cfg2<NVF4>;
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200Q_ERR_CUDA;
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(gemm_pair_kernel<NVF4>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+      return B200Q_ERR_CUDA;
+    configured[dev] = true;
+  }
+  CUtensorMap ta, tb, tout, tsfa, tsfb;
+  if (int rc = make_operand_map(&ta, a, p.M, p.k_bytes, 128)) return rc;
+  if (int rc = make_operand_map(&tb, b, p.N, p.k_bytes, kPairN / 2)) return rc;
+  p.tma_store = (p.N % 8 == 0) ? 1 : 0;
+  if (p.tma_store) {
+    if (int rc = make_output_map(&tout, p.out, p.M, p.N)) return rc;
+  } else {
+    tout = ta;
+  }
+  if constexpr (NVF4) {
+    if (int rc = make_scale_map(&tsfa, p.sfa, (p.M + 127) / 128, p.sf_col_tiles, 1)) return rc;
+    if (int rc = make_scale_map(&tsfb, p.sfb, (p.N + 127) / 128, p.sf_col_tiles, 2)) return rc;
+  } else {
+    tsfa = ta;
+    tsfb = ta;
+  }
+  const int tiles = ((p.M + kPairM - 1) / kPairM) * ((p.N + kPairN - 1) / kPairN);
+  const int max_pairs = sm_count() / 2;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(pairs * 2));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemm_pair_kernel<NVF4>, ta, tb, tout, tsfa, tsfb, p) != cudaSuccess) {
+    cudaGetLastError();
+    return B200Q_ERR_CUDA;
+  }
+  return B200Q_OK;
+}
+
 // Tile width: 256 when that still gives every SM a tile, else 128.  `force_bn` (128 / 256)
-// overrides the choice (used by tests to cover both instantiations).
+// overrides the choice (used by tests to cover both instantiations); 512 forces the CTA-pair
+// kernel (256 x 256 tiles), which is otherwise used when there are at least sm_count/2 such tiles.
 template <bool NVF4>
 int launch(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, int force_bn) {
   p.status = device_status_word();
   if (p.status == nullptr) return B200Q_ERR_CUDA;
   int bn = force_bn;
+  const int64_t pair_tiles = static_cast<int64_t>((p.M + kPairM - 1) / kPairM) * ((p.N + kPairN - 1) / kPairN);
+  if (bn == 512 || (bn == 0 && pair_tiles >= sm_count() / 2)) return launch_pair<NVF4>(a, b, p, st);
   if (bn != 128 && bn != 256) {
     const int64_t tiles256 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 255) / 256);
     bn = (tiles256 >= sm_count()) ? 256 : 128;

@@ -92,12 +92,17 @@ class CudaBackend:
             return capi.fp8_quantize(w, capi.row_amax(w))
         return capi.nvfp4_quantize(w, capi.amax(w))
 
-    def linear(self, x: torch.Tensor, qw) -> torch.Tensor:
+    def linear(self, x: torch.Tensor, qw, amax: torch.Tensor | None = None) -> torch.Tensor:
+        """`amax`: calibrated (static) activation amax for NVFP4; None = measured on this input.
+        FP8 activations are always scaled per token inside the quantize kernel."""
         if self.mode == "fp8":
             xc, xs = capi.fp8_quantize(x, None)
             return capi.fp8_gemm(xc, xs, qw[0], qw[1], None)
-        xc, xs, xg = capi.nvfp4_quantize(x, capi.amax(x))
+        xc, xs, xg = capi.nvfp4_quantize(x, capi.amax(x) if amax is None else amax)
         return capi.nvfp4_gemm(xc, xs, xg, qw[0], qw[1], qw[2], None)
+
+    def measure_amax(self, x: torch.Tensor):
+        return capi.amax(x) if self.mode == "nvfp4" else None
 
     rms_norm = staticmethod(capi.rms_norm)
     silu_mul = staticmethod(capi.silu_mul)
@@ -128,18 +133,18 @@ class OverlappedRowParallel:
         self.backend, self.reduce, self.slabs = backend, reduce, max(1, slabs)
         self.comm_stream = torch.cuda.Stream() if torch.cuda.is_available() and reduce.world > 1 else None
 
-    def __call__(self, x: torch.Tensor, qw) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, qw, amax=None) -> torch.Tensor:
         if self.reduce.world == 1:
-            return self.backend.linear(x, qw)
+            return self.backend.linear(x, qw, amax)
         rows = x.shape[0]
         slabs = min(self.slabs, max(1, rows // 128))
         if slabs == 1 or self.comm_stream is None:
-            return self.reduce(self.backend.linear(x, qw))
+            return self.reduce(self.backend.linear(x, qw, amax))
         bounds = [rows * i // slabs for i in range(slabs + 1)]
         outs = []
         main = torch.cuda.current_stream()
         for i in range(slabs):
-            part = self.backend.linear(x[bounds[i]:bounds[i + 1]], qw)
+            part = self.backend.linear(x[bounds[i]:bounds[i + 1]], qw, amax)
             ev = torch.cuda.Event()
             ev.record(main)
             with torch.cuda.stream(self.comm_stream):
@@ -160,22 +165,30 @@ class DecoderLayer:
         self.wo = backend.prepare_weight(weights["wo"])
         self.wgu = backend.prepare_weight(weights["wgu"])
         self.wdown = backend.prepare_weight(weights["wdown"])
-        self.row_parallel = row_parallel or (lambda x, qw: backend.linear(x, qw))
+        self.row_parallel = row_parallel or (lambda x, qw, amax=None: backend.linear(x, qw, amax))
+        # Calibrated activation amax per linear input (the `amax` operand of the quantize op is a
+        # constant after calibration in the reference flow); filled by a calibration pass.
+        self.amax: dict = {}
+        self.calibrating = False
+
+    def _amax(self, name: str, x: torch.Tensor):
+        if self.calibrating and hasattr(self.backend, "measure_amax"):
+            m = self.backend.measure_amax(x)
+            if m is not None:
+                self.amax[name] = m if name not in self.amax else torch.maximum(self.amax[name], m)
+        return self.amax.get(name)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         """h: [tokens, hidden] bf16."""
         cfg, be, w = self.cfg, self.backend, self.world
         x = be.rms_norm(h, self.norm1, cfg.eps)
-        qkv = be.linear(x, self.wqkv)                                   # [T, (q + 2 kv) / W]
+        qkv = be.linear(x, self.wqkv, self._amax("qkv", x))             # [T, (q + 2 kv) / W]
         q_local, kv_local = cfg.q_width // w, cfg.kv_width // w
         attn = be.expand_heads(qkv, q_local + kv_local, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
-        h = be.add(h, self.row_parallel(attn, self.wo))
+        h = be.add(h, self.row_parallel(attn, self.wo, self._amax("o", attn)))
         x = be.rms_norm(h, self.norm2, cfg.eps)
-        act = be.silu_mul(self.gate_up(x))
-        return be.add(h, self.row_parallel(act, self.wdown))
-
-    def gate_up(self, x):
-        return self.backend.linear(x, self.wgu)
+        act = be.silu_mul(be.linear(x, self.wgu, self._amax("gate_up", x)))
+        return be.add(h, self.row_parallel(act, self.wdown, self._amax("down", act)))
 
 
 class DecoderStack:
@@ -193,7 +206,7 @@ class DecoderStack:
                 row_parallel = OverlappedRowParallel(self.backend, reduce, slabs)
             else:
                 be = self.backend
-                row_parallel = lambda x, qw: reduce(be.linear(x, qw))  # noqa: E731
+                row_parallel = lambda x, qw, amax=None: reduce(be.linear(x, qw, amax))  # noqa: E731
         self.layers = [DecoderLayer(cfg, shard_layer_weights(w, cfg, rank, world) if world > 1 else w, self.backend, world,
                                     row_parallel) for w in weights]
 
@@ -205,6 +218,17 @@ class DecoderStack:
         return h.view(shape)
 
     __call__ = forward
+
+    def calibrate(self, h: torch.Tensor) -> torch.Tensor:
+        """One forward that records the activation amax in front of every linear; later forwards
+        use the recorded values as static quantizer inputs (NVFP4 only; FP8 is per-token dynamic)."""
+        for layer in self.layers:
+            layer.calibrating = True
+        try:
+            return self.forward(h)
+        finally:
+            for layer in self.layers:
+                layer.calibrating = False
 
 
 def random_layer_weights(cfg: StackConfig, seed: int, device="cuda", dtype=torch.bfloat16):

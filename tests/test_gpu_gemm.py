@@ -66,7 +66,7 @@ FP8_SHAPES = [(128, 128, 128), (128, 256, 512), (1, 4096, 4096), (16, 4096, 4096
               (200, 384, 1040), (77, 520, 144), (256, 264, 4096), (2048, 4096, 4096), (300, 4096, 14336)]
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, 512])
 @pytest.mark.parametrize("M,N,K", FP8_SHAPES)
 def test_fp8_gemm(capi, M, N, K, bn):
     x, w, b = _inputs(M, N, K, seed=2 + M + N + K)
@@ -104,7 +104,7 @@ NVFP4_SHAPES = [(128, 128, 256), (128, 256, 512), (16, 4096, 4096), (200, 384, 1
                 (256, 6144, 4096), (2048, 4096, 4096), (130, 4096, 14336)]
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 256, 512])
 @pytest.mark.parametrize("M,N,K", NVFP4_SHAPES)
 def test_nvfp4_gemm(capi, M, N, K, bn):
     x, w, b = _inputs(M, N, K, seed=3 + M + N + K)

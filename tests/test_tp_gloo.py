@@ -26,7 +26,7 @@ class OracleBackend:
     def prepare_weight(self, w):
         return w
 
-    def linear(self, x, w):
+    def linear(self, x, w, amax=None):
         o = self.o
         y = o.fp8_linear_ref(x, w) if self.mode == "fp8" else o.nvfp4_linear_ref(x, w)
         return y.to(x.dtype)
