@@ -15,6 +15,13 @@
 //   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp its own 32-lane quarter),
 //               scale, add bias, convert, store; overlaps the next tile's main loop when
 //               the accumulator is double-buffered in tensor memory
+// NVFP4 scale path, what was measured (8192^3, one B200): skipping the tcgen05.cp copies takes
+// the kernel from 336 us to 250 us, so they cost about a quarter of the run; moving the scales
+// with tcgen05.st from four extra warps (with the scale tiles in a ring of their own running
+// ahead of the operands) was slower still (2.8 vs 3.4 PFLOP/s on the same GPU), as was issuing
+// the copies of K tile i+1 before the MMAs of K tile i.  The loads alone (no MMA, no copies,
+// no epilogue) take 158 us at 128 x 256 tiles: the L2 -> SM path delivers ~20 TB/s.
+//
 // No TMA multicast is used anywhere.  Every mbarrier wait is bounded; a wait that gives up
 // raises a flag in global memory, the CTA drains and leaves, and the host reports
 // B200Q_ERR_TIMEOUT from b200q_device_status().
@@ -79,6 +86,97 @@ struct Params {
 };
 
 __device__ __forceinline__ void raise_timeout(int* status, int where) { atomicCAS(status, 0, where); }
+
+// 32 columns of one accumulator row: scale, bias, convert to 16 packed bf16 pairs.
+__device__ __forceinline__ void epilogue_convert(const uint32_t* r, float rscale, const float* colscale, const float* colbias,
+                                                 uint32_t* w) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float x0 = fmaf(__uint_as_float(r[2 * j]) * rscale, colscale[2 * j], colbias[2 * j]);
+    const float x1 = fmaf(__uint_as_float(r[2 * j + 1]) * rscale, colscale[2 * j + 1], colbias[2 * j + 1]);
+    __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+    w[j] = *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+// Direct (non-TMA) store of 32 converted columns of one row, with a scalar tail for ragged N.
+__device__ __forceinline__ void epilogue_store_direct(__nv_bfloat16* orow_chunk, const uint32_t* w, int col0, int N, bool vec_ok) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const int col = col0 + v * 8;
+    if (vec_ok && col + 8 <= N) {
+      *reinterpret_cast<uint4*>(orow_chunk + v * 8) = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (col + j < N) {
+          const uint32_t word = w[4 * v + (j >> 1)];
+          const uint16_t hbits = (j & 1) ? static_cast<uint16_t>(word >> 16) : static_cast<uint16_t>(word & 0xffffu);
+          reinterpret_cast<uint16_t*>(orow_chunk)[v * 8 + j] = hbits;
+        }
+      }
+    }
+  }
+}
+
+// Epilogue of one 128 x BN accumulator slice by one warp (lane quarter q): two register sets so
+// that the tensor-memory load of chunk c+1 is in flight while chunk c is converted and stored.
+// `release` is called once, right after the last tensor-memory load has completed.
+template <int BN, int EPI_BUFS, int PANEL_BYTES, typename Release>
+__device__ __forceinline__ void epilogue_tile(uint32_t taddr, float rscale, const float* colscale, const float* colbias,
+                                              uint8_t* warp_panels, int& sbuf, const CUtensorMap* tmap_out, bool tma_store,
+                                              __nv_bfloat16* orow, int row, int row0, int n0, int M, int N, bool vec_ok, int lane,
+                                              Release release) {
+  uint32_t ra[32], rb[32];
+  ptx::tmem_ld_32x32(taddr, ra);
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; c += 2) {
+    // ---- chunk c (in ra); prefetch c+1 into rb
+    ptx::tmem_ld_wait();
+    ptx::tmem_ld_32x32(taddr + (c + 1) * 32, rb);
+    uint32_t w[16];
+    epilogue_convert(ra, rscale, colscale + c * 32, colbias + c * 32, w);
+    uint8_t* panel = warp_panels + sbuf * PANEL_BYTES;
+    if (tma_store) {
+      // two 32-column chunks fill one 64-column panel (32 rows x 128 bytes, 128-byte swizzle:
+      // the 16-byte piece j of row r lands at piece j ^ (r & 7)), then one lane stores it
+      if (lane == 0) ptx::bulk_wait_group_read<EPI_BUFS - 1>();
+      __syncwarp();
+#pragma unroll
+      for (int v = 0; v < 4; ++v)
+        *reinterpret_cast<uint4*>(panel + lane * 128 + ((v ^ (lane & 7)) * 16)) = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+    } else if (row < M) {
+      epilogue_store_direct(orow + c * 32, w, n0 + c * 32, N, vec_ok);
+    }
+    // ---- chunk c+1 (in rb); prefetch c+2 into ra
+    ptx::tmem_ld_wait();
+    if (c + 2 < BN / 32) {
+      ptx::tmem_ld_32x32(taddr + (c + 2) * 32, ra);
+    } else {
+      // the whole accumulator has been read: hand the tensor-memory buffer back before the
+      // remaining conversion and stores
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) release();
+    }
+    epilogue_convert(rb, rscale, colscale + (c + 1) * 32, colbias + (c + 1) * 32, w);
+    if (tma_store) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v)
+        *reinterpret_cast<uint4*>(panel + lane * 128 + (((4 + v) ^ (lane & 7)) * 16)) = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+      ptx::fence_proxy_async();
+      __syncwarp();
+      const int col0 = n0 + (c >> 1) * 64;
+      if (lane == 0 && row0 < M && col0 < N) {
+        ptx::tma_store_2d(tmap_out, panel, col0, row0);
+        ptx::bulk_commit_group();
+      }
+      if (++sbuf == EPI_BUFS) sbuf = 0;
+    } else if (row < M) {
+      epilogue_store_direct(orow + (c + 1) * 32, w, n0 + (c + 1) * 32, N, vec_ok);
+    }
+  }
+}
 
 template <bool NVF4, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -327,71 +425,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       if constexpr (!NVF4) rscale = (row < p.M) ? __ldg(p.a_scales + static_cast<int64_t>(row) * p.a_scale_stride) : 0.0f;
       __nv_bfloat16* orow = p.out + static_cast<int64_t>(row) * p.N + n0;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(taddr + c * 32, r);
-        ptx::tmem_ld_wait();
-        if (c == BN / 32 - 1) {
-          // the accumulator is in registers now: hand the tensor-memory buffer back before
-          // the stores of this last chunk
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(acc_empty + acc);
-        }
-        uint32_t w[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int i0 = c * 32 + 2 * j;
-          const float x0 = fmaf(__uint_as_float(r[2 * j]) * rscale, colscale[i0], colbias[i0]);
-          const float x1 = fmaf(__uint_as_float(r[2 * j + 1]) * rscale, colscale[i0 + 1], colbias[i0 + 1]);
-          __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-          w[j] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        if (p.tma_store) {
-          // two 32-column chunks fill one 64-column panel (32 rows x 128 bytes, 128-byte swizzle:
-          // the 16-byte piece j of row r lands at piece j ^ (r & 7)), then one lane stores it
-          const int half = c & 1;
-          uint8_t* panel = store_stage + (q * C::kEpiBufs + sbuf) * C::kPanelBytes;
-          if (half == 0) {
-            if (lane == 0) ptx::bulk_wait_group_read<C::kEpiBufs - 1>();
-            __syncwarp();
-          }
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int piece = (half * 4 + v) ^ (lane & 7);
-            *reinterpret_cast<uint4*>(panel + lane * 128 + piece * 16) = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
-          }
-          if (half == 1) {
-            ptx::fence_proxy_async();
-            __syncwarp();
-            const int col0 = n0 + (c >> 1) * 64;
-            if (lane == 0 && row0 < p.M && col0 < p.N) {
-              ptx::tma_store_2d(&tmap_out, panel, col0, row0);
-              ptx::bulk_commit_group();
-            }
-            if (++sbuf == C::kEpiBufs) sbuf = 0;
-          }
-        } else if (row < p.M) {
-          const int cbase = n0 + c * 32;
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int col = cbase + v * 8;
-            if (vec_ok && col + 8 <= p.N) {
-              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if (col + j < p.N) {
-                  const uint32_t word = w[4 * v + (j >> 1)];
-                  const uint16_t hbits = (j & 1) ? static_cast<uint16_t>(word >> 16) : static_cast<uint16_t>(word & 0xffffu);
-                  reinterpret_cast<uint16_t*>(orow)[c * 32 + v * 8 + j] = hbits;
-                }
-              }
-            }
-          }
-        }
-      }
+      uint64_t* release_bar = acc_empty + acc;
+      epilogue_tile<BN, C::kEpiBufs, C::kPanelBytes>(taddr, rscale, colscale, colbias, store_stage + q * C::kEpiBufs * C::kPanelBytes,
+                                                     sbuf, &tmap_out, p.tma_store != 0, orow, row, row0, n0, p.M, p.N, vec_ok, lane,
+                                                     [release_bar]() { ptx::mbar_arrive(release_bar); });
       if (++acc == C::kAccStages) acc = 0, acc_phase ^= 1u;
     }
     // shared memory must stay valid until the last store has read it

@@ -259,67 +259,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if constexpr (!NVF4) rscale = (row < p.M) ? __ldg(p.a_scales + static_cast<int64_t>(row) * p.a_scale_stride) : 0.0f;
       __nv_bfloat16* orow = p.out + static_cast<int64_t>(row) * p.N + n0;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(taddr + c * 32, r);
-        ptx::tmem_ld_wait();
-        if (c == BN / 32 - 1) {
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive_cluster(acc_empty + acc, 0);  // the leader's barrier
-        }
-        uint32_t w[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int i0 = c * 32 + 2 * j;
-          const float x0 = fmaf(__uint_as_float(r[2 * j]) * rscale, colscale[i0], colbias[i0]);
-          const float x1 = fmaf(__uint_as_float(r[2 * j + 1]) * rscale, colscale[i0 + 1], colbias[i0 + 1]);
-          __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-          w[j] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        if (p.tma_store) {
-          const int half = c & 1;
-          uint8_t* panel = store_stage + (q * C::kEpiBufs + sbuf) * C::kPanelBytes;
-          if (half == 0) {
-            if (lane == 0) ptx::bulk_wait_group_read<C::kEpiBufs - 1>();
-            __syncwarp();
-          }
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int piece = (half * 4 + v) ^ (lane & 7);
-            *reinterpret_cast<uint4*>(panel + lane * 128 + piece * 16) = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
-          }
-          if (half == 1) {
-            ptx::fence_proxy_async();
-            __syncwarp();
-            const int col0 = n0 + (c >> 1) * 64;
-            if (lane == 0 && row0 < p.M && col0 < p.N) {
-              ptx::tma_store_2d(&tmap_out, panel, col0, row0);
-              ptx::bulk_commit_group();
-            }
-            if (++sbuf == C::kEpiBufs) sbuf = 0;
-          }
-        } else if (row < p.M) {
-          const int cbase = n0 + c * 32;
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int col = cbase + v * 8;
-            if (vec_ok && col + 8 <= p.N) {
-              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if (col + j < p.N) {
-                  const uint32_t word = w[4 * v + (j >> 1)];
-                  const uint16_t hbits = (j & 1) ? static_cast<uint16_t>(word >> 16) : static_cast<uint16_t>(word & 0xffffu);
-                  reinterpret_cast<uint16_t*>(orow)[c * 32 + v * 8 + j] = hbits;
-                }
-              }
-            }
-          }
-        }
-      }
+      uint64_t* release_bar = acc_empty + acc;
+      epilogue_tile<BN, C::kEpiBufs, C::kPanelBytes>(taddr, rscale, colscale, colbias, store_stage + q * C::kEpiBufs * C::kPanelBytes,
+                                                     sbuf, &tmap_out, p.tma_store != 0, orow, row, row0, n0, p.M, p.N, vec_ok, lane,
+                                                     [release_bar]() { ptx::mbar_arrive_cluster(release_bar, 0); });
       if (++acc == C::kAccStages) acc = 0, acc_phase ^= 1u;
     }
     if (lane == 0) ptx::bulk_wait_group_read<0>();
