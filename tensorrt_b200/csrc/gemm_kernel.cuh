@@ -15,13 +15,6 @@
 //   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp its own 32-lane quarter),
 //               scale, add bias, convert, store; overlaps the next tile's main loop when
 //               the accumulator is double-buffered in tensor memory
-// NVFP4 scale path, what was measured (8192^3, one B200): skipping the tcgen05.cp copies takes
-// the kernel from 336 us to 250 us, so they cost about a quarter of the run; moving the scales
-// with tcgen05.st from four extra warps (with the scale tiles in a ring of their own running
-// ahead of the operands) was slower still (2.8 vs 3.4 PFLOP/s on the same GPU), as was issuing
-// the copies of K tile i+1 before the MMAs of K tile i.  The loads alone (no MMA, no copies,
-// no epilogue) take 158 us at 128 x 256 tiles: the L2 -> SM path delivers ~20 TB/s.
-//
 // No TMA multicast is used anywhere.  Every mbarrier wait is bounded; a wait that gives up
 // raises a flag in global memory, the CTA drains and leaves, and the host reports
 // B200Q_ERR_TIMEOUT from b200q_device_status().
