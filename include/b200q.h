@@ -155,6 +155,49 @@ int b200q_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_scales, const floa
                      const void* bias, void* out, int64_t M, int64_t N, int64_t K,
                      b200q_stream_t stream);
 
+/* ------------------------------------------------------------------ fused row-parallel linear (GEMM + all-reduce over peer memory)
+ * Replaces "row-parallel linear, then tensorrt::fused_nccl_all_reduce" (the reference's
+ * _RowParallelLinear, tools/llm/tensor_parallel_llama_export.py:109-125: out = linear(x);
+ * all_reduce(out, "sum"); and the ALL_REDUCE collective layer of
+ * py/torch_tensorrt/dynamo/conversion/impl/nccl_ops.py:440-451) by two launches:
+ *
+ *   b200q_*_gemm_reduce_scatter  the GEMM; its epilogue TMA-stores every 32-row panel of the
+ *                                partial result straight into the receive buffer of the rank
+ *                                that owns those rows (rank r owns rows [r*M/world, (r+1)*M/world)),
+ *                                so the transfer overlaps the math tile by tile;
+ *   b200q_reduce_gather          each rank sums the `world` partials of its rows, adds the bias
+ *                                once, and stores the bf16 result into every rank's output.
+ *
+ * `b200q_peers` holds device pointers that are valid in THIS process for every rank's buffers
+ * (peer mappings, e.g. from CUDA IPC or a symmetric-memory allocator):
+ *   recv[r]   rank r's receive buffer, world * (M/world) * N bf16
+ *   out[r]    rank r's output, M * N bf16
+ *   flags[r]  rank r's flag words, at least 2 * world + 1 uint32, zeroed once before first use
+ * M must be a multiple of world * 128 and N of 8.  `epoch` must increase by one with every
+ * reduce_gather call on the group (all ranks pass the same value).  Both calls only enqueue
+ * work; device-side waits for peers are bounded and reported through b200q_device_status().
+ * The result is in out[rank] when the stream reaches the end of b200q_reduce_gather and stays
+ * valid until the next b200q_reduce_gather of the group.
+ */
+typedef struct b200q_peers {
+  int32_t rank;
+  int32_t world;
+  void* recv[8];
+  void* out[8];
+  uint32_t* flags[8];
+} b200q_peers;
+
+int b200q_fp8_gemm_reduce_scatter(const uint8_t* a_codes, const float* a_scales, int64_t a_scales_numel,
+                                  const uint8_t* b_codes, const float* b_scales, int64_t b_scales_numel,
+                                  const b200q_peers* peers, int64_t M, int64_t N, int64_t K,
+                                  b200q_stream_t stream);
+int b200q_nvfp4_gemm_reduce_scatter(const uint8_t* a_codes, const uint8_t* a_scales, const float* a_global,
+                                    const uint8_t* b_codes, const uint8_t* b_scales, const float* b_global,
+                                    const b200q_peers* peers, int64_t M, int64_t N, int64_t K,
+                                    b200q_stream_t stream);
+int b200q_reduce_gather(const b200q_peers* peers, const void* bias, int64_t M, int64_t N, uint32_t epoch,
+                        b200q_stream_t stream);
+
 /* ------------------------------------------------------------------ glue of the decoder linear stack
  * The benchmark workloads wrap the quantized linears in a Llama-shaped decoder layer
  * (RMSNorm -> QKV -> attention replaced by identity on V -> O -> residual -> RMSNorm ->

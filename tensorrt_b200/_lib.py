@@ -34,6 +34,9 @@ SIGNATURES = {
     "b200q_nvfp4_dequantize": (_c.c_int, [_p, _p, _p, _i64, _i64, _p, _c.c_int, _p]),
     "b200q_fp8_gemm": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _p]),
     "b200q_nvfp4_gemm": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
+    "b200q_fp8_gemm_reduce_scatter": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _p]),
+    "b200q_nvfp4_gemm_reduce_scatter": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
+    "b200q_reduce_gather": (_c.c_int, [_p, _p, _i64, _i64, _c.c_uint32, _p]),
     "b200q_rms_norm": (_c.c_int, [_p, _p, _p, _i64, _i64, _c.c_float, _p]),
     "b200q_silu_mul": (_c.c_int, [_p, _p, _i64, _i64, _p]),
     "b200q_add": (_c.c_int, [_p, _p, _p, _i64, _p]),
@@ -41,6 +44,13 @@ SIGNATURES = {
     "b200q_gemm_set_tile_n": (_c.c_int, [_c.c_int]),
     "b200q_device_status": (_c.c_int, [_c.c_int]),
 }
+
+
+
+class Peers(ctypes.Structure):
+    """struct b200q_peers of include/b200q.h."""
+    _fields_ = [("rank", _c.c_int32), ("world", _c.c_int32), ("recv", _p * 8), ("out", _p * 8), ("flags", _p * 8)]
+
 
 _lib = None
 

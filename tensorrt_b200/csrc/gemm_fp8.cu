@@ -90,4 +90,41 @@ int b200q_fp8_gemm(const uint8_t* a_codes, const float* a_scales, int64_t a_scal
   return gemm::launch<false>(a_codes, b_codes, p, static_cast<cudaStream_t>(stream), gemm::forced_bn());
 }
 
+static int fill_rs(gemm::Params& p, gemm::RsTargets& rs, const b200q_peers* peers, int64_t M) {
+  if (peers == nullptr || peers->world < 2 || peers->world > 8 || peers->rank < 0 || peers->rank >= peers->world) return B200Q_ERR_INVALID;
+  if (M % (static_cast<int64_t>(peers->world) * 128) != 0) return B200Q_ERR_INVALID;
+  p.rs_world = peers->world;
+  p.rs_rank = peers->rank;
+  p.rs_rows = static_cast<int>(M / peers->world);
+  for (int r = 0; r < peers->world; ++r) {
+    if (peers->recv[r] == nullptr) return B200Q_ERR_INVALID;
+    if (!aligned(peers->recv[r], 16)) return B200Q_ERR_ALIGN;
+    rs.recv[r] = peers->recv[r];
+  }
+  return B200Q_OK;
+}
+
+int b200q_fp8_gemm_reduce_scatter(const uint8_t* a_codes, const float* a_scales, int64_t a_scales_numel, const uint8_t* b_codes,
+                                  const float* b_scales, int64_t b_scales_numel, const b200q_peers* peers, int64_t M, int64_t N,
+                                  int64_t K, b200q_stream_t stream) {
+  if (a_codes == nullptr || b_codes == nullptr || a_scales == nullptr || b_scales == nullptr) return B200Q_ERR_INVALID;
+  if (M <= 0 || N <= 0 || K <= 0 || M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200Q_ERR_INVALID;
+  if (K % 16 != 0 || N % 8 != 0) return B200Q_ERR_INVALID;
+  if ((a_scales_numel != 1 && a_scales_numel != M) || (b_scales_numel != 1 && b_scales_numel != N)) return B200Q_ERR_INVALID;
+  if (!aligned(a_codes, 16) || !aligned(b_codes, 16)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  gemm::Params p{};
+  gemm::RsTargets rs{};
+  if (int rc = fill_rs(p, rs, peers, M)) return rc;
+  p.a_scales = a_scales;
+  p.b_scales = b_scales;
+  p.a_scale_stride = a_scales_numel == 1 ? 0 : 1;
+  p.b_scale_stride = b_scales_numel == 1 ? 0 : 1;
+  p.out = static_cast<__nv_bfloat16*>(peers->recv[peers->rank]);
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.k_bytes = static_cast<int>(K);
+  return gemm::launch<false>(a_codes, b_codes, p, static_cast<cudaStream_t>(stream), gemm::forced_bn(), &rs);
+}
+
 }  // extern "C"

@@ -48,8 +48,28 @@ inline int make_output_map(CUtensorMap* map, const void* base, int64_t M, int64_
   return r == CUDA_SUCCESS ? B200Q_OK : B200Q_ERR_CUDA;
 }
 
+// Receive buffers of the reduce-scatter epilogue: recv[r] is rank r's buffer
+// [world][rows_per_rank][N] bf16, mapped into this process (peer memory).
+struct RsTargets {
+  void* recv[8];
+};
+
+// Output maps of a launch: the local output, or one map per destination rank.
+inline int build_out_maps(OutMaps* maps, Params& p, const RsTargets* rs) {
+  p.tma_store = (p.N % 8 == 0) ? 1 : 0;
+  if (p.rs_world > 1) {
+    if (rs == nullptr || !p.tma_store || p.rs_world > 8 || p.rs_rows % 128 != 0 || p.rs_rows * p.rs_world != p.M)
+      return B200Q_ERR_INVALID;
+    for (int r = 0; r < p.rs_world; ++r)
+      if (int rc = make_output_map(&maps->m[r], rs->recv[r], static_cast<int64_t>(p.rs_world) * p.rs_rows, p.N)) return rc;
+    return B200Q_OK;
+  }
+  if (p.tma_store) return make_output_map(&maps->m[0], p.out, p.M, p.N);
+  return B200Q_OK;
+}
+
 template <bool NVF4, int BN>
-int launch_tile(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st) {
+int launch_tile(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, const RsTargets* rs = nullptr) {
   using C = Cfg<NVF4, BN>;
   static bool configured[64] = {};
   int dev = 0;
@@ -59,15 +79,11 @@ int launch_tile(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st) {
       return B200Q_ERR_CUDA;
     configured[dev] = true;
   }
-  CUtensorMap ta, tb, tout;
+  CUtensorMap ta, tb;
+  OutMaps tout = {};
   if (int rc = make_operand_map(&ta, a, p.M, p.k_bytes, kBM)) return rc;
   if (int rc = make_operand_map(&tb, b, p.N, p.k_bytes, BN)) return rc;
-  p.tma_store = (p.N % 8 == 0) ? 1 : 0;
-  if (p.tma_store) {
-    if (int rc = make_output_map(&tout, p.out, p.M, p.N)) return rc;
-  } else {
-    tout = ta;  // unused by the kernel
-  }
+  if (int rc = build_out_maps(&tout, p, rs)) return rc;
   const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   gemm_kernel<NVF4, BN><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, tout, p);
@@ -90,7 +106,7 @@ inline int make_scale_map(CUtensorMap* map, const void* base, int64_t row_tiles,
 
 // CTA-pair kernel: clusters of two CTAs, one cluster per 256 x 256 output tile.
 template <bool NVF4>
-int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st) {
+int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, const RsTargets* rs = nullptr) {
   using C = Cfg2<NVF4>;
   static bool configured[64] = {};
   int dev = 0;
@@ -100,15 +116,11 @@ int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st) {
       return B200Q_ERR_CUDA;
     configured[dev] = true;
   }
-  CUtensorMap ta, tb, tout, tsfa, tsfb;
+  CUtensorMap ta, tb, tsfa, tsfb;
+  OutMaps tout = {};
   if (int rc = make_operand_map(&ta, a, p.M, p.k_bytes, 128)) return rc;
   if (int rc = make_operand_map(&tb, b, p.N, p.k_bytes, kPairN / 2)) return rc;
-  p.tma_store = (p.N % 8 == 0) ? 1 : 0;
-  if (p.tma_store) {
-    if (int rc = make_output_map(&tout, p.out, p.M, p.N)) return rc;
-  } else {
-    tout = ta;
-  }
+  if (int rc = build_out_maps(&tout, p, rs)) return rc;
   if constexpr (NVF4) {
     if (int rc = make_scale_map(&tsfa, p.sfa, (p.M + 127) / 128, p.sf_col_tiles, 1)) return rc;
     if (int rc = make_scale_map(&tsfb, p.sfb, (p.N + 127) / 128, p.sf_col_tiles, 2)) return rc;
@@ -142,19 +154,19 @@ int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st) {
 // overrides the choice (used by tests to cover both instantiations); 512 forces the CTA-pair
 // kernel (256 x 256 tiles), which is otherwise used when there are at least sm_count/2 such tiles.
 template <bool NVF4>
-int launch(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, int force_bn) {
+int launch(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, int force_bn, const RsTargets* rs = nullptr) {
   p.status = device_status_word();
   if (p.status == nullptr) return B200Q_ERR_CUDA;
   int bn = force_bn;
   const int64_t pair_tiles = static_cast<int64_t>((p.M + kPairM - 1) / kPairM) * ((p.N + kPairN - 1) / kPairN);
   // measured: the CTA-pair kernel wins for FP8 (2.9 vs 2.75 PFLOP/s at 8192^3); for NVFP4 the
   // single-CTA 128 x 256 tile is faster (3.45 vs 3.2), so it is only used there when forced
-  if (bn == 512 || (bn == 0 && !NVF4 && pair_tiles >= sm_count() / 2)) return launch_pair<NVF4>(a, b, p, st);
+  if (bn == 512 || (bn == 0 && !NVF4 && pair_tiles >= sm_count() / 2)) return launch_pair<NVF4>(a, b, p, st, rs);
   if (bn != 128 && bn != 256) {
     const int64_t tiles256 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 255) / 256);
     bn = (tiles256 >= sm_count()) ? 256 : 128;
   }
-  return bn == 256 ? launch_tile<NVF4, 256>(a, b, p, st) : launch_tile<NVF4, 128>(a, b, p, st);
+  return bn == 256 ? launch_tile<NVF4, 256>(a, b, p, st, rs) : launch_tile<NVF4, 128>(a, b, p, st, rs);
 }
 
 int forced_bn();  // from the environment variable B200Q_GEMM_BN (0 when unset)

@@ -62,6 +62,12 @@ struct Cfg {
   static_assert(kColsNeeded <= 512, "tensor memory overflow");
 };
 
+// Output tensor maps: m[0] is the local output; in reduce-scatter mode m[r] is rank r's receive
+// buffer viewed as [world * rows_per_rank, N].
+struct OutMaps {
+  CUtensorMap m[8];
+};
+
 struct Params {
   const float* a_scales;   // FP8: [M] or [1]; NVFP4: pointer to the global scale of A
   const float* b_scales;   // FP8: [N] or [1]; NVFP4: pointer to the global scale of B
@@ -75,6 +81,9 @@ struct Params {
   int k_bytes;             // bytes per operand row (K for FP8, K/2 for NVFP4)
   int sf_col_tiles;        // NVFP4: number of 4-scale column tiles per row tile (ceil(K/64))
   int tma_store;           // 1: output leaves through TMA stores (needs N % 8 == 0), 0: direct stores
+  int rs_world;            // > 1: reduce-scatter epilogue over `rs_world` ranks (TMA stores to peer buffers)
+  int rs_rank;             //      this rank
+  int rs_rows;             //      rows owned by each rank (M / rs_world, a multiple of 128)
   int* status;             // device status word (0 = ok)
 };
 
@@ -117,7 +126,7 @@ __device__ __forceinline__ void epilogue_store_direct(__nv_bfloat16* orow_chunk,
 // `release` is called once, right after the last tensor-memory load has completed.
 template <int BN, int EPI_BUFS, int PANEL_BYTES, typename Release>
 __device__ __forceinline__ void epilogue_tile(uint32_t taddr, float rscale, const float* colscale, const float* colbias,
-                                              uint8_t* warp_panels, int& sbuf, const CUtensorMap* tmap_out, bool tma_store,
+                                              uint8_t* warp_panels, int& sbuf, const CUtensorMap* tmap_out, int store_y, bool tma_store,
                                               __nv_bfloat16* orow, int row, int row0, int n0, int M, int N, bool vec_ok, int lane,
                                               Release release) {
   uint32_t ra[32], rb[32];
@@ -161,7 +170,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, float rscale, cons
       __syncwarp();
       const int col0 = n0 + (c >> 1) * 64;
       if (lane == 0 && row0 < M && col0 < N) {
-        ptx::tma_store_2d(tmap_out, panel, col0, row0);
+        ptx::tma_store_2d(tmap_out, panel, col0, store_y);
         ptx::bulk_commit_group();
       }
       if (++sbuf == EPI_BUFS) sbuf = 0;
@@ -174,7 +183,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, float rscale, cons
 template <bool NVF4, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const __grid_constant__ CUtensorMap tmap_out, const Params p) {
+            const __grid_constant__ OutMaps tmap_out, const Params p) {
   using C = Cfg<NVF4, BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -215,7 +224,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     ptx::fence_barrier_init();
     ptx::prefetch_tmap(&tmap_a);
     ptx::prefetch_tmap(&tmap_b);
-    if (p.tma_store) ptx::prefetch_tmap(&tmap_out);
+    if (p.tma_store) ptx::prefetch_tmap(&tmap_out.m[0]);
   }
   if (warp == 1) {
     ptx::tmem_alloc<1>(tmem_holder, C::kTmemCols);
@@ -418,14 +427,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       if constexpr (!NVF4) rscale = (row < p.M) ? __ldg(p.a_scales + static_cast<int64_t>(row) * p.a_scale_stride) : 0.0f;
       __nv_bfloat16* orow = p.out + static_cast<int64_t>(row) * p.N + n0;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      // Row-parallel reduce-scatter mode: the 32-row panel goes to the rank that owns these rows,
+      // into the slot of its receive buffer reserved for this rank.
+      const CUtensorMap* omap = &tmap_out.m[0];
+      int store_y = row0;
+      if (p.rs_world > 1) {
+        const int owner = row0 / p.rs_rows;
+        omap = &tmap_out.m[owner];
+        store_y = p.rs_rank * p.rs_rows + (row0 - owner * p.rs_rows);
+      }
       uint64_t* release_bar = acc_empty + acc;
       epilogue_tile<BN, C::kEpiBufs, C::kPanelBytes>(taddr, rscale, colscale, colbias, store_stage + q * C::kEpiBufs * C::kPanelBytes,
-                                                     sbuf, &tmap_out, p.tma_store != 0, orow, row, row0, n0, p.M, p.N, vec_ok, lane,
+                                                     sbuf, omap, store_y, p.tma_store != 0, orow, row, row0, n0, p.M, p.N, vec_ok, lane,
                                                      [release_bar]() { ptx::mbar_arrive(release_bar); });
       if (++acc == C::kAccStages) acc = 0, acc_phase ^= 1u;
     }
     // shared memory must stay valid until the last store has read it
-    if (lane == 0) ptx::bulk_wait_group_read<0>();
+    if (lane == 0) {
+      ptx::bulk_wait_group_read<0>();
+      if (p.rs_world > 1) ptx::bulk_wait_group_all();  // stores to peers are complete before the kernel retires
+    }
   }
 
   ptx::tc_fence_before();

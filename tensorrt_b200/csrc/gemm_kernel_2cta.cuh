@@ -59,7 +59,7 @@ struct Cfg2 {
 template <bool NVF4>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_sfa,
+                 const __grid_constant__ OutMaps tmap_out, const __grid_constant__ CUtensorMap tmap_sfa,
                  const __grid_constant__ CUtensorMap tmap_sfb, const Params p) {
   using C = Cfg2<NVF4>;
   constexpr int BN = kPairN;
@@ -102,7 +102,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     ptx::fence_barrier_init();
     ptx::prefetch_tmap(&tmap_a);
     ptx::prefetch_tmap(&tmap_b);
-    if (p.tma_store) ptx::prefetch_tmap(&tmap_out);
+    if (p.tma_store) ptx::prefetch_tmap(&tmap_out.m[0]);
   }
   if (warp == 1) {
     ptx::tmem_alloc<2>(tmem_holder, C::kTmemCols);
@@ -259,13 +259,25 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if constexpr (!NVF4) rscale = (row < p.M) ? __ldg(p.a_scales + static_cast<int64_t>(row) * p.a_scale_stride) : 0.0f;
       __nv_bfloat16* orow = p.out + static_cast<int64_t>(row) * p.N + n0;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      // Row-parallel reduce-scatter mode: the 32-row panel goes to the rank that owns these rows,
+      // into the slot of its receive buffer reserved for this rank.
+      const CUtensorMap* omap = &tmap_out.m[0];
+      int store_y = row0;
+      if (p.rs_world > 1) {
+        const int owner = row0 / p.rs_rows;
+        omap = &tmap_out.m[owner];
+        store_y = p.rs_rank * p.rs_rows + (row0 - owner * p.rs_rows);
+      }
       uint64_t* release_bar = acc_empty + acc;
       epilogue_tile<BN, C::kEpiBufs, C::kPanelBytes>(taddr, rscale, colscale, colbias, store_stage + q * C::kEpiBufs * C::kPanelBytes,
-                                                     sbuf, &tmap_out, p.tma_store != 0, orow, row, row0, n0, p.M, p.N, vec_ok, lane,
+                                                     sbuf, omap, store_y, p.tma_store != 0, orow, row, row0, n0, p.M, p.N, vec_ok, lane,
                                                      [release_bar]() { ptx::mbar_arrive_cluster(release_bar, 0); });
       if (++acc == C::kAccStages) acc = 0, acc_phase ^= 1u;
     }
-    if (lane == 0) ptx::bulk_wait_group_read<0>();
+    if (lane == 0) {
+      ptx::bulk_wait_group_read<0>();
+      if (p.rs_world > 1) ptx::bulk_wait_group_all();  // stores to peers are complete before the kernel retires
+    }
   }
 
   ptx::tc_fence_before();

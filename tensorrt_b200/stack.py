@@ -195,13 +195,22 @@ class DecoderStack:
     """`layers` decoder layers sharing one TP group.  `weights` is an iterable of per-layer dicts
     of full (unsharded) bf16 weights; each is sharded, quantized and dropped."""
 
-    def __init__(self, cfg: StackConfig, weights, backend=None, rank: int = 0, world: int = 1, group=None, slabs: int = 1):
+    def __init__(self, cfg: StackConfig, weights, backend=None, rank: int = 0, world: int = 1, group=None, slabs: int = 1,
+                 fused_rows: int = 0):
+        """`fused_rows` > 0: row-parallel linears use the fused GEMM + peer-memory all-reduce
+        (tp.FusedRowParallel) for up to that many rows; other row counts use NCCL."""
         cfg.check(world)
         self.cfg, self.rank, self.world = cfg, rank, world
         self.backend = backend or CudaBackend(cfg.mode)
         reduce = AllReduce(group) if world > 1 else None
         row_parallel = None
-        if world > 1:
+        if world > 1 and fused_rows > 0:
+            from .tp import FusedRowParallel
+
+            be = self.backend
+            row_parallel = FusedRowParallel(cfg.mode, fused_rows, cfg.hidden, group,
+                                            fallback=lambda x, qw, amax=None: reduce(be.linear(x, qw, amax)))
+        elif world > 1:
             if slabs > 1:
                 row_parallel = OverlappedRowParallel(self.backend, reduce, slabs)
             else:

@@ -35,13 +35,13 @@ def run(args):
     seed = 4 if tp else 3
     group = None
     t0 = time.time()
+    batch, seq = (32, 1024) if tp else (8, 2048)
     stack = DecoderStack(cfg, random_layer_weights(cfg, seed, device=dev), rank=rank, world=world, group=group,
-                         slabs=args.slabs if world > 1 else 1)
+                         slabs=args.slabs if world > 1 else 1, fused_rows=batch * seq if (world > 1 and args.fused) else 0)
     torch.cuda.synchronize()
     build_s = time.time() - t0
 
     g = torch.Generator().manual_seed(seed)
-    batch, seq = (32, 1024) if tp else (8, 2048)
     h_host = torch.randn(batch, seq, cfg.hidden, generator=g).bfloat16().pin_memory()
     h = h_host.to(dev)
     tokens = batch * seq
@@ -85,6 +85,8 @@ def run(args):
                                "attention core = identity on the V slice (kv heads repeated to the query width)"
                                + ("; activation amax calibrated once (static quantizer input)" if cfg.mode == "nvfp4" else ""),
                    "parallelism": f"tp{world}", "slabs": args.slabs if world > 1 else 1,
+                   "row_parallel": ("fused GEMM reduce-scatter epilogue + peer-memory reduce/all-gather" if (world > 1 and args.fused)
+                                    else ("NCCL all-reduce" if world > 1 else "none")),
                    "l2": "weights + activations per forward far exceed the 126 MB L2"},
         "clocks": clocks.summary(), "build_seconds": round(build_s, 1), "device_status": status,
         "e2e": {"value": tokens * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h_host.numel() * 2,

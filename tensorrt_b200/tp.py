@@ -78,3 +78,78 @@ def check_same_shape(t: torch.Tensor, group=None) -> None:
     dist.all_gather_object(seen, mine, group=group)
     if any(s != seen[0] for s in seen):
         raise ShapeMismatchError(f"all-reduce operands differ across ranks: {seen}")
+
+
+class FusedRowParallel:
+    """Row-parallel quantized linear + all-reduce as two b200q launches over peer memory
+    (include/b200q.h: b200q_*_gemm_reduce_scatter, b200q_reduce_gather) instead of a GEMM followed
+    by an NCCL all-reduce.  torch's symmetric-memory allocator provides the peer mappings (one
+    rendezvous at construction); nothing else of it is used: the data path and the flag
+    protocol are this library's own kernels.
+
+    `max_rows` x `n_out` bf16 bounds the buffers.  Calls whose row count is not a multiple of
+    world * 128 (decode steps) fall back to `fallback(x, qw, amax)`, the NCCL path.
+    The returned tensor is a view of this rank's output buffer and is valid until the next call.
+    """
+
+    def __init__(self, mode: str, max_rows: int, n_out: int, group=None, fallback=None):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib
+
+        self.mode, self.group, self.fallback = mode, group or dist.group.WORLD, fallback
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        if self.world > 8:
+            raise ValueError("FusedRowParallel supports at most 8 ranks")
+        self.max_rows, self.n_out = max_rows, n_out
+        dev = torch.device("cuda", torch.cuda.current_device())
+        name = self.group.group_name
+        nbytes = max_rows * n_out * 2
+        self._bufs = []
+        ptrs = []
+        for size in (nbytes, nbytes, 4096):
+            t = symm_mem.empty(size, dtype=torch.uint8, device=dev)
+            t.zero_()
+            h = symm_mem.rendezvous(t, name)
+            self._bufs.append((t, h))
+            ptrs.append([int(p) for p in h.buffer_ptrs])
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        self.out_local = self._bufs[1][0]
+        self.peers = _lib.Peers()
+        self.peers.rank, self.peers.world = self.rank, self.world
+        for r in range(self.world):
+            self.peers.recv[r], self.peers.out[r], self.peers.flags[r] = ptrs[0][r], ptrs[1][r], ptrs[2][r]
+        self._peers_ref = ctypes.byref(self.peers)
+        self.epoch = 0
+
+    def __call__(self, x: torch.Tensor, qw, amax=None, bias=None) -> torch.Tensor:
+        from . import capi
+        from ._lib import check, load
+
+        rows = x.shape[0]
+        n = self.n_out
+        if rows % (self.world * 128) or rows > self.max_rows:
+            if self.fallback is None:
+                raise ValueError(f"{rows} rows: need a multiple of {self.world * 128} and at most {self.max_rows}")
+            return self.fallback(x, qw, amax)
+        lib = load()
+        stream = torch.cuda.current_stream().cuda_stream
+        if self.mode == "fp8":
+            xc, xs = capi.fp8_quantize(x, None)
+            k = xc.shape[1]
+            check(lib.b200q_fp8_gemm_reduce_scatter(xc.data_ptr(), xs.data_ptr(), xs.numel(), qw[0].data_ptr(), qw[1].data_ptr(),
+                                                    qw[1].numel(), self._peers_ref, rows, n, k, stream), "b200q_fp8_gemm_reduce_scatter")
+        else:
+            xc, xs, xg = capi.nvfp4_quantize(x, capi.amax(x) if amax is None else amax)
+            k = xc.shape[1] * 2
+            check(lib.b200q_nvfp4_gemm_reduce_scatter(xc.data_ptr(), xs.data_ptr(), xg.data_ptr(), qw[0].data_ptr(), qw[1].data_ptr(),
+                                                      qw[2].data_ptr(), self._peers_ref, rows, n, k, stream),
+                  "b200q_nvfp4_gemm_reduce_scatter")
+        self.epoch += 1
+        b = None if bias is None else bias.to(torch.bfloat16).contiguous()
+        check(lib.b200q_reduce_gather(self._peers_ref, None if b is None else b.data_ptr(), rows, n, self.epoch, stream),
+              "b200q_reduce_gather")
+        return self.out_local[: rows * n * 2].view(torch.bfloat16).view(rows, n)

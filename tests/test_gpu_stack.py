@@ -74,7 +74,7 @@ def test_stack_matches_oracle_single_gpu(b200, mode):
     assert o.rel_l2(y.float().cpu(), ref.float()) < (2e-2 if mode == "fp8" else 6e-2)
 
 
-def _tp_worker(rank, world, store_path, out_path, slabs):
+def _tp_worker(rank, world, store_path, out_path, slabs, fused):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
 
@@ -95,7 +95,10 @@ def _tp_worker(rank, world, store_path, out_path, slabs):
 
     r = torch.ops.tensorrt.fused_nccl_all_reduce(t, "sum", group_name_of())
     assert torch.allclose(r.cpu(), torch.full((1, 4), world * (world + 1) / 2), atol=1e-3, rtol=1e-3)
-    y = DecoderStack(cfg, _to(ws, "cuda"), rank=rank, world=world, slabs=slabs)(h.cuda())
+    stack = DecoderStack(cfg, _to(ws, "cuda"), rank=rank, world=world, slabs=slabs, fused_rows=512 if fused else 0)
+    y = stack(h.cuda())
+    y2 = stack(h.cuda())          # a second pass reuses the peer buffers and flag epochs
+    assert torch.equal(y, y2)
     torch.cuda.synchronize()
     assert tensorrt_b200.capi.device_status() == 0
     if rank == 0:
@@ -104,8 +107,8 @@ def _tp_worker(rank, world, store_path, out_path, slabs):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("slabs", [1, 2])
-def test_tp2_stack_matches_oracle(b200, slabs):
+@pytest.mark.parametrize("slabs,fused", [(1, False), (2, False), (1, True)])
+def test_tp2_stack_matches_oracle(b200, slabs, fused):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -115,7 +118,7 @@ def test_tp2_stack_matches_oracle(b200, slabs):
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     with tempfile.TemporaryDirectory() as d:
         out = os.path.join(d, "y.pt")
-        mp.spawn(_tp_worker, args=(2, os.path.join(d, "store"), out, slabs), nprocs=2, join=True)
+        mp.spawn(_tp_worker, args=(2, os.path.join(d, "store"), out, slabs, fused), nprocs=2, join=True)
         y = torch.load(out)
     cfg = StackConfig(hidden=512, n_q=8, n_kv=2, head_dim=64, ffn=1024, layers=2, mode="fp8")
     ws = _weights(cfg, 7)
