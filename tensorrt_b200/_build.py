@@ -35,11 +35,31 @@ def _nvcc() -> str:
 
 
 def _stamp(paths, extra="") -> str:
+    # content + file name only: the stamp must not change when the tree is copied elsewhere
     h = hashlib.sha256(extra.encode())
-    for p in sorted(paths):
-        h.update(str(p).encode())
+    for p in sorted(paths, key=lambda q: Path(q).name):
+        h.update(Path(p).name.encode())
         h.update(Path(p).read_bytes())
     return h.hexdigest()
+
+
+class _BuildLock:
+    """Inter-process lock: ranks of one job importing the package at the same time must not
+    compile into the same files concurrently."""
+
+    def __enter__(self):
+        import fcntl
+
+        (PKG / "build").mkdir(exist_ok=True)
+        self.f = open(PKG / "build" / ".lock", "w")
+        fcntl.flock(self.f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        import fcntl
+
+        fcntl.flock(self.f, fcntl.LOCK_UN)
+        self.f.close()
 
 
 def _run(cmd, log_path: Path | None = None) -> str:
@@ -54,6 +74,11 @@ def _run(cmd, log_path: Path | None = None) -> str:
 
 def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     """Compile every .cu under csrc/ for sm_100a and link libb200q.so."""
+    with _BuildLock():
+        return _build_cuda(force, verbose)
+
+
+def _build_cuda(force: bool, verbose: bool) -> Path:
     sources = [CSRC / s for s in CUDA_SOURCES if (CSRC / s).exists()]
     headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + [ROOT / "include" / "b200q.h"]
     stamp = _stamp(sources + headers, " ".join(NVCC_FLAGS))
@@ -87,6 +112,11 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
 
 def build_torch_shim(force: bool = False) -> Path:
     """Compile the torch.library shim (C++17, no CUDA code) against libb200q.so."""
+    with _BuildLock():
+        return _build_torch_shim(force)
+
+
+def _build_torch_shim(force: bool) -> Path:
     import torch
     from torch.utils import cpp_extension
 

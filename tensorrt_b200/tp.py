@@ -94,7 +94,11 @@ class FusedRowParallel:
 
     def __init__(self, mode: str, max_rows: int, n_out: int, group=None, fallback=None):
         import ctypes
+        import os
 
+        # plain peer mappings are all this path needs; keep the allocator from also binding the
+        # buffers to an NVLink multicast object
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
         from . import _lib
