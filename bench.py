@@ -381,6 +381,8 @@ def main():
     ap.add_argument("--workload", default="nvfp4_quantize")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--shape", default="", help="M,N,K for the GEMM workloads (default: the whole sweep)")
+    ap.add_argument("--micro-batches", type=int, default=2, dest="micro_batches",
+                    help="tp_stack: token halves walking the layers on separate streams (all-reduce / GEMM overlap)")
     ap.add_argument("--fused", type=int, default=1, help="tp_stack: 1 = fused GEMM + peer-memory all-reduce, 0 = NCCL")
     ap.add_argument("--slabs", type=int, default=1, help="row slabs per row-parallel linear (all-reduce overlap) in tp_stack")
     args = ap.parse_args()

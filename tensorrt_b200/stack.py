@@ -219,12 +219,36 @@ class DecoderStack:
         self.layers = [DecoderLayer(cfg, shard_layer_weights(w, cfg, rank, world) if world > 1 else w, self.backend, world,
                                     row_parallel) for w in weights]
 
-    def forward(self, h: torch.Tensor) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, micro_batches: int = 1) -> torch.Tensor:
+        """`micro_batches` = 2 (tensor-parallel, CUDA): the tokens are split in two halves that walk
+        the layers on two streams, so the all-reduce of one half runs while the other half's
+        GEMMs compute.  The result is the same as with one batch: every op is row-wise."""
         shape = h.shape
         h = h.reshape(-1, shape[-1])
+        if micro_batches > 1 and self.world > 1 and h.is_cuda and h.shape[0] >= 2 * 128 * self.world:
+            return self._forward_overlapped(h, micro_batches).view(shape)
         for layer in self.layers:
             h = layer.forward(h)
         return h.view(shape)
+
+    def _forward_overlapped(self, h: torch.Tensor, n: int) -> torch.Tensor:
+        main = torch.cuda.current_stream()
+        if getattr(self, "_streams", None) is None or len(self._streams) != n:
+            self._streams = [torch.cuda.Stream() for _ in range(n)]
+        rows = h.shape[0]
+        step = (rows // n + 127) // 128 * 128
+        parts = [h[i * step:min(rows, (i + 1) * step)] for i in range(n)]
+        for st in self._streams:
+            st.wait_stream(main)
+        for layer in self.layers:
+            for i, st in enumerate(self._streams):
+                with torch.cuda.stream(st):
+                    parts[i] = layer.forward(parts[i])
+        for i, st in enumerate(self._streams):
+            parts[i].record_stream(main)
+            main.wait_stream(st)
+        h.record_stream(self._streams[0])
+        return torch.cat(parts, dim=0)
 
     __call__ = forward
 

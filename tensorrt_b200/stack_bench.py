@@ -50,13 +50,14 @@ def run(args):
         stack.calibrate(h)  # static activation amax in front of every linear, as after calibration
 
     with bench.ClockSampler(local) as clocks:
-        ms = _fwd_time(lambda: stack(h), steps, warmup, world, bench)
+        mb = args.micro_batches if world > 1 else 1
+        ms = _fwd_time(lambda: stack.forward(h, mb), steps, warmup, world, bench)
     status = capi.device_status()
     prefill_tps = tokens * steps / (ms * 1e-3)
 
     def e2e():
         x = h_host.to(dev, non_blocking=True)
-        y = stack(x)
+        y = stack.forward(x, args.micro_batches if world > 1 else 1)
         return float(y.float().abs().mean().item())  # device -> host read of a scalar of the result
 
     e2e_ms = _fwd_time(e2e, max(1, min(steps, 3)), 1, world, bench)
@@ -84,7 +85,7 @@ def run(args):
                                f"ffn {cfg.ffn}, {cfg.layers} layers; prefill {batch} x {seq} tokens; random-init weights N(0, 0.02); "
                                "attention core = identity on the V slice (kv heads repeated to the query width)"
                                + ("; activation amax calibrated once (static quantizer input)" if cfg.mode == "nvfp4" else ""),
-                   "parallelism": f"tp{world}", "slabs": args.slabs if world > 1 else 1,
+                   "parallelism": f"tp{world}", "micro_batches": args.micro_batches if world > 1 else 1, "slabs": args.slabs if world > 1 else 1,
                    "row_parallel": ("fused GEMM reduce-scatter epilogue + peer-memory reduce/all-gather" if (world > 1 and args.fused)
                                     else ("NCCL all-reduce" if world > 1 else "none")),
                    "l2": "weights + activations per forward far exceed the 126 MB L2"},

@@ -93,41 +93,52 @@ class FusedRowParallel:
     """
 
     def __init__(self, mode: str, max_rows: int, n_out: int, group=None, fallback=None):
-        import ctypes
         import os
 
         # plain peer mappings are all this path needs; keep the allocator from also binding the
         # buffers to an NVLink multicast object
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        import torch.distributed._symmetric_memory as symm_mem
-
-        from . import _lib
-
         self.mode, self.group, self.fallback = mode, group or dist.group.WORLD, fallback
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         if self.world > 8:
             raise ValueError("FusedRowParallel supports at most 8 ranks")
         self.max_rows, self.n_out = max_rows, n_out
+        # one set of peer buffers, flags and epoch counter per CUDA stream that calls in: calls on
+        # different streams may overlap on the device and must not share them
+        self._ctx: dict = {}
+
+    def _context(self, rows: int):
+        """Buffers of the calling stream, (re)allocated collectively: every rank reaches this point
+        with the same stream order and the same `rows`."""
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib
+
+        key = torch.cuda.current_stream().cuda_stream
+        ctx = self._ctx.get(key)
+        if ctx is not None and ctx["rows"] >= rows:
+            return ctx
         dev = torch.device("cuda", torch.cuda.current_device())
         name = self.group.group_name
-        nbytes = max_rows * n_out * 2
-        self._bufs = []
-        ptrs = []
+        nbytes = rows * self.n_out * 2
+        bufs, ptrs = [], []
         for size in (nbytes, nbytes, 4096):
             t = symm_mem.empty(size, dtype=torch.uint8, device=dev)
             t.zero_()
             h = symm_mem.rendezvous(t, name)
-            self._bufs.append((t, h))
+            bufs.append((t, h))
             ptrs.append([int(p) for p in h.buffer_ptrs])
-        torch.cuda.synchronize()
+        torch.cuda.current_stream().synchronize()
         dist.barrier(self.group)
-        self.out_local = self._bufs[1][0]
-        self.peers = _lib.Peers()
-        self.peers.rank, self.peers.world = self.rank, self.world
+        peers = _lib.Peers()
+        peers.rank, peers.world = self.rank, self.world
         for r in range(self.world):
-            self.peers.recv[r], self.peers.out[r], self.peers.flags[r] = ptrs[0][r], ptrs[1][r], ptrs[2][r]
-        self._peers_ref = ctypes.byref(self.peers)
-        self.epoch = 0
+            peers.recv[r], peers.out[r], peers.flags[r] = ptrs[0][r], ptrs[1][r], ptrs[2][r]
+        ctx = {"rows": rows, "bufs": bufs, "peers": peers, "ref": ctypes.byref(peers), "out": bufs[1][0], "epoch": 0}
+        self._ctx[key] = ctx
+        return ctx
 
     def __call__(self, x: torch.Tensor, qw, amax=None, bias=None) -> torch.Tensor:
         from . import capi
@@ -140,20 +151,22 @@ class FusedRowParallel:
                 raise ValueError(f"{rows} rows: need a multiple of {self.world * 128} and at most {self.max_rows}")
             return self.fallback(x, qw, amax)
         lib = load()
+        ctx = self._context(rows)
+        ref = ctx["ref"]
         stream = torch.cuda.current_stream().cuda_stream
         if self.mode == "fp8":
             xc, xs = capi.fp8_quantize(x, None)
             k = xc.shape[1]
             check(lib.b200q_fp8_gemm_reduce_scatter(xc.data_ptr(), xs.data_ptr(), xs.numel(), qw[0].data_ptr(), qw[1].data_ptr(),
-                                                    qw[1].numel(), self._peers_ref, rows, n, k, stream), "b200q_fp8_gemm_reduce_scatter")
+                                                    qw[1].numel(), ref, rows, n, k, stream), "b200q_fp8_gemm_reduce_scatter")
         else:
             xc, xs, xg = capi.nvfp4_quantize(x, capi.amax(x) if amax is None else amax)
             k = xc.shape[1] * 2
             check(lib.b200q_nvfp4_gemm_reduce_scatter(xc.data_ptr(), xs.data_ptr(), xg.data_ptr(), qw[0].data_ptr(), qw[1].data_ptr(),
-                                                      qw[2].data_ptr(), self._peers_ref, rows, n, k, stream),
+                                                      qw[2].data_ptr(), ref, rows, n, k, stream),
                   "b200q_nvfp4_gemm_reduce_scatter")
-        self.epoch += 1
+        ctx["epoch"] += 1
         b = None if bias is None else bias.to(torch.bfloat16).contiguous()
-        check(lib.b200q_reduce_gather(self._peers_ref, None if b is None else b.data_ptr(), rows, n, self.epoch, stream),
+        check(lib.b200q_reduce_gather(ref, None if b is None else b.data_ptr(), rows, n, ctx["epoch"], stream),
               "b200q_reduce_gather")
-        return self.out_local[: rows * n * 2].view(torch.bfloat16).view(rows, n)
+        return ctx["out"][: rows * n * 2].view(torch.bfloat16).view(rows, n)
