@@ -205,6 +205,9 @@ int b200q_reduce_gather(const b200q_peers* peers, const void* bias, int64_t M, i
  * elementwise layers (RMSNorm: lowering/passes/replace_fused_rms_norm.py:12-92); here they are
  * plain streaming kernels over bf16 so that the stack runs without any library kernel.
  *   b200q_rms_norm      out = x * rsqrt(mean(x^2) + eps) * weight, per row; cols % 8 == 0
+ *   b200q_add_rms_norm_fp8_quantize   the three steps in front of a quantized linear in one pass:
+ *                       h_out = h + delta (delta NULL: no add, h_out unused), x = rms_norm(h_out),
+ *                       per-token FP8 codes and scales of x; cols % 16 == 0, cols <= 16384
  *   b200q_silu_mul      out[t, j] = silu(gu[t, j]) * gu[t, f + j], gu is [rows, 2f]; f % 8 == 0
  *   b200q_add           out = a + b over n elements (n % 8 == 0)
  *   b200q_expand_heads  out[t, h*hd + d] = src[t*src_stride + src_col0 + (h / rep)*hd + d]
@@ -212,6 +215,9 @@ int b200q_reduce_gather(const b200q_peers* peers, const void* bias, int64_t M, i
  */
 int b200q_rms_norm(const void* x, const void* weight, void* out, int64_t rows, int64_t cols, float eps,
                    b200q_stream_t stream);
+int b200q_add_rms_norm_fp8_quantize(const void* h, const void* delta, const void* weight, void* h_out,
+                                    uint8_t* codes_out, float* scales_out, int64_t rows, int64_t cols,
+                                    float eps, b200q_stream_t stream);
 int b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t f, b200q_stream_t stream);
 int b200q_add(const void* a, const void* b, void* out, int64_t n, b200q_stream_t stream);
 int b200q_expand_heads(const void* src, int64_t src_stride, int64_t src_col0, void* out, int64_t rows,

@@ -38,6 +38,7 @@ SIGNATURES = {
     "b200q_nvfp4_gemm_reduce_scatter": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "b200q_reduce_gather": (_c.c_int, [_p, _p, _i64, _i64, _c.c_uint32, _p]),
     "b200q_rms_norm": (_c.c_int, [_p, _p, _p, _i64, _i64, _c.c_float, _p]),
+    "b200q_add_rms_norm_fp8_quantize": (_c.c_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _c.c_float, _p]),
     "b200q_silu_mul": (_c.c_int, [_p, _p, _i64, _i64, _p]),
     "b200q_add": (_c.c_int, [_p, _p, _p, _i64, _p]),
     "b200q_expand_heads": (_c.c_int, [_p, _i64, _i64, _p, _i64, _c.c_int, _c.c_int, _c.c_int, _p]),

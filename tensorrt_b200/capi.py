@@ -216,6 +216,25 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.
     return out
 
 
+def add_rms_norm_fp8_quantize(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float = 1e-5):
+    """-> (h + delta (h itself when delta is None), FP8 codes of rms_norm(h + delta), per-token scales)."""
+    _need_cuda(h, delta, weight)
+    _bf16(h, weight)
+    h = h.contiguous()
+    rows, cols = _rows_cols(h)
+    h_out = h
+    if delta is not None:
+        _bf16(delta)
+        delta = delta.contiguous()
+        h_out = torch.empty_like(h)
+    codes = torch.empty(h.shape, dtype=torch.uint8, device=h.device)
+    scales = torch.empty(rows, dtype=torch.float32, device=h.device)
+    with torch.cuda.device(h.device):
+        check(load().b200q_add_rms_norm_fp8_quantize(h.data_ptr(), _ptr(delta), weight.data_ptr(), h_out.data_ptr(), codes.data_ptr(),
+                                                     scales.data_ptr(), rows, cols, eps, _stream(h)), "b200q_add_rms_norm_fp8_quantize")
+    return h_out, codes, scales
+
+
 def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     """[.., 2F] (gate columns first) -> [.., F] = silu(gate) * up."""
     _need_cuda(gate_up)

@@ -77,6 +77,80 @@ rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   }
 }
 
+// Residual add + RMSNorm + per-token FP8 quantize of one row per CTA, the row held in registers:
+//   h_new = bf16(h + delta)            (delta may be null: h_new = h, nothing is written back)
+//   x     = bf16(h_new * rsqrt(mean(h_new^2) + eps) * w)
+//   scale = max|x| / 448 (0 -> 1);  code = e4m3(x / scale)
+// Same arithmetic and rounding points as add -> rms_norm -> fp8 quantize run one after the
+// other, with 1.75 bytes of traffic per element and step instead of 3.25.
+template <int ITEMS>
+__global__ void __launch_bounds__(kThreads)
+add_norm_quant_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ delta,
+                      const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out, uint8_t* __restrict__ codes,
+                      float* __restrict__ scales, int64_t cols, float eps) {
+  __shared__ float red[kThreads / 32];
+  const int64_t row = blockIdx.x;
+  const int groups = static_cast<int>(cols >> 3);
+  float v[ITEMS][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int g = threadIdx.x + i * kThreads;
+    if (g < groups) {
+      Elem<__nv_bfloat16>::load8(h + row * cols + (int64_t)g * 8, v[i]);
+      if (delta != nullptr) {
+        float d[8];
+        Elem<__nv_bfloat16>::load8(delta + row * cols + (int64_t)g * 8, d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j] + d[j]));
+        Elem<__nv_bfloat16>::store8(h_out + row * cols + (int64_t)g * 8, v[i]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+    }
+  }
+  const float inv = rsqrtf(block_sum<kThreads>(ss, red) / static_cast<float>(cols) + eps);
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int g = threadIdx.x + i * kThreads;
+    if (g < groups) {
+      float wv[8];
+      Elem<__nv_bfloat16>::load8(w + (int64_t)g * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j] * inv * wv[j]));
+        amax = fmaxf(amax, fabsf(v[i][j]));
+      }
+    }
+  }
+  // block max (values are >= 0): reuse the sum scratch
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = (threadIdx.x & 31) < kThreads / 32 ? red[threadIdx.x & 31] : 0.0f;
+  amax = warp_max(amax);
+  const float scale = fp8_scale_from_amax(amax);
+  if (threadIdx.x == 0) scales[row] = scale;
+  const float y = b200q_rcp_rn(scale);
+  const bool fast = b200q_div_fast_ok(scale);
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int g = threadIdx.x + i * kThreads;
+    if (g < groups) {
+      float q[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q[j] = fast ? b200q_div_by_shared(v[i][j], scale, y) : __fdiv_rn(v[i][j], scale);
+      const uint32_t lo = f32x2_to_e4m3x2(q[0], q[1]) | (f32x2_to_e4m3x2(q[2], q[3]) << 16);
+      const uint32_t hi = f32x2_to_e4m3x2(q[4], q[5]) | (f32x2_to_e4m3x2(q[6], q[7]) << 16);
+      *reinterpret_cast<uint2*>(codes + row * cols + (int64_t)g * 8) = make_uint2(lo, hi);
+    }
+  }
+}
+
 // act[t, j] = silu(gu[t, j]) * gu[t, F + j], gu is [T, 2F] (gate columns first)
 __global__ void __launch_bounds__(kThreads)
 silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int64_t rows, int64_t f) {
@@ -151,6 +225,29 @@ int b200q_rms_norm(const void* x, const void* weight, void* out, int64_t rows, i
   else if (items <= 2) rms_norm_kernel<2><<<grid, kThreads, 0, st>>>(xp, wp, yp, cols, eps);
   else if (items <= 4) rms_norm_kernel<4><<<grid, kThreads, 0, st>>>(xp, wp, yp, cols, eps);
   else rms_norm_kernel<0><<<grid, kThreads, 0, st>>>(xp, wp, yp, cols, eps);
+  return check_launch();
+}
+
+int b200q_add_rms_norm_fp8_quantize(const void* h, const void* delta, const void* weight, void* h_out, uint8_t* codes_out,
+                                    float* scales_out, int64_t rows, int64_t cols, float eps, b200q_stream_t stream) {
+  if (rows < 0 || cols < 0 || cols % 16 != 0 || rows > 0x7fffffffLL || cols > kThreads * 8 * 8) return B200Q_ERR_INVALID;
+  if (rows == 0 || cols == 0) return B200Q_OK;
+  if (h == nullptr || weight == nullptr || codes_out == nullptr || scales_out == nullptr) return B200Q_ERR_INVALID;
+  if (delta != nullptr && h_out == nullptr) return B200Q_ERR_INVALID;
+  if (!aligned(h, 16) || !aligned(weight, 16) || !aligned(codes_out, 8) || (delta != nullptr && (!aligned(delta, 16) || !aligned(h_out, 16))))
+    return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const auto* hp = static_cast<const __nv_bfloat16*>(h);
+  const auto* dp = static_cast<const __nv_bfloat16*>(delta);
+  const auto* wp = static_cast<const __nv_bfloat16*>(weight);
+  auto* op = static_cast<__nv_bfloat16*>(h_out);
+  const int items = static_cast<int>(((cols >> 3) + kThreads - 1) / kThreads);
+  dim3 grid(static_cast<unsigned>(rows));
+  if (items <= 1) add_norm_quant_kernel<1><<<grid, kThreads, 0, st>>>(hp, dp, wp, op, codes_out, scales_out, cols, eps);
+  else if (items <= 2) add_norm_quant_kernel<2><<<grid, kThreads, 0, st>>>(hp, dp, wp, op, codes_out, scales_out, cols, eps);
+  else if (items <= 4) add_norm_quant_kernel<4><<<grid, kThreads, 0, st>>>(hp, dp, wp, op, codes_out, scales_out, cols, eps);
+  else add_norm_quant_kernel<8><<<grid, kThreads, 0, st>>>(hp, dp, wp, op, codes_out, scales_out, cols, eps);
   return check_launch();
 }
 

@@ -92,14 +92,36 @@ class CudaBackend:
             return capi.fp8_quantize(w, capi.row_amax(w))
         return capi.nvfp4_quantize(w, capi.amax(w))
 
-    def linear(self, x: torch.Tensor, qw, amax: torch.Tensor | None = None) -> torch.Tensor:
-        """`amax`: calibrated (static) activation amax for NVFP4; None = measured on this input.
-        FP8 activations are always scaled per token inside the quantize kernel."""
+    def quantize(self, x: torch.Tensor, amax: torch.Tensor | None = None):
+        """Activation -> quantized operand of `matmul`.  `amax`: calibrated (static) tensor amax for
+        NVFP4, None = measured on this input; FP8 activations are scaled per token in the kernel."""
         if self.mode == "fp8":
-            xc, xs = capi.fp8_quantize(x, None)
-            return capi.fp8_gemm(xc, xs, qw[0], qw[1], None)
-        xc, xs, xg = capi.nvfp4_quantize(x, capi.amax(x) if amax is None else amax)
-        return capi.nvfp4_gemm(xc, xs, xg, qw[0], qw[1], qw[2], None)
+            return capi.fp8_quantize(x, None)
+        return capi.nvfp4_quantize(x, capi.amax(x) if amax is None else amax)
+
+    def matmul(self, xq, qw) -> torch.Tensor:
+        if self.mode == "fp8":
+            return capi.fp8_gemm(xq[0], xq[1], qw[0], qw[1], None)
+        return capi.nvfp4_gemm(xq[0], xq[1], xq[2], qw[0], qw[1], qw[2], None)
+
+    def linear(self, x: torch.Tensor, qw, amax: torch.Tensor | None = None) -> torch.Tensor:
+        return self.matmul(self.quantize(x, amax), qw)
+
+    def add_norm_quantize(self, h: torch.Tensor, delta, weight: torch.Tensor, eps: float, amax=None):
+        """(h + delta, quantized rms_norm(h + delta)).  FP8: one fused kernel; NVFP4: add, norm and
+        block quantize as separate kernels (the block quantize needs the tensor amax)."""
+        if self.mode == "fp8":
+            h_new, codes, scales = capi.add_rms_norm_fp8_quantize(h, delta, weight, eps)
+            return h_new, (codes, scales)
+        h_new = h if delta is None else capi.add(h, delta)
+        x = capi.rms_norm(h_new, weight, eps)
+        return h_new, self.quantize(x, amax)
+
+    def measure_norm_amax(self, h, delta, weight, eps):
+        if self.mode != "nvfp4":
+            return None
+        h_new = h if delta is None else capi.add(h, delta)
+        return capi.amax(capi.rms_norm(h_new, weight, eps))
 
     def measure_amax(self, x: torch.Tensor):
         return capi.amax(x) if self.mode == "nvfp4" else None
@@ -178,17 +200,26 @@ class DecoderLayer:
                 self.amax[name] = m if name not in self.amax else torch.maximum(self.amax[name], m)
         return self.amax.get(name)
 
-    def forward(self, h: torch.Tensor) -> torch.Tensor:
-        """h: [tokens, hidden] bf16."""
+    def _norm_amax(self, name: str, h, delta, weight):
+        if self.calibrating and hasattr(self.backend, "measure_norm_amax"):
+            m = self.backend.measure_norm_amax(h, delta, weight, self.cfg.eps)
+            if m is not None:
+                self.amax[name] = m if name not in self.amax else torch.maximum(self.amax[name], m)
+        return self.amax.get(name)
+
+    def forward(self, h: torch.Tensor, delta=None):
+        """h: [tokens, hidden] bf16 residual stream; `delta`: output of the previous row-parallel
+        linear that has not been added to h yet (the add is fused into the next norm).
+        Returns (h, delta) in the same form."""
         cfg, be, w = self.cfg, self.backend, self.world
-        x = be.rms_norm(h, self.norm1, cfg.eps)
-        qkv = be.linear(x, self.wqkv, self._amax("qkv", x))             # [T, (q + 2 kv) / W]
+        h, xq = be.add_norm_quantize(h, delta, self.norm1, cfg.eps, self._norm_amax("qkv", h, delta, self.norm1))
+        qkv = be.matmul(xq, self.wqkv)                                   # [T, (q + 2 kv) / W]
         q_local, kv_local = cfg.q_width // w, cfg.kv_width // w
         attn = be.expand_heads(qkv, q_local + kv_local, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
-        h = be.add(h, self.row_parallel(attn, self.wo, self._amax("o", attn)))
-        x = be.rms_norm(h, self.norm2, cfg.eps)
-        act = be.silu_mul(be.linear(x, self.wgu, self._amax("gate_up", x)))
-        return be.add(h, self.row_parallel(act, self.wdown, self._amax("down", act)))
+        delta = self.row_parallel(attn, self.wo, self._amax("o", attn))
+        h, xq = be.add_norm_quantize(h, delta, self.norm2, cfg.eps, self._norm_amax("gate_up", h, delta, self.norm2))
+        act = be.silu_mul(be.matmul(xq, self.wgu))
+        return h, self.row_parallel(act, self.wdown, self._amax("down", act))
 
 
 class DecoderStack:
@@ -227,9 +258,10 @@ class DecoderStack:
         h = h.reshape(-1, shape[-1])
         if micro_batches > 1 and self.world > 1 and h.is_cuda and h.shape[0] >= 2 * 128 * self.world:
             return self._forward_overlapped(h, micro_batches).view(shape)
+        delta = None
         for layer in self.layers:
-            h = layer.forward(h)
-        return h.view(shape)
+            h, delta = layer.forward(h, delta)
+        return self.backend.add(h, delta).view(shape)
 
     def _forward_overlapped(self, h: torch.Tensor, n: int) -> torch.Tensor:
         main = torch.cuda.current_stream()
@@ -240,11 +272,14 @@ class DecoderStack:
         parts = [h[i * step:min(rows, (i + 1) * step)] for i in range(n)]
         for st in self._streams:
             st.wait_stream(main)
+        deltas = [None] * n
         for layer in self.layers:
             for i, st in enumerate(self._streams):
                 with torch.cuda.stream(st):
-                    parts[i] = layer.forward(parts[i])
+                    parts[i], deltas[i] = layer.forward(parts[i], deltas[i])
         for i, st in enumerate(self._streams):
+            with torch.cuda.stream(st):
+                parts[i] = self.backend.add(parts[i], deltas[i])
             parts[i].record_stream(main)
             main.wait_stream(st)
         h.record_stream(self._streams[0])

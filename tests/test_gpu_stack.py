@@ -54,6 +54,32 @@ def test_glue_kernels(b200):
     assert torch.equal(out, v)
 
 
+@pytest.mark.parametrize("cols", [64, 4096, 8192, 12288])
+def test_fused_add_norm_quantize(b200, cols):
+    """h + delta, RMSNorm and per-token FP8 quantize in one kernel against the three separate
+    kernels (same rounding points: identical h, codes equal wherever the norm's fp32 sum order
+    does not flip a bf16 rounding) and against the oracle."""
+    capi = b200.capi
+    g = torch.Generator().manual_seed(cols)
+    h = torch.randn(37, cols, generator=g).bfloat16()
+    d = (torch.randn(37, cols, generator=g) * 0.3).bfloat16()
+    w = (1 + 0.1 * torch.randn(cols, generator=g)).bfloat16()
+    h_new, codes, scales = capi.add_rms_norm_fp8_quantize(h.cuda(), d.cuda(), w.cuda(), 1e-5)
+    h_ref = capi.add(h.cuda(), d.cuda())
+    assert torch.equal(h_new, h_ref)
+    c_ref, s_ref = capi.fp8_quantize(capi.rms_norm(h_ref, w.cuda(), 1e-5), None)
+    assert torch.allclose(scales, s_ref, rtol=1e-2)
+    assert (codes != c_ref).float().mean().item() < 2e-2
+    x_oracle = o.rms_norm_ref(h + d, w)
+    deq = capi.fp8_dequantize(codes, scales, torch.float32).cpu()
+    assert o.rel_l2(deq, x_oracle.float()) < 4e-2
+    # without a delta: h passes through untouched
+    h2, codes2, scales2 = capi.add_rms_norm_fp8_quantize(h.cuda(), None, w.cuda(), 1e-5)
+    assert h2.data_ptr() == h2.data_ptr() and torch.equal(h2.cpu(), h)
+    c3, s3 = capi.fp8_quantize(capi.rms_norm(h.cuda(), w.cuda(), 1e-5), None)
+    assert (codes2 != c3).float().mean().item() < 2e-2
+
+
 @pytest.mark.parametrize("mode", ["fp8", "nvfp4"])
 def test_stack_matches_oracle_single_gpu(b200, mode):
     from tensorrt_b200.stack import DecoderStack, StackConfig

@@ -31,6 +31,13 @@ class OracleBackend:
         y = o.fp8_linear_ref(x, w) if self.mode == "fp8" else o.nvfp4_linear_ref(x, w)
         return y.to(x.dtype)
 
+    def matmul(self, xq, w):
+        return self.linear(xq, w)
+
+    def add_norm_quantize(self, h, delta, w, eps, amax=None):
+        h_new = h if delta is None else h + delta
+        return h_new, self.o.rms_norm_ref(h_new, w, eps)
+
     def rms_norm(self, x, w, eps):
         return self.o.rms_norm_ref(x, w, eps)
 
