@@ -224,7 +224,10 @@ int b200q_expand_heads(const void* src, int64_t src_stride, int64_t src_col0, vo
                        int heads_out, int rep, int head_dim, b200q_stream_t stream);
 
 /* Tile width of the GEMM kernels: 0 = chosen per problem (default), 128 or 256 = forced
- * single-CTA tiles of 128 x bn, 512 = forced CTA-pair kernel (256 x 256 tiles, cta_group::2).
+ * single-CTA tiles of 128 x bn, 512 = forced CTA-pair kernel (256 x 256 tiles, cta_group::2),
+ * 1001 / 1002 / 1004 / 1008 = forced small-M kernel (weights on the tensor core's M side, K
+ * split over a cluster of 1 / 2 / 4 / 8 CTAs, partial tiles summed through distributed shared
+ * memory; chosen automatically for M <= 128, ignored for larger M).
  * Process-wide tuning knob; results do not depend on it beyond fp32 summation order. */
 int b200q_gemm_set_tile_n(int bn);
 

@@ -2,6 +2,7 @@
 // quantized GEMMs: the TMA descriptor encoder lookup, the device status word and the
 // tile-width override.
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 #include "gemm_host.cuh"
@@ -41,6 +42,14 @@ int* device_status_word() {
 
 int forced_bn() { return g_force_bn.load(); }
 
+int forced_smallm_stages() {
+  static const int v = [] {
+    const char* e = std::getenv("B200Q_SMALLM_STAGES");
+    return e != nullptr ? std::atoi(e) : 0;
+  }();
+  return v;
+}
+
 }  // namespace gemm
 }  // namespace b200q
 
@@ -49,7 +58,7 @@ using namespace b200q;
 extern "C" {
 
 int b200q_gemm_set_tile_n(int bn) {
-  if (bn != 0 && bn != 128 && bn != 256 && bn != 512) return B200Q_ERR_INVALID;
+  if (bn != 0 && bn != 128 && bn != 256 && bn != 512 && bn != 1001 && bn != 1002 && bn != 1004 && bn != 1008) return B200Q_ERR_INVALID;
   gemm::g_force_bn.store(bn);
   return B200Q_OK;
 }

@@ -4,6 +4,7 @@
 #include <cuda.h>
 
 #include "gemm_kernel_2cta.cuh"
+#include "gemm_kernel_splitk.cuh"
 
 namespace b200q {
 namespace gemm {
@@ -150,14 +151,90 @@ int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, c
   return B200Q_OK;
 }
 
+// Small-M kernel (M <= 128): operands swapped, one cluster of `splits` CTAs per tile of 128
+// weight rows.  Up to one CTA per SM the operand ring takes all of shared memory; beyond that
+// the ring is sized so that two CTAs share an SM, which lets one CTA's prologue and cluster
+// reduction overlap the other's weight stream and fits twice as many CTAs into a wave.
+// `stages` > 0 overrides the ring depth.
+template <bool NVF4>
+int launch_smallm(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, int splits, int stages) {
+  using C = SmallCfg<NVF4>;
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200Q_ERR_CUDA;
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(gemm_smallm_kernel<NVF4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess)
+      return B200Q_ERR_CUDA;
+    configured[dev] = true;
+  }
+  const int bt = ((p.M + 15) / 16) * 16;
+  const int tiles = (p.N + kSmallWRows - 1) / kSmallWRows;
+  const int most = C::max_stages(bt, kSmemLimit);
+  if (stages <= 0) {
+    stages = most;
+    if (tiles * splits > sm_count()) {
+      // two CTAs per SM: half of the SM's 228 KiB (1 KiB reserved per CTA) and, for NVFP4,
+      // half of the 512 tensor-memory columns (128 accumulator + 32 scale columns per stage)
+      stages = C::max_stages(bt, kSmallHalfSmem);
+      if (NVF4 && stages > 4) stages = 4;
+    }
+  }
+  if (stages > most) stages = most;
+  if (stages < 2) stages = 2;
+  CUtensorMap tw, tx;
+  if (int rc = make_operand_map(&tw, b, p.N, p.k_bytes, kSmallWRows)) return rc;
+  if (int rc = make_operand_map(&tx, a, p.M, p.k_bytes, bt)) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * splits));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(C::smem_bytes(bt, stages));
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(splits);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<NVF4>, tw, tx, p, splits, stages, bt) != cudaSuccess) {
+    cudaGetLastError();
+    return B200Q_ERR_CUDA;
+  }
+  return B200Q_OK;
+}
+
+// Cluster size of the small-M kernel.  Measured: one SM pulls about 60 bytes per nanosecond
+// through TMA whatever the ring depth, so about 110 streaming SMs are needed to saturate HBM;
+// the smallest power of two that reaches that many CTAs wins, larger clusters only add
+// reduction cost.
+inline int smallm_splits(int n_tiles, int k_tiles, int sms) {
+  const int want = (sms * 3) / 4;
+  int s = 1;
+  while (s < 8 && n_tiles * s < want && s * 2 <= k_tiles) s <<= 1;
+  return s;
+}
+
+int forced_smallm_stages();  // from the environment variable B200Q_SMALLM_STAGES (0 when unset)
+
 // Tile width: 256 when that still gives every SM a tile, else 128.  `force_bn` (128 / 256)
 // overrides the choice (used by tests to cover both instantiations); 512 forces the CTA-pair
 // kernel (256 x 256 tiles), which is otherwise used when there are at least sm_count/2 such tiles.
+// M <= 128 goes to the small-M kernel unless a tile width is forced.
 template <bool NVF4>
 int launch(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, int force_bn, const RsTargets* rs = nullptr) {
   p.status = device_status_word();
   if (p.status == nullptr) return B200Q_ERR_CUDA;
   int bn = force_bn;
+  const int k_tiles = (p.k_bytes + kBKBytes - 1) / kBKBytes;
+  if (rs == nullptr && p.M <= kBM) {
+    // small M: weights are streamed once; the swapped-operand cluster kernel handles it
+    // (1001 / 1002 / 1004 / 1008 force 1 / 2 / 4 / 8 CTAs per tile)
+    int splits = 0;
+    if (bn == 1001 || bn == 1002 || bn == 1004 || bn == 1008) splits = bn - 1000;
+    else if (bn == 0) splits = smallm_splits((p.N + kSmallWRows - 1) / kSmallWRows, k_tiles, sm_count());
+    if (splits >= 1 && splits <= k_tiles) return launch_smallm<NVF4>(a, b, p, st, splits, forced_smallm_stages());
+  }
+  if (bn >= 1000) bn = 0;
   const int64_t pair_tiles = static_cast<int64_t>((p.M + kPairM - 1) / kPairM) * ((p.N + kPairN - 1) / kPairN);
   // measured: the CTA-pair kernel wins for FP8 (2.9 vs 2.75 PFLOP/s at 8192^3); for NVFP4 the
   // single-CTA 128 x 256 tile is faster (3.45 vs 3.2), so it is only used there when forced

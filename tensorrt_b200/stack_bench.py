@@ -67,8 +67,23 @@ def run(args):
     if tp:
         hd = torch.randn(64, 1, cfg.hidden, generator=g).bfloat16().to(dev)
         dsteps = 20
-        dms = _fwd_time(lambda: stack(hd), dsteps, 3, world, bench)
-        decode = {"tokens_per_s": 64 * dsteps / (dms * 1e-3), "ms_per_step": dms / dsteps, "batch": 64,
+        decode_fn = lambda: stack(hd)  # noqa: E731
+        graphed = False
+        if world == 1:
+            # a decode step is ~400 short launches: replay it as one CUDA graph
+            for _ in range(2):
+                stack(hd)
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    stack(hd)
+            torch.cuda.current_stream().wait_stream(side)
+            decode_fn, graphed = graph.replay, True
+        dms = _fwd_time(decode_fn, dsteps, 3, world, bench)
+        decode = {"tokens_per_s": 64 * dsteps / (dms * 1e-3), "ms_per_step": dms / dsteps, "batch": 64, "cuda_graph": graphed,
                   "weight_bytes_per_rank": cfg.weights_per_layer() * cfg.layers // world,
                   "weight_stream_GBps_per_rank": cfg.weights_per_layer() * cfg.layers / world / (dms / dsteps * 1e-3) / 1e9}
 

@@ -78,6 +78,31 @@ def test_fp8_gemm(capi, M, N, K, bn):
     assert o.rel_l2(out.float(), ref) <= TOL
 
 
+SMALL_M = [(1, 4096, 4096), (16, 4096, 4096), (128, 4096, 14336), (64, 8192, 8192), (5, 520, 1040), (100, 384, 256), (33, 136, 4096)]
+
+
+@pytest.mark.parametrize("force", [0, 128, 1001, 1002, 1004, 1008])
+@pytest.mark.parametrize("M,N,K", SMALL_M)
+def test_small_m_split_k(capi, M, N, K, force):
+    """Decode-sized problems: swapped operands, K split over a CTA cluster, partials summed through
+    distributed shared memory; every forced cluster size, the automatic choice, and the
+    persistent 128-wide kernel on the same inputs."""
+    if force > 1000 and (K + 127) // 128 < force - 1000:
+        pytest.skip("fewer K tiles than splits")
+    x, w, b = _inputs(M, N, K, seed=7 + M + N + K)
+    (xc, xs, wc, ws), ref = _ref_fp8(x, w, b)
+    capi.set_gemm_tile_n(force)
+    out = capi.fp8_gemm(xc.cuda(), xs.reshape(-1).cuda(), wc.cuda(), ws.reshape(-1).cuda(), b.cuda())
+    torch.cuda.synchronize()
+    assert o.rel_l2(out.float(), ref) <= TOL
+    if K % 32 == 0:
+        xq, wq, ref4 = _ref_nvfp4(x, w, b)
+        out = capi.nvfp4_gemm(xq[0].cuda(), o.swizzle_scales(xq[1]).cuda(), xq[2].cuda(),
+                              wq[0].cuda(), o.swizzle_scales(wq[1]).cuda(), wq[2].cuda(), b.cuda())
+        torch.cuda.synchronize()
+        assert o.rel_l2(out.float(), ref4) <= TOL
+
+
 def test_fp8_gemm_per_tensor_scales_no_bias(capi):
     x, w, _ = _inputs(256, 512, 1024, seed=9, bias=False)
     xa, wa = x.float().abs().max(), w.float().abs().max()

@@ -51,6 +51,7 @@ def test_argument_validation_without_a_device(b200):
     assert lib.b200q_fp8_gemm(p, p, 3, p, p, 1, None, p, 4, 4, 64, None) == -1     # scale count
     assert lib.b200q_amax(p, 2, 64, p, None, 0, None) == -5                         # no workspace
     assert lib.b200q_gemm_set_tile_n(64) == -1
+    assert lib.b200q_gemm_set_tile_n(1003) == -1
     assert lib.b200q_gemm_set_tile_n(0) == 0
 
 
