@@ -384,6 +384,9 @@ def main():
     ap.add_argument("--micro-batches", type=int, default=2, dest="micro_batches",
                     help="tp_stack: token halves walking the layers on separate streams (all-reduce / GEMM overlap)")
     ap.add_argument("--fused", type=int, default=1, help="tp_stack: 1 = fused GEMM + peer-memory all-reduce, 0 = NCCL")
+    ap.add_argument("--sharded", type=int, default=1,
+                    help="tp_stack prefill: 1 = token-sharded residual stream (reduce-scatter + all-gather of FP8 codes), "
+                         "0 = all-reduce")
     ap.add_argument("--slabs", type=int, default=1, help="row slabs per row-parallel linear (all-reduce overlap) in tp_stack")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

@@ -198,6 +198,35 @@ int b200q_nvfp4_gemm_reduce_scatter(const uint8_t* a_codes, const uint8_t* a_sca
 int b200q_reduce_gather(const b200q_peers* peers, const void* bias, int64_t M, int64_t N, uint32_t epoch,
                         b200q_stream_t stream);
 
+/* Token-sharded residual stream (sequence-parallel form of the same TP plan,
+ * tools/llm/tensor_parallel_llama_llm.py:134-157): every rank keeps the residual rows it owns
+ * ([M/world, N] bf16) and the reduction of a row-parallel linear is fused with what follows it.
+ *   b200q_reduce_add_rms_norm_fp8_quantize_gather
+ *        after b200q_*_gemm_reduce_scatter: sum the partials of this rank's rows, add the bias,
+ *        h_shard += that (in place, bf16 rounding as b200q_add_rms_norm_fp8_quantize), RMSNorm
+ *        with `norm_weight`, per-token FP8 quantize, and store codes and scales into codes[r] /
+ *        scales[r] of EVERY rank: the gathered [M, N] operand of the next column-parallel GEMM.
+ *        Only the 1-byte codes cross NVLink.  N % 16 == 0, N <= 16384.
+ *   b200q_reduce_add_gather
+ *        the last step of a stack: out[r] rows of this rank = residual_shard + sum + bias.
+ * `b200q_gather_peers`: recv / flags as in b200q_peers; codes[r] = rank r's M * N bytes,
+ * scales[r] = rank r's M floats.  Same epoch and flag rules as b200q_reduce_gather (one counter
+ * for all three calls on a group). */
+typedef struct b200q_gather_peers {
+  int32_t rank;
+  int32_t world;
+  void* recv[8];
+  uint8_t* codes[8];
+  float* scales[8];
+  uint32_t* flags[8];
+} b200q_gather_peers;
+
+int b200q_reduce_add_rms_norm_fp8_quantize_gather(const b200q_gather_peers* peers, const void* bias, void* h_shard,
+                                                  const void* norm_weight, float eps, int64_t M, int64_t N,
+                                                  uint32_t epoch, b200q_stream_t stream);
+int b200q_reduce_add_gather(const b200q_peers* peers, const void* bias, const void* residual_shard, int64_t M,
+                            int64_t N, uint32_t epoch, b200q_stream_t stream);
+
 /* ------------------------------------------------------------------ glue of the decoder linear stack
  * The benchmark workloads wrap the quantized linears in a Llama-shaped decoder layer
  * (RMSNorm -> QKV -> attention replaced by identity on V -> O -> residual -> RMSNorm ->

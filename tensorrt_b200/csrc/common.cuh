@@ -186,6 +186,21 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Sum over the CTA (THREADS threads); `smem` holds THREADS / 32 floats and is free again on return.
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* smem) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float r = (lane < THREADS / 32) ? smem[lane] : 0.0f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  __syncthreads();
+  return r;
+}
+
 // fp8 scale from amax: amax / 448, zero -> 1 (true division, as the CPU restatement).
 __device__ __forceinline__ float fp8_scale_from_amax(float amax) {
   float s = __fdiv_rn(amax, kE4M3Max);

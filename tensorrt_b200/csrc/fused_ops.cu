@@ -8,20 +8,6 @@ namespace {
 
 constexpr int kThreads = 256;
 
-template <int THREADS>
-__device__ __forceinline__ float block_sum(float v, float* smem) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) smem[warp] = v;
-  __syncthreads();
-  float r = (lane < THREADS / 32) ? smem[lane] : 0.0f;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
-  __syncthreads();
-  return r;
-}
-
 // y = x * rsqrt(mean(x^2) + eps) * w, fp32 math, bf16 in/out; one CTA per row, the row stays
 // in registers (ITEMS groups of 8 per thread) or is re-read (ITEMS == 0).
 template <int ITEMS>

@@ -9,6 +9,7 @@
 //      16-byte peer stores; no TMA multicast, no multimem),
 //   C. tells every peer "your output rows from me are written" and waits for the same, so that
 //      when the kernel retires the local output is complete.
+// A runs as its own single-warp launch in front of the reduction (see exchange_flags_kernel).
 // Flags are 32-bit epoch numbers in each rank's flag words (2 * world + 1 words, zeroed once):
 // word s of rank r = "rank s finished phase A", word world + s = "... phase C", last word =
 // block ticket.  Every wait is bounded (2 s); a wait that gives up records it in the device
@@ -54,27 +55,31 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t* p, uint32_t epoch) {
   }
 }
 
+// Phase A on its own: one warp tells every peer "my partials are in your buffer" and waits for the
+// same from all peers.  It is a separate single-warp launch so that a rank that is still waiting
+// never keeps SM resources away from the GEMMs of another stream that its peers are waiting for.
+struct FlagPeers {
+  int rank, world;
+  uint32_t* flags[8];
+};
+
+__global__ void __launch_bounds__(32) exchange_flags_kernel(const FlagPeers fp, uint32_t epoch, int* status) {
+  if (threadIdx.x < fp.world) {
+    __threadfence_system();
+    st_release_sys(fp.flags[threadIdx.x] + fp.rank, epoch);
+    if (!wait_epoch(fp.flags[fp.rank] + threadIdx.x, epoch)) atomicCAS(status, 0, 21);
+  }
+}
+
 __global__ void __launch_bounds__(kThreads)
-reduce_gather_kernel(const Peers pr, const __nv_bfloat16* __restrict__ bias, int64_t rows_per, int64_t N, uint32_t epoch,
-                     int* status) {
-  __shared__ int s_ok;
+reduce_gather_kernel(const Peers pr, const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
+                     int64_t rows_per, int64_t N, uint32_t epoch, int* status) {
   __shared__ int s_last;
   const int W = pr.world;
   uint32_t* my_flags = pr.flags[pr.rank];
 
-  // ---- A: partials exchanged
-  if (blockIdx.x == 0 && threadIdx.x < W) {
-    __threadfence_system();
-    st_release_sys(pr.flags[threadIdx.x] + pr.rank, epoch);
-  }
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  if (threadIdx.x < W && !wait_epoch(my_flags + threadIdx.x, epoch)) {
-    s_ok = 0;
-    atomicCAS(status, 0, 21);
-  }
-  __syncthreads();
-  const bool ok = s_ok != 0;
+  // phase A ran as exchange_flags_kernel; a wait that gave up there (or earlier) skips the work
+  const bool ok = *reinterpret_cast<volatile int*>(status) == 0;
 
   // ---- B: reduce my rows, store to every rank
   if (ok) {
@@ -99,6 +104,14 @@ reduce_gather_kernel(const Peers pr, const __nv_bfloat16* __restrict__ bias, int
         Elem<__nv_bfloat16>::load8(bias + col, b);
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] += b[j];
+      }
+      if (residual != nullptr) {
+        // residual stream rows owned by this rank: out = bf16(h + bf16(sum + bias)), the same
+        // two roundings as a separate add after the reduction
+        float hres[8];
+        Elem<__nv_bfloat16>::load8(residual + g * 8, hres);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = hres[j] + __bfloat162float(__float2bfloat16_rn(acc[j]));
       }
       uint4 w;
       uint32_t* u = &w.x;
@@ -131,6 +144,133 @@ reduce_gather_kernel(const Peers pr, const __nv_bfloat16* __restrict__ bias, int
   }
 }
 
+// Token-sharded residual stream: the owner of a block of tokens reduces the partials, adds the
+// bias and the residual it keeps, applies RMSNorm, quantizes per token to FP8 E4M3 and stores
+// codes + scales into the gathered activation buffers of EVERY rank (8-byte peer stores), so
+// only 1 byte per element crosses NVLink on the way out and the bf16 residual never does.
+struct GatherPeers {
+  int rank, world;
+  const __nv_bfloat16* recv;      // this rank's receive buffer [world][rows_per][N]
+  uint8_t* codes[8];              // every rank's gathered FP8 codes [M][N]
+  float* scales[8];               // every rank's gathered per-token scales [M]
+  uint32_t* flags[8];
+};
+
+template <int ITEMS>
+__global__ void __launch_bounds__(kThreads)
+reduce_norm_quant_gather_kernel(const GatherPeers pr, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ h,
+                                const __nv_bfloat16* __restrict__ w, int64_t rows_per, int64_t N, float eps, uint32_t epoch,
+                                int* status) {
+  __shared__ int s_last;
+  __shared__ float red[kThreads / 32];
+  const int W = pr.world;
+  uint32_t* my_flags = pr.flags[pr.rank];
+
+  const bool ok = *reinterpret_cast<volatile int*>(status) == 0;
+
+  // ---- B: one token per block iteration
+  if (ok) {
+    const int groups = static_cast<int>(N >> 3);
+    const int64_t slot = rows_per * N;
+    for (int64_t row = blockIdx.x; row < rows_per; row += gridDim.x) {
+      float v[ITEMS][8];
+      float ss = 0.0f;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int g = threadIdx.x + i * kThreads;
+        if (g < groups) {
+          const int64_t off = row * N + static_cast<int64_t>(g) * 8;
+          float acc[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+          for (int s = 0; s < W; ++s) {
+            const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(pr.recv + s * slot + off));
+            float p[8];
+            Elem<__nv_bfloat16>::unpack(raw, p);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += p[j];
+          }
+          if (bias != nullptr) {
+            float b[8];
+            Elem<__nv_bfloat16>::load8(bias + static_cast<int64_t>(g) * 8, b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += b[j];
+          }
+          Elem<__nv_bfloat16>::load8(h + off, v[i]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j] + __bfloat162float(__float2bfloat16_rn(acc[j]))));
+            ss = fmaf(v[i][j], v[i][j], ss);
+          }
+          Elem<__nv_bfloat16>::store8(h + off, v[i]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+        }
+      }
+      const float inv = rsqrtf(block_sum<kThreads>(ss, red) / static_cast<float>(N) + eps);
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int g = threadIdx.x + i * kThreads;
+        if (g < groups) {
+          float wv[8];
+          Elem<__nv_bfloat16>::load8(w + static_cast<int64_t>(g) * 8, wv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j] * inv * wv[j]));
+            amax = fmaxf(amax, fabsf(v[i][j]));
+          }
+        }
+      }
+      __syncthreads();  // every thread has left block_sum's scratch
+      amax = warp_max(amax);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+      __syncthreads();
+      amax = (threadIdx.x & 31) < kThreads / 32 ? red[threadIdx.x & 31] : 0.0f;
+      amax = warp_max(amax);
+      __syncthreads();  // scratch free for the next token
+      const float scale = fp8_scale_from_amax(amax);
+      const int64_t grow = static_cast<int64_t>(pr.rank) * rows_per + row;
+      if (threadIdx.x < W) pr.scales[threadIdx.x][grow] = scale;
+      const float y = b200q_rcp_rn(scale);
+      const bool fast = b200q_div_fast_ok(scale);
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int g = threadIdx.x + i * kThreads;
+        if (g < groups) {
+          float q[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) q[j] = fast ? b200q_div_by_shared(v[i][j], scale, y) : __fdiv_rn(v[i][j], scale);
+          const uint32_t lo = f32x2_to_e4m3x2(q[0], q[1]) | (f32x2_to_e4m3x2(q[2], q[3]) << 16);
+          const uint32_t hi = f32x2_to_e4m3x2(q[4], q[5]) | (f32x2_to_e4m3x2(q[6], q[7]) << 16);
+          const uint2 packed = make_uint2(lo, hi);
+          for (int r = 0; r < W; ++r) *reinterpret_cast<uint2*>(pr.codes[r] + grow * N + static_cast<int64_t>(g) * 8) = packed;
+        }
+      }
+    }
+  }
+
+  // ---- C: gathered activations exchanged; the last block to finish signals and waits
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int t = atomicAdd(my_flags + 2 * W, 1u);
+    s_last = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) my_flags[2 * W] = 0u;  // re-arm the ticket
+    if (ok) {
+      if (threadIdx.x < W) {
+        __threadfence_system();
+        st_release_sys(pr.flags[threadIdx.x] + W + pr.rank, epoch);
+        if (!wait_epoch(my_flags + W + threadIdx.x, epoch)) atomicCAS(status, 0, 24);
+      }
+    }
+  }
+}
+
 }  // namespace
 }  // namespace b200q
 
@@ -138,7 +278,8 @@ using namespace b200q;
 
 extern "C" {
 
-int b200q_reduce_gather(const b200q_peers* peers, const void* bias, int64_t M, int64_t N, uint32_t epoch, b200q_stream_t stream) {
+static int reduce_gather_impl(const b200q_peers* peers, const void* bias, const void* residual, int64_t M, int64_t N, uint32_t epoch,
+                              b200q_stream_t stream) {
   if (peers == nullptr || M <= 0 || N <= 0 || N % 8 != 0) return B200Q_ERR_INVALID;
   const int W = peers->world;
   if (W < 1 || W > 8 || peers->rank < 0 || peers->rank >= W || M % (static_cast<int64_t>(W) * 128) != 0) return B200Q_ERR_INVALID;
@@ -152,6 +293,7 @@ int b200q_reduce_gather(const b200q_peers* peers, const void* bias, int64_t M, i
     pr.out[r] = static_cast<__nv_bfloat16*>(peers->out[r]);
     pr.flags[r] = peers->flags[r];
   }
+  if (residual != nullptr && !aligned(residual, 16)) return B200Q_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
   int* status = gemm::device_status_word();
   if (status == nullptr) return B200Q_ERR_CUDA;
@@ -160,8 +302,68 @@ int b200q_reduce_gather(const b200q_peers* peers, const void* bias, int64_t M, i
   int64_t blocks = (groups + kThreads - 1) / kThreads;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 4;
   if (blocks > cap) blocks = cap;
+  FlagPeers fp{};
+  fp.rank = pr.rank;
+  fp.world = W;
+  for (int r = 0; r < W; ++r) fp.flags[r] = pr.flags[r];
+  exchange_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(fp, epoch, status);
   reduce_gather_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      pr, static_cast<const __nv_bfloat16*>(bias), rows_per, N, epoch, status);
+      pr, static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(residual), rows_per, N, epoch, status);
+  return check_launch();
+}
+
+int b200q_reduce_gather(const b200q_peers* peers, const void* bias, int64_t M, int64_t N, uint32_t epoch, b200q_stream_t stream) {
+  return reduce_gather_impl(peers, bias, nullptr, M, N, epoch, stream);
+}
+
+int b200q_reduce_add_gather(const b200q_peers* peers, const void* bias, const void* residual_shard, int64_t M, int64_t N,
+                            uint32_t epoch, b200q_stream_t stream) {
+  if (residual_shard == nullptr) return B200Q_ERR_INVALID;
+  return reduce_gather_impl(peers, bias, residual_shard, M, N, epoch, stream);
+}
+
+int b200q_reduce_add_rms_norm_fp8_quantize_gather(const b200q_gather_peers* peers, const void* bias, void* h_shard,
+                                                  const void* norm_weight, float eps, int64_t M, int64_t N, uint32_t epoch,
+                                                  b200q_stream_t stream) {
+  if (peers == nullptr || h_shard == nullptr || norm_weight == nullptr || M <= 0 || N <= 0 || N % 16 != 0 || N > 16384)
+    return B200Q_ERR_INVALID;
+  const int W = peers->world;
+  if (W < 1 || W > 8 || peers->rank < 0 || peers->rank >= W || M % (static_cast<int64_t>(W) * 128) != 0) return B200Q_ERR_INVALID;
+  GatherPeers pr{};
+  pr.rank = peers->rank;
+  pr.world = W;
+  pr.recv = static_cast<const __nv_bfloat16*>(peers->recv[peers->rank]);
+  for (int r = 0; r < W; ++r) {
+    if (peers->recv[r] == nullptr || peers->codes[r] == nullptr || peers->scales[r] == nullptr || peers->flags[r] == nullptr)
+      return B200Q_ERR_INVALID;
+    if (!aligned(peers->recv[r], 16) || !aligned(peers->codes[r], 16) || !aligned(peers->scales[r], 4)) return B200Q_ERR_ALIGN;
+    pr.codes[r] = peers->codes[r];
+    pr.scales[r] = peers->scales[r];
+    pr.flags[r] = peers->flags[r];
+  }
+  if (!aligned(h_shard, 16) || !aligned(norm_weight, 16) || (bias != nullptr && !aligned(bias, 16))) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  int* status = gemm::device_status_word();
+  if (status == nullptr) return B200Q_ERR_CUDA;
+  const int64_t rows_per = M / W;
+  int64_t blocks = rows_per;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  if (blocks > cap) blocks = cap;
+  const int items = static_cast<int>(((N >> 3) + kThreads - 1) / kThreads);
+  const unsigned grid = static_cast<unsigned>(blocks);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
+  __nv_bfloat16* hp = static_cast<__nv_bfloat16*>(h_shard);
+  const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(norm_weight);
+  FlagPeers fp{};
+  fp.rank = pr.rank;
+  fp.world = W;
+  for (int r = 0; r < W; ++r) fp.flags[r] = pr.flags[r];
+  exchange_flags_kernel<<<1, 32, 0, st>>>(fp, epoch, status);
+  if (items <= 1) reduce_norm_quant_gather_kernel<1><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, status);
+  else if (items <= 2) reduce_norm_quant_gather_kernel<2><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, status);
+  else if (items <= 4) reduce_norm_quant_gather_kernel<4><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, status);
+  else reduce_norm_quant_gather_kernel<8><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, status);
   return check_launch();
 }
 

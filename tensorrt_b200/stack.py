@@ -11,6 +11,13 @@ sliced, partial outputs summed by `tensorrt::fused_nccl_all_reduce` semantics). 
 quantizes the activation slice it owns (per-token amax over the local slice for FP8, a
 tensor amax of the local slice for NVFP4).
 
+With `sharded=True` the residual stream itself is sharded by tokens (sequence-parallel form of
+the same plan): a row-parallel linear ends in a reduce-scatter instead of an all-reduce, the
+residual add + RMSNorm + quantize run on the T/W tokens a rank owns, and the column-parallel
+linear that follows starts with an all-gather of the *quantized* activations (1 byte per element
+plus one scale per token instead of 2 bytes).  Same arithmetic per token, half the bytes on
+NVLink and no replicated norm work.
+
 The numerical work is done by a `backend` object.  `CudaBackend` (the product) calls the b200q
 kernels through the C ABI; tests drive the same layer logic on CPU/gloo ranks with a backend
 built from the CPU oracle.
@@ -147,6 +154,49 @@ class AllReduce:
         return t
 
 
+class ShardedComm:
+    """Collectives of the token-sharded residual stream: reduce-scatter of row-parallel partial
+    outputs and all-gather of quantized activations, both along the token axis.  NCCL runs the
+    native collectives; gloo (CPU tests) has no reduce-scatter, so it reduces and slices."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.native = dist.get_backend(group) == "nccl"
+
+    def shard(self, t: torch.Tensor) -> torch.Tensor:
+        rows = t.shape[0] // self.world
+        return t[self.rank * rows:(self.rank + 1) * rows]
+
+    def reduce_scatter(self, part: torch.Tensor) -> torch.Tensor:
+        if part.shape[0] % self.world:
+            raise ValueError(f"{part.shape[0]} tokens do not divide over {self.world} ranks")
+        if self.native:
+            out = part.new_empty((part.shape[0] // self.world,) + tuple(part.shape[1:]))
+            dist.reduce_scatter_tensor(out, part, op=dist.ReduceOp.SUM, group=self.group)
+            return out
+        dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
+        return self.shard(part).contiguous()
+
+    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        t = t.contiguous()
+        if self.native:
+            out = t.new_empty((t.shape[0] * self.world,) + tuple(t.shape[1:]))
+            dist.all_gather_into_tensor(out, t, group=self.group)
+            return out
+        parts = [torch.empty_like(t) for _ in range(self.world)]
+        dist.all_gather(parts, t, group=self.group)
+        return torch.cat(parts, dim=0)
+
+    def all_gather_quantized(self, xq):
+        """Quantized activation (codes and per-token scales, every member indexed by token on
+        axis 0) of this rank's tokens -> the same for all tokens."""
+        if isinstance(xq, torch.Tensor):
+            return self.all_gather(xq)
+        return tuple(self.all_gather(t) for t in xq)
+
+
 class OverlappedRowParallel:
     """Row-parallel linear + all-reduce with the collective of slab i running on a side stream
     while the GEMM of slab i+1 runs on the compute stream (CUDA only)."""
@@ -222,6 +272,42 @@ class DecoderLayer:
         return h, self.row_parallel(act, self.wdown, self._amax("down", act))
 
 
+    def forward_sharded(self, h: torch.Tensor, delta, comm: ShardedComm):
+        """Same layer on a token-sharded residual stream: h, delta are [tokens / W, hidden]; the
+        row-parallel partial outputs are computed without their reduction (`partial_linear`) and
+        reduce-scattered, the quantized norm outputs are all-gathered."""
+        cfg, be, w = self.cfg, self.backend, self.world
+        if cfg.mode != "fp8":
+            raise ValueError("the token-sharded residual stream is implemented for FP8 stacks")
+        h, xq = be.add_norm_quantize(h, delta, self.norm1, cfg.eps)
+        qkv = be.matmul(comm.all_gather_quantized(xq), self.wqkv)
+        q_local, kv_local = cfg.q_width // w, cfg.kv_width // w
+        attn = be.expand_heads(qkv, q_local + kv_local, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
+        delta = comm.reduce_scatter(be.linear(attn, self.wo))
+        h, xq = be.add_norm_quantize(h, delta, self.norm2, cfg.eps)
+        act = be.silu_mul(be.matmul(comm.all_gather_quantized(xq), self.wgu))
+        return h, comm.reduce_scatter(be.linear(act, self.wdown))
+
+
+    def forward_fused_sharded(self, h: torch.Tensor, xq, rp, next_norm):
+        """Token-sharded layer on the fused peer-memory path (tp.FusedRowParallel, sharded): `h` is
+        this rank's residual rows (updated in place), `xq` the gathered quantized input of the QKV
+        linear.  Each row-parallel GEMM pushes its partial tiles to the owners; one kernel then
+        reduces, adds the residual, applies the following RMSNorm, quantizes and gathers.  Returns
+        the gathered quantized input of the next layer, or (next_norm None) the full bf16 output."""
+        cfg, be, w = self.cfg, self.backend, self.world
+        qkv = be.matmul(xq, self.wqkv)
+        q_local, kv_local = cfg.q_width // w, cfg.kv_width // w
+        attn = be.expand_heads(qkv, q_local + kv_local, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
+        rp.partials_to_owners(attn, self.wo)
+        xq = rp.reduce_norm_quantize(h, self.norm2, cfg.eps)
+        act = be.silu_mul(be.matmul(xq, self.wgu))
+        rp.partials_to_owners(act, self.wdown)
+        if next_norm is None:
+            return rp.reduce_add(h)
+        return rp.reduce_norm_quantize(h, next_norm, cfg.eps)
+
+
 class DecoderStack:
     """`layers` decoder layers sharing one TP group.  `weights` is an iterable of per-layer dicts
     of full (unsharded) bf16 weights; each is sharded, quantized and dropped."""
@@ -231,7 +317,9 @@ class DecoderStack:
         """`fused_rows` > 0: row-parallel linears use the fused GEMM + peer-memory all-reduce
         (tp.FusedRowParallel) for up to that many rows; other row counts use NCCL."""
         cfg.check(world)
-        self.cfg, self.rank, self.world = cfg, rank, world
+        self.cfg, self.rank, self.world, self.group = cfg, rank, world, group
+        self._comm = None
+        self._fused = None
         self.backend = backend or CudaBackend(cfg.mode)
         reduce = AllReduce(group) if world > 1 else None
         row_parallel = None
@@ -240,7 +328,9 @@ class DecoderStack:
 
             be = self.backend
             row_parallel = FusedRowParallel(cfg.mode, fused_rows, cfg.hidden, group,
-                                            fallback=lambda x, qw, amax=None: reduce(be.linear(x, qw, amax)))
+                                            fallback=lambda x, qw, amax=None: reduce(be.linear(x, qw, amax)),
+                                            sharded=cfg.mode == "fp8")
+            self._fused = row_parallel
         elif world > 1:
             if slabs > 1:
                 row_parallel = OverlappedRowParallel(self.backend, reduce, slabs)
@@ -250,40 +340,104 @@ class DecoderStack:
         self.layers = [DecoderLayer(cfg, shard_layer_weights(w, cfg, rank, world) if world > 1 else w, self.backend, world,
                                     row_parallel) for w in weights]
 
-    def forward(self, h: torch.Tensor, micro_batches: int = 1) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, micro_batches: int = 1, sharded: bool = False) -> torch.Tensor:
         """`micro_batches` = 2 (tensor-parallel, CUDA): the tokens are split in two halves that walk
-        the layers on two streams, so the all-reduce of one half runs while the other half's
-        GEMMs compute.  The result is the same as with one batch: every op is row-wise."""
+        the layers on two streams, so the collectives of one half run while the other half's
+        GEMMs compute.  The result is the same as with one batch: every op is row-wise.
+        `sharded`: token-sharded residual stream (reduce-scatter / all-gather of quantized
+        activations instead of all-reduce); needs the token count of every micro-batch to divide
+        by the TP size."""
         shape = h.shape
         h = h.reshape(-1, shape[-1])
+        sharded = sharded and self.world > 1
         if micro_batches > 1 and self.world > 1 and h.is_cuda and h.shape[0] >= 2 * 128 * self.world:
-            return self._forward_overlapped(h, micro_batches).view(shape)
-        delta = None
-        for layer in self.layers:
-            h, delta = layer.forward(h, delta)
-        return self.backend.add(h, delta).view(shape)
+            return self._forward_overlapped(h, micro_batches, sharded).view(shape)
+        return self._micro_batch(h, sharded).view(shape)
 
-    def _forward_overlapped(self, h: torch.Tensor, n: int) -> torch.Tensor:
+    def _micro_batch(self, h: torch.Tensor, sharded: bool) -> torch.Tensor:
+        """All layers over one batch of tokens on the current stream."""
+        if sharded and self._fused is not None and self._fused.usable(h.shape[0]):
+            return self._walk_fused_sharded(h).clone()
+        return self._finish(*self._walk(self._enter(h, sharded), None, sharded), sharded)
+
+    def _walk_fused_sharded(self, h: torch.Tensor) -> torch.Tensor:
+        comm, be, cfg = self._comm_obj(), self.backend, self.cfg
+        h = comm.shard(h).clone()                         # updated in place from here on
+        _, xq = be.add_norm_quantize(h, None, self.layers[0].norm1, cfg.eps)
+        xq = comm.all_gather_quantized(xq)
+        for i, layer in enumerate(self.layers):
+            nxt = self.layers[i + 1].norm1 if i + 1 < len(self.layers) else None
+            xq = layer.forward_fused_sharded(h, xq, self._fused, nxt)
+        return xq
+
+    # one micro-batch: enter (take this rank's tokens), walk the layers, finish (last residual add
+    # and, token-sharded, the all-gather of the bf16 result)
+    def _comm_obj(self) -> ShardedComm:
+        if self._comm is None:
+            self._comm = ShardedComm(self.group)
+        return self._comm
+
+    def _enter(self, h: torch.Tensor, sharded: bool) -> torch.Tensor:
+        if not sharded:
+            return h
+        if h.shape[0] % self.world:
+            raise ValueError(f"{h.shape[0]} tokens do not divide over {self.world} ranks")
+        return self._comm_obj().shard(h)
+
+    def _walk(self, h, delta, sharded: bool):
+        for layer in self.layers:
+            h, delta = layer.forward_sharded(h, delta, self._comm_obj()) if sharded else layer.forward(h, delta)
+        return h, delta
+
+    def _finish(self, h, delta, sharded: bool) -> torch.Tensor:
+        out = self.backend.add(h, delta)
+        return self._comm_obj().all_gather(out) if sharded else out
+
+    def _forward_overlapped(self, h: torch.Tensor, n: int, sharded: bool = False) -> torch.Tensor:
         main = torch.cuda.current_stream()
         if getattr(self, "_streams", None) is None or len(self._streams) != n:
             self._streams = [torch.cuda.Stream() for _ in range(n)]
         rows = h.shape[0]
         step = (rows // n + 127) // 128 * 128
-        parts = [h[i * step:min(rows, (i + 1) * step)] for i in range(n)]
+        chunks = [h[i * step:min(rows, (i + 1) * step)] for i in range(n)]
         for st in self._streams:
             st.wait_stream(main)
-        deltas = [None] * n
-        for layer in self.layers:
+        if sharded and self._fused is not None and all(self._fused.usable(c.shape[0]) for c in chunks):
+            parts = self._overlapped_fused_sharded(chunks)
+        else:
+            parts = [self._enter(c, sharded) for c in chunks]
+            deltas = [None] * n
+            comm = self._comm_obj() if sharded else None
+            for layer in self.layers:
+                for i, st in enumerate(self._streams):
+                    with torch.cuda.stream(st):
+                        if sharded:
+                            parts[i], deltas[i] = layer.forward_sharded(parts[i], deltas[i], comm)
+                        else:
+                            parts[i], deltas[i] = layer.forward(parts[i], deltas[i])
             for i, st in enumerate(self._streams):
                 with torch.cuda.stream(st):
-                    parts[i], deltas[i] = layer.forward(parts[i], deltas[i])
+                    parts[i] = self._finish(parts[i], deltas[i], sharded)
         for i, st in enumerate(self._streams):
-            with torch.cuda.stream(st):
-                parts[i] = self.backend.add(parts[i], deltas[i])
             parts[i].record_stream(main)
             main.wait_stream(st)
         h.record_stream(self._streams[0])
         return torch.cat(parts, dim=0)
+
+    def _overlapped_fused_sharded(self, chunks):
+        comm, be, cfg = self._comm_obj(), self.backend, self.cfg
+        hs, xqs = [None] * len(chunks), [None] * len(chunks)
+        for i, st in enumerate(self._streams):
+            with torch.cuda.stream(st):
+                hs[i] = comm.shard(chunks[i]).clone()
+                _, xq = be.add_norm_quantize(hs[i], None, self.layers[0].norm1, cfg.eps)
+                xqs[i] = comm.all_gather_quantized(xq)
+        for li, layer in enumerate(self.layers):
+            nxt = self.layers[li + 1].norm1 if li + 1 < len(self.layers) else None
+            for i, st in enumerate(self._streams):
+                with torch.cuda.stream(st):
+                    xqs[i] = layer.forward_fused_sharded(hs[i], xqs[i], self._fused, nxt)
+        return xqs
 
     __call__ = forward
 

@@ -51,13 +51,14 @@ def run(args):
 
     with bench.ClockSampler(local) as clocks:
         mb = args.micro_batches if world > 1 else 1
-        ms = _fwd_time(lambda: stack.forward(h, mb), steps, warmup, world, bench)
+        sharded = bool(world > 1 and args.sharded and cfg.mode == "fp8")
+        ms = _fwd_time(lambda: stack.forward(h, mb, sharded), steps, warmup, world, bench)
     status = capi.device_status()
     prefill_tps = tokens * steps / (ms * 1e-3)
 
     def e2e():
         x = h_host.to(dev, non_blocking=True)
-        y = stack.forward(x, args.micro_batches if world > 1 else 1)
+        y = stack.forward(x, args.micro_batches if world > 1 else 1, sharded)
         return float(y.float().abs().mean().item())  # device -> host read of a scalar of the result
 
     e2e_ms = _fwd_time(e2e, max(1, min(steps, 3)), 1, world, bench)
@@ -101,6 +102,7 @@ def run(args):
                                "attention core = identity on the V slice (kv heads repeated to the query width)"
                                + ("; activation amax calibrated once (static quantizer input)" if cfg.mode == "nvfp4" else ""),
                    "parallelism": f"tp{world}", "micro_batches": args.micro_batches if world > 1 else 1, "slabs": args.slabs if world > 1 else 1,
+                   "residual_stream": "token-sharded (reduce-scatter, norm + quantize on owned tokens, all-gather of FP8 codes)" if sharded else "replicated",
                    "row_parallel": ("fused GEMM reduce-scatter epilogue + peer-memory reduce/all-gather" if (world > 1 and args.fused)
                                     else ("NCCL all-reduce" if world > 1 else "none")),
                    "l2": "weights + activations per forward far exceed the 126 MB L2"},

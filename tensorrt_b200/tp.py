@@ -92,7 +92,9 @@ class FusedRowParallel:
     The returned tensor is a view of this rank's output buffer and is valid until the next call.
     """
 
-    def __init__(self, mode: str, max_rows: int, n_out: int, group=None, fallback=None):
+    def __init__(self, mode: str, max_rows: int, n_out: int, group=None, fallback=None, sharded: bool = False):
+        """`sharded`: also allocate the gathered-activation buffers of the token-sharded residual
+        stream (`partials_to_owners` / `reduce_norm_quantize` / `reduce_add`)."""
         import os
 
         # plain peer mappings are all this path needs; keep the allocator from also binding the
@@ -102,7 +104,7 @@ class FusedRowParallel:
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         if self.world > 8:
             raise ValueError("FusedRowParallel supports at most 8 ranks")
-        self.max_rows, self.n_out = max_rows, n_out
+        self.max_rows, self.n_out, self.sharded = max_rows, n_out, sharded
         # one set of peer buffers, flags and epoch counter per CUDA stream that calls in: calls on
         # different streams may overlap on the device and must not share them
         self._ctx: dict = {}
@@ -124,7 +126,10 @@ class FusedRowParallel:
         name = self.group.group_name
         nbytes = rows * self.n_out * 2
         bufs, ptrs = [], []
-        for size in (nbytes, nbytes, 4096):
+        sizes = [nbytes, nbytes, 4096]
+        if self.sharded:
+            sizes += [rows * self.n_out, rows * 4]           # gathered FP8 codes and per-token scales
+        for size in sizes:
             t = symm_mem.empty(size, dtype=torch.uint8, device=dev)
             t.zero_()
             h = symm_mem.rendezvous(t, name)
@@ -137,6 +142,12 @@ class FusedRowParallel:
         for r in range(self.world):
             peers.recv[r], peers.out[r], peers.flags[r] = ptrs[0][r], ptrs[1][r], ptrs[2][r]
         ctx = {"rows": rows, "bufs": bufs, "peers": peers, "ref": ctypes.byref(peers), "out": bufs[1][0], "epoch": 0}
+        if self.sharded:
+            gp = _lib.GatherPeers()
+            gp.rank, gp.world = self.rank, self.world
+            for r in range(self.world):
+                gp.recv[r], gp.flags[r], gp.codes[r], gp.scales[r] = ptrs[0][r], ptrs[2][r], ptrs[3][r], ptrs[4][r]
+            ctx.update(gather=gp, gather_ref=ctypes.byref(gp), codes=bufs[3][0], scales=bufs[4][0])
         self._ctx[key] = ctx
         return ctx
 
@@ -150,6 +161,20 @@ class FusedRowParallel:
             if self.fallback is None:
                 raise ValueError(f"{rows} rows: need a multiple of {self.world * 128} and at most {self.max_rows}")
             return self.fallback(x, qw, amax)
+        ctx = self._gemm_to_owners(x, qw, amax)
+        lib = load()
+        b = None if bias is None else bias.to(torch.bfloat16).contiguous()
+        check(lib.b200q_reduce_gather(ctx["ref"], None if b is None else b.data_ptr(), rows, n, ctx["epoch"],
+                                      torch.cuda.current_stream().cuda_stream), "b200q_reduce_gather")
+        return ctx["out"][: rows * n * 2].view(torch.bfloat16).view(rows, n)
+
+    def _gemm_to_owners(self, x: torch.Tensor, qw, amax=None):
+        """Quantize x, run the GEMM whose epilogue stores every partial tile into the receive buffer
+        of the rank owning those rows; opens a new epoch.  Returns the calling stream's context."""
+        from . import capi
+        from ._lib import check, load
+
+        rows, n = x.shape[0], self.n_out
         lib = load()
         ctx = self._context(rows)
         ref = ctx["ref"]
@@ -166,7 +191,48 @@ class FusedRowParallel:
                                                       qw[2].data_ptr(), ref, rows, n, k, stream),
                   "b200q_nvfp4_gemm_reduce_scatter")
         ctx["epoch"] += 1
+        ctx["pending_rows"] = rows
+        return ctx
+
+    # ---- token-sharded residual stream -------------------------------------------------
+    def usable(self, rows: int) -> bool:
+        return rows % (self.world * 128) == 0 and rows <= self.max_rows
+
+    def partials_to_owners(self, x: torch.Tensor, qw, amax=None) -> None:
+        """First half of a row-parallel linear: the partial outputs land at their owners; one of
+        `reduce_norm_quantize` / `reduce_add` must follow on the same stream."""
+        if not self.usable(x.shape[0]):
+            raise ValueError(f"{x.shape[0]} rows: need a multiple of {self.world * 128} and at most {self.max_rows}")
+        self._gemm_to_owners(x, qw, amax)
+
+    def reduce_norm_quantize(self, h_shard: torch.Tensor, norm_weight: torch.Tensor, eps: float, bias=None):
+        """Second half, fused with the start of the next layer: h_shard (this rank's residual rows,
+        updated in place) += reduced partials; returns the FP8 codes [rows, n] and per-token scales
+        [rows] of rms_norm(h) for ALL tokens (views of this rank's gathered buffers, valid until
+        the next call on this stream)."""
+        from ._lib import check, load
+
+        ctx = self._ctx[torch.cuda.current_stream().cuda_stream]
+        rows, n = ctx.pop("pending_rows"), self.n_out
+        if tuple(h_shard.shape) != (rows // self.world, n) or not h_shard.is_contiguous() or h_shard.dtype != torch.bfloat16:
+            raise ValueError(f"h_shard must be a contiguous bf16 [{rows // self.world}, {n}] tensor")
         b = None if bias is None else bias.to(torch.bfloat16).contiguous()
-        check(lib.b200q_reduce_gather(ref, None if b is None else b.data_ptr(), rows, n, ctx["epoch"], stream),
-              "b200q_reduce_gather")
+        w = norm_weight.to(torch.bfloat16).contiguous()
+        check(load().b200q_reduce_add_rms_norm_fp8_quantize_gather(
+            ctx["gather_ref"], None if b is None else b.data_ptr(), h_shard.data_ptr(), w.data_ptr(), float(eps), rows, n,
+            ctx["epoch"], torch.cuda.current_stream().cuda_stream), "b200q_reduce_add_rms_norm_fp8_quantize_gather")
+        return ctx["codes"][: rows * n].view(rows, n), ctx["scales"][: rows * 4].view(torch.float32)
+
+    def reduce_add(self, h_shard: torch.Tensor, bias=None) -> torch.Tensor:
+        """Second half at the end of a stack: the full [rows, n] bf16 result h + reduced partials on
+        every rank (a view of this rank's output buffer, valid until the next call)."""
+        from ._lib import check, load
+
+        ctx = self._ctx[torch.cuda.current_stream().cuda_stream]
+        rows, n = ctx.pop("pending_rows"), self.n_out
+        if tuple(h_shard.shape) != (rows // self.world, n) or not h_shard.is_contiguous() or h_shard.dtype != torch.bfloat16:
+            raise ValueError(f"h_shard must be a contiguous bf16 [{rows // self.world}, {n}] tensor")
+        b = None if bias is None else bias.to(torch.bfloat16).contiguous()
+        check(load().b200q_reduce_add_gather(ctx["ref"], None if b is None else b.data_ptr(), h_shard.data_ptr(), rows, n,
+                                             ctx["epoch"], torch.cuda.current_stream().cuda_stream), "b200q_reduce_add_gather")
         return ctx["out"][: rows * n * 2].view(torch.bfloat16).view(rows, n)

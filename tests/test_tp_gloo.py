@@ -100,6 +100,18 @@ def _worker_stack(rank, world, store_path, mode, out_path):
         ref_1 = o.decoder_layer_ref(ref_1, w, cfg.n_q, cfg.n_kv, cfg.head_dim, mode, world=1)
     assert torch.equal(y, ref_tp), o.rel_l2(y.float(), ref_tp.float())
     assert o.rel_l2(y.float(), ref_1.float()) < (3e-2 if mode == "fp8" else 1e-1)
+    if mode == "fp8":
+        # token-sharded residual stream: reduce-scatter + all-gather of the norm outputs; every
+        # token sees the same arithmetic as with the all-reduce
+        y_sharded = stack.forward(h, sharded=True)
+        assert torch.equal(y_sharded, ref_tp), o.rel_l2(y_sharded.float(), ref_tp.float())
+        try:
+            stack.forward(h[:, :7], sharded=True)       # 14 tokens over 2 ranks is fine, 2 x 7 ...
+            stack.forward(h[:1, :7], sharded=True)      # ... 7 tokens are not
+        except ValueError as e:
+            assert "do not divide" in str(e)
+        else:
+            raise AssertionError("ragged token count not rejected")
     if rank == 0:
         torch.save(y, out_path)
     dist.barrier()
