@@ -248,6 +248,11 @@ int b200q_add_rms_norm_fp8_quantize(const void* h, const void* delta, const void
                                     uint8_t* codes_out, float* scales_out, int64_t rows, int64_t cols,
                                     float eps, b200q_stream_t stream);
 int b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t f, b200q_stream_t stream);
+/* silu(gate) * up followed by the per-token FP8 quantize (b200q_fp8_quantize, dynamic per-row
+ * amax) in one pass: codes [rows, f] and scales [rows] equal those of the two separate calls,
+ * the bf16 activation is never written.  f % 8 == 0, f <= 32768. */
+int b200q_silu_mul_fp8_quantize(const void* gate_up, uint8_t* codes_out, float* scales_out, int64_t rows, int64_t f,
+                                b200q_stream_t stream);
 int b200q_add(const void* a, const void* b, void* out, int64_t n, b200q_stream_t stream);
 int b200q_expand_heads(const void* src, int64_t src_stride, int64_t src_col0, void* out, int64_t rows,
                        int heads_out, int rep, int head_dim, b200q_stream_t stream);

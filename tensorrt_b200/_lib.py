@@ -42,6 +42,7 @@ SIGNATURES = {
     "b200q_rms_norm": (_c.c_int, [_p, _p, _p, _i64, _i64, _c.c_float, _p]),
     "b200q_add_rms_norm_fp8_quantize": (_c.c_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _c.c_float, _p]),
     "b200q_silu_mul": (_c.c_int, [_p, _p, _i64, _i64, _p]),
+    "b200q_silu_mul_fp8_quantize": (_c.c_int, [_p, _p, _p, _i64, _i64, _p]),
     "b200q_add": (_c.c_int, [_p, _p, _p, _i64, _p]),
     "b200q_expand_heads": (_c.c_int, [_p, _i64, _i64, _p, _i64, _c.c_int, _c.c_int, _c.c_int, _p]),
     "b200q_gemm_set_tile_n": (_c.c_int, [_c.c_int]),

@@ -247,6 +247,21 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def silu_mul_fp8_quantize(gate_up: torch.Tensor):
+    """[T, 2F] (gate columns first) -> (FP8 codes [T, F], per-token scales [T]) of silu(gate) * up,
+    bit-identical to silu_mul followed by fp8_quantize(.., None)."""
+    _need_cuda(gate_up)
+    _bf16(gate_up)
+    gate_up = gate_up.contiguous()
+    rows, two_f = _rows_cols(gate_up)
+    codes = torch.empty(*gate_up.shape[:-1], two_f // 2, dtype=torch.uint8, device=gate_up.device)
+    scales = torch.empty(rows, dtype=torch.float32, device=gate_up.device)
+    with torch.cuda.device(gate_up.device):
+        check(load().b200q_silu_mul_fp8_quantize(gate_up.data_ptr(), codes.data_ptr(), scales.data_ptr(), rows, two_f // 2,
+                                                 _stream(gate_up)), "b200q_silu_mul_fp8_quantize")
+    return codes, scales
+
+
 def add(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     _need_cuda(a, b)
     _bf16(a, b)

@@ -153,6 +153,61 @@ silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict_
   }
 }
 
+// silu(gate) * up fused with the per-token FP8 quantize that feeds the down projection: the
+// bf16 activation [T, F] is never written.  One CTA per token; the row stays in registers as
+// packed bf16 (ITEMS groups of 8 per thread), rounded exactly as silu_mul_kernel stores it, so
+// codes and scales equal those of the two separate kernels.
+template <int ITEMS>
+__global__ void __launch_bounds__(kThreads)
+silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict__ codes, float* __restrict__ scales, int64_t f) {
+  __shared__ float red[kThreads / 32];
+  const int64_t row = blockIdx.x;
+  const int groups = static_cast<int>(f >> 3);
+  uint4 y[ITEMS];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int g = threadIdx.x + i * kThreads;
+    y[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (g < groups) {
+      float a[8], b[8];
+      Elem<__nv_bfloat16>::load8(gu + row * 2 * f + (int64_t)g * 8, a);
+      Elem<__nv_bfloat16>::load8(gu + row * 2 * f + f + (int64_t)g * 8, b);
+      uint32_t* u = &y[i].x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float o0 = a[2 * j] / (1.0f + __expf(-a[2 * j])) * b[2 * j];
+        const float o1 = a[2 * j + 1] / (1.0f + __expf(-a[2 * j + 1])) * b[2 * j + 1];
+        __nv_bfloat162 h = __floats2bfloat162_rn(o0, o1);
+        u[j] = *reinterpret_cast<uint32_t*>(&h);
+        amax = fmaxf(amax, fmaxf(fabsf(__low2float(h)), fabsf(__high2float(h))));
+      }
+    }
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = (threadIdx.x & 31) < kThreads / 32 ? red[threadIdx.x & 31] : 0.0f;
+  amax = warp_max(amax);
+  const float scale = fp8_scale_from_amax(amax);
+  if (threadIdx.x == 0) scales[row] = scale;
+  const float rcp = b200q_rcp_rn(scale);
+  const bool fast = b200q_div_fast_ok(scale);
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int g = threadIdx.x + i * kThreads;
+    if (g < groups) {
+      float v[8], q[8];
+      Elem<__nv_bfloat16>::unpack(y[i], v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q[j] = fast ? b200q_div_by_shared(v[j], scale, rcp) : __fdiv_rn(v[j], scale);
+      const uint32_t lo = f32x2_to_e4m3x2(q[0], q[1]) | (f32x2_to_e4m3x2(q[2], q[3]) << 16);
+      const uint32_t hi = f32x2_to_e4m3x2(q[4], q[5]) | (f32x2_to_e4m3x2(q[6], q[7]) << 16);
+      *reinterpret_cast<uint2*>(codes + row * f + (int64_t)g * 8) = make_uint2(lo, hi);
+    }
+  }
+}
+
 // out = a + b (bf16, fp32 add)
 __global__ void __launch_bounds__(kThreads)
 add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ out, int64_t n) {
@@ -245,6 +300,25 @@ int b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t f, b200
   if (int rc = check_arch()) return rc;
   silu_mul_kernel<<<grid_for(rows * (f >> 3)), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, f);
+  return check_launch();
+}
+
+int b200q_silu_mul_fp8_quantize(const void* gate_up, uint8_t* codes_out, float* scales_out, int64_t rows, int64_t f,
+                                b200q_stream_t stream) {
+  if (rows < 0 || f < 0 || f % 8 != 0 || rows > 0x7fffffffLL || f > kThreads * 8 * 16) return B200Q_ERR_INVALID;
+  if (rows == 0 || f == 0) return B200Q_OK;
+  if (gate_up == nullptr || codes_out == nullptr || scales_out == nullptr) return B200Q_ERR_INVALID;
+  if (!aligned(gate_up, 16) || !aligned(codes_out, 8)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const auto* gp = static_cast<const __nv_bfloat16*>(gate_up);
+  const int items = static_cast<int>(((f >> 3) + kThreads - 1) / kThreads);
+  dim3 grid(static_cast<unsigned>(rows));
+  if (items <= 1) silu_mul_quant_kernel<1><<<grid, kThreads, 0, st>>>(gp, codes_out, scales_out, f);
+  else if (items <= 2) silu_mul_quant_kernel<2><<<grid, kThreads, 0, st>>>(gp, codes_out, scales_out, f);
+  else if (items <= 4) silu_mul_quant_kernel<4><<<grid, kThreads, 0, st>>>(gp, codes_out, scales_out, f);
+  else if (items <= 8) silu_mul_quant_kernel<8><<<grid, kThreads, 0, st>>>(gp, codes_out, scales_out, f);
+  else silu_mul_quant_kernel<16><<<grid, kThreads, 0, st>>>(gp, codes_out, scales_out, f);
   return check_launch();
 }
 

@@ -1,0 +1,140 @@
+"""FX rewrite: Q/DQ-wrapped linears -> real-quant GEMM nodes.
+
+The reference keeps `linear(input_quantizer(x), weight_quantizer(W), bias)` as three nodes
+(`tensorrt::quantize_op` / `tensorrt::dynamic_block_quantize_op` twice, then `aten.linear`;
+converters at py/torch_tensorrt/dynamo/conversion/aten_ops_converters.py:904-960 and :4197-4213)
+and relies on TensorRT to fuse the Q/DQ pairs into an FP8/FP4 GEMM.  `fuse_quantized_linear`
+does that fusion on the graph itself:
+
+    xq = quantize_op(x, ax, 8, 4, False, False)
+    wq = quantize_op(W, aw, 8, 4, False, False)          ==>   xc, xs = b200_fp8_quantize(x, ax)
+    y  = linear(xq, wq, b)                                     wc, ws = b200_fp8_quantize(W, aw)
+                                                               y = b200_fp8_gemm(xc, xs, wc, ws, b)
+
+and the same with `dynamic_block_quantize_op(.., 16, amax, 4, 2, 8, 4)` -> `b200_nvfp4_*`.
+The fake-quantized bf16 tensors are never materialised; the result differs from the unfused
+graph only by the GEMM's accumulation (fp32 over code products instead of bf16 operands).
+A weight that is a constant of the graph module on a CUDA device is quantized once at rewrite
+time and replaced by its codes and scales (`fold_weights=True`).
+
+The rewritten nodes are `torch.ops.tensorrt.b200_*` dispatcher ops with Meta kernels, so the
+graph still traces under FakeTensorMode and each node can be handed to
+`torch_tensorrt.dynamo.conversion.plugins.custom_op` (see plugin.register_with_torch_tensorrt).
+"""
+from __future__ import annotations
+
+import operator
+
+import torch
+from torch import fx
+
+_FP8_ARGS = (8, 4)          # num_bits, exponent_bits of quantize_op for E4M3
+_NVFP4_ARGS = (16, 4, 2, 8, 4)  # block_size, num_bits, exponent_bits, scale_num_bits, scale_exponent_bits
+
+
+def _is_op(node: fx.Node, packet) -> bool:
+    if node.op != "call_function":
+        return False
+    t = node.target
+    return t is packet or t is getattr(packet, "default", None)
+
+
+def _linear_targets():
+    return (torch.nn.functional.linear, torch.ops.aten.linear, torch.ops.aten.linear.default)
+
+
+def _match_fp8(node: fx.Node):
+    """quantize_op(input, amax, 8, 4, unsigned=False, narrow_range=False) -> (input, amax)."""
+    if not _is_op(node, torch.ops.tensorrt.quantize_op) or len(node.args) < 4:
+        return None
+    if tuple(node.args[2:4]) != _FP8_ARGS:
+        return None
+    return node.args[0], node.args[1]
+
+
+def _match_nvfp4(node: fx.Node):
+    """dynamic_block_quantize_op(input, 16, amax, 4, 2, 8, 4) -> (input, amax)."""
+    if not _is_op(node, torch.ops.tensorrt.dynamic_block_quantize_op) or len(node.args) < 7:
+        return None
+    if (node.args[1],) + tuple(node.args[3:7]) != _NVFP4_ARGS:
+        return None
+    return node.args[0], node.args[2]
+
+
+def _const_tensor(gm: fx.GraphModule, node):
+    """Tensor behind a get_attr node, else None."""
+    if not isinstance(node, fx.Node) or node.op != "get_attr":
+        return None
+    obj = gm
+    for part in node.target.split("."):
+        obj = getattr(obj, part, None)
+        if obj is None:
+            return None
+    return obj if isinstance(obj, torch.Tensor) else None
+
+
+def _out_dtype(node: fx.Node):
+    val = node.meta.get("val")
+    if isinstance(val, torch.Tensor):
+        return val.dtype
+    tm = node.meta.get("tensor_meta")
+    return getattr(tm, "dtype", None)
+
+
+def fuse_quantized_linear(gm: fx.GraphModule, fold_weights: bool = True) -> int:
+    """Rewrite every linear whose input and weight both come from matching FP8 (or both from
+    NVFP4) quantize ops.  Returns the number of linears rewritten; the module is recompiled
+    in place.  Quantize nodes left without users are removed; a quantize node that still feeds
+    something else is kept for that user."""
+    from . import ops
+
+    ops.load_ops()
+    t = torch.ops.tensorrt
+    graph, n_fused, n_const = gm.graph, 0, 0
+    for node in list(graph.nodes):
+        if node.op != "call_function" or node.target not in _linear_targets() or len(node.args) < 2:
+            continue
+        xq, wq = node.args[0], node.args[1]
+        bias = node.args[2] if len(node.args) > 2 else node.kwargs.get("bias")
+        if not isinstance(xq, fx.Node) or not isinstance(wq, fx.Node):
+            continue
+        mode, mx, mw = "fp8", _match_fp8(xq), _match_fp8(wq)
+        if mx is None or mw is None:
+            mode, mx, mw = "nvfp4", _match_nvfp4(xq), _match_nvfp4(wq)
+        if mx is None or mw is None:
+            continue
+        quant = t.b200_fp8_quantize.default if mode == "fp8" else t.b200_nvfp4_quantize.default
+        gemm = t.b200_fp8_gemm.default if mode == "fp8" else t.b200_nvfp4_gemm.default
+        parts = 2 if mode == "fp8" else 3
+        with graph.inserting_before(node):
+            xs = graph.call_function(quant, (mx[0], mx[1]))
+            x_parts = [graph.call_function(operator.getitem, (xs, i)) for i in range(parts)]
+            w_const, a_const = _const_tensor(gm, mw[0]), _const_tensor(gm, mw[1])
+            if fold_weights and w_const is not None and a_const is not None and w_const.is_cuda:
+                with torch.no_grad():
+                    folded = quant(w_const.detach(), a_const.detach().to(w_const.device))
+                w_parts = []
+                for i, tensor in enumerate(folded):
+                    name = f"_b200q_w{n_const}_{i}"
+                    gm.register_buffer(name, tensor)
+                    w_parts.append(graph.get_attr(name))
+                n_const += 1
+            else:
+                ws = graph.call_function(quant, (mw[0], mw[1]))
+                w_parts = [graph.call_function(operator.getitem, (ws, i)) for i in range(parts)]
+            out = graph.call_function(gemm, (*x_parts, *w_parts, bias))
+            dtype = _out_dtype(node)
+            if dtype is not None and dtype != torch.bfloat16:
+                out = graph.call_method("to", (out, dtype))
+        out.meta.update({k: v for k, v in node.meta.items() if k in ("val", "tensor_meta")})
+        node.replace_all_uses_with(out)
+        graph.erase_node(node)
+        for q in (xq, wq):
+            if not q.users:
+                graph.erase_node(q)
+        n_fused += 1
+    if n_fused:
+        graph.eliminate_dead_code()
+        graph.lint()
+        gm.recompile()
+    return n_fused

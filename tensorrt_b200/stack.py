@@ -111,8 +111,16 @@ class CudaBackend:
             return capi.fp8_gemm(xq[0], xq[1], qw[0], qw[1], None)
         return capi.nvfp4_gemm(xq[0], xq[1], xq[2], qw[0], qw[1], qw[2], None)
 
-    def linear(self, x: torch.Tensor, qw, amax: torch.Tensor | None = None) -> torch.Tensor:
-        return self.matmul(self.quantize(x, amax), qw)
+    def linear(self, x, qw, amax: torch.Tensor | None = None) -> torch.Tensor:
+        """`x`: bf16 activation, or an already quantized operand (tuple, as `quantize` returns)."""
+        return self.matmul(x if isinstance(x, tuple) else self.quantize(x, amax), qw)
+
+    def silu_mul_quantize(self, gate_up: torch.Tensor):
+        """silu(gate) * up as the quantized operand of the down projection (one kernel), or None
+        when the mode has no fused form (NVFP4 block quantize needs the tensor amax first)."""
+        if self.mode != "fp8":
+            return None
+        return capi.silu_mul_fp8_quantize(gate_up)
 
     def add_norm_quantize(self, h: torch.Tensor, delta, weight: torch.Tensor, eps: float, amax=None):
         """(h + delta, quantized rms_norm(h + delta)).  FP8: one fused kernel; NVFP4: add, norm and
@@ -205,10 +213,11 @@ class OverlappedRowParallel:
         self.backend, self.reduce, self.slabs = backend, reduce, max(1, slabs)
         self.comm_stream = torch.cuda.Stream() if torch.cuda.is_available() and reduce.world > 1 else None
 
-    def __call__(self, x: torch.Tensor, qw, amax=None) -> torch.Tensor:
+    def __call__(self, x, qw, amax=None) -> torch.Tensor:
         if self.reduce.world == 1:
             return self.backend.linear(x, qw, amax)
-        rows = x.shape[0]
+        quantized = isinstance(x, tuple)                  # (codes, per-token scales): slice both by token
+        rows = x[0].shape[0] if quantized else x.shape[0]
         slabs = min(self.slabs, max(1, rows // 128))
         if slabs == 1 or self.comm_stream is None:
             return self.reduce(self.backend.linear(x, qw, amax))
@@ -216,7 +225,8 @@ class OverlappedRowParallel:
         outs = []
         main = torch.cuda.current_stream()
         for i in range(slabs):
-            part = self.backend.linear(x[bounds[i]:bounds[i + 1]], qw, amax)
+            rows_i = slice(bounds[i], bounds[i + 1])
+            part = self.backend.linear(tuple(t[rows_i] for t in x) if quantized else x[rows_i], qw, amax)
             ev = torch.cuda.Event()
             ev.record(main)
             with torch.cuda.stream(self.comm_stream):
@@ -243,7 +253,9 @@ class DecoderLayer:
         self.amax: dict = {}
         self.calibrating = False
 
-    def _amax(self, name: str, x: torch.Tensor):
+    def _amax(self, name: str, x):
+        if isinstance(x, tuple):
+            return None                                   # already quantized (per-token dynamic scales)
         if self.calibrating and hasattr(self.backend, "measure_amax"):
             m = self.backend.measure_amax(x)
             if m is not None:
@@ -257,6 +269,14 @@ class DecoderLayer:
                 self.amax[name] = m if name not in self.amax else torch.maximum(self.amax[name], m)
         return self.amax.get(name)
 
+    def _ffn_act(self, xq):
+        """gate/up linear + silu(gate) * up -> input of the down projection (quantized when the
+        backend fuses the quantize, else bf16)."""
+        be = self.backend
+        gu = be.matmul(xq, self.wgu)
+        act = be.silu_mul_quantize(gu) if hasattr(be, "silu_mul_quantize") and not self.calibrating else None
+        return be.silu_mul(gu) if act is None else act
+
     def forward(self, h: torch.Tensor, delta=None):
         """h: [tokens, hidden] bf16 residual stream; `delta`: output of the previous row-parallel
         linear that has not been added to h yet (the add is fused into the next norm).
@@ -268,7 +288,7 @@ class DecoderLayer:
         attn = be.expand_heads(qkv, q_local + kv_local, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
         delta = self.row_parallel(attn, self.wo, self._amax("o", attn))
         h, xq = be.add_norm_quantize(h, delta, self.norm2, cfg.eps, self._norm_amax("gate_up", h, delta, self.norm2))
-        act = be.silu_mul(be.matmul(xq, self.wgu))
+        act = self._ffn_act(xq)
         return h, self.row_parallel(act, self.wdown, self._amax("down", act))
 
 
@@ -285,7 +305,7 @@ class DecoderLayer:
         attn = be.expand_heads(qkv, q_local + kv_local, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
         delta = comm.reduce_scatter(be.linear(attn, self.wo))
         h, xq = be.add_norm_quantize(h, delta, self.norm2, cfg.eps)
-        act = be.silu_mul(be.matmul(comm.all_gather_quantized(xq), self.wgu))
+        act = self._ffn_act(comm.all_gather_quantized(xq))
         return h, comm.reduce_scatter(be.linear(act, self.wdown))
 
 
@@ -301,8 +321,7 @@ class DecoderLayer:
         attn = be.expand_heads(qkv, q_local + kv_local, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
         rp.partials_to_owners(attn, self.wo)
         xq = rp.reduce_norm_quantize(h, self.norm2, cfg.eps)
-        act = be.silu_mul(be.matmul(xq, self.wgu))
-        rp.partials_to_owners(act, self.wdown)
+        rp.partials_to_owners(self._ffn_act(xq), self.wdown)
         if next_norm is None:
             return rp.reduce_add(h)
         return rp.reduce_norm_quantize(h, next_norm, cfg.eps)

@@ -151,11 +151,12 @@ class FusedRowParallel:
         self._ctx[key] = ctx
         return ctx
 
-    def __call__(self, x: torch.Tensor, qw, amax=None, bias=None) -> torch.Tensor:
-        from . import capi
+    def __call__(self, x, qw, amax=None, bias=None) -> torch.Tensor:
+        """`x`: bf16 activation [rows, K/world] or an already quantized operand (FP8: (codes,
+        per-token scales))."""
         from ._lib import check, load
 
-        rows = x.shape[0]
+        rows = x[0].shape[0] if isinstance(x, tuple) else x.shape[0]
         n = self.n_out
         if rows % (self.world * 128) or rows > self.max_rows:
             if self.fallback is None:
@@ -168,24 +169,24 @@ class FusedRowParallel:
                                       torch.cuda.current_stream().cuda_stream), "b200q_reduce_gather")
         return ctx["out"][: rows * n * 2].view(torch.bfloat16).view(rows, n)
 
-    def _gemm_to_owners(self, x: torch.Tensor, qw, amax=None):
+    def _gemm_to_owners(self, x, qw, amax=None):
         """Quantize x, run the GEMM whose epilogue stores every partial tile into the receive buffer
         of the rank owning those rows; opens a new epoch.  Returns the calling stream's context."""
         from . import capi
         from ._lib import check, load
 
-        rows, n = x.shape[0], self.n_out
+        rows, n = (x[0].shape[0] if isinstance(x, tuple) else x.shape[0]), self.n_out
         lib = load()
         ctx = self._context(rows)
         ref = ctx["ref"]
         stream = torch.cuda.current_stream().cuda_stream
         if self.mode == "fp8":
-            xc, xs = capi.fp8_quantize(x, None)
+            xc, xs = x if isinstance(x, tuple) else capi.fp8_quantize(x, None)
             k = xc.shape[1]
             check(lib.b200q_fp8_gemm_reduce_scatter(xc.data_ptr(), xs.data_ptr(), xs.numel(), qw[0].data_ptr(), qw[1].data_ptr(),
                                                     qw[1].numel(), ref, rows, n, k, stream), "b200q_fp8_gemm_reduce_scatter")
         else:
-            xc, xs, xg = capi.nvfp4_quantize(x, capi.amax(x) if amax is None else amax)
+            xc, xs, xg = x if isinstance(x, tuple) else capi.nvfp4_quantize(x, capi.amax(x) if amax is None else amax)
             k = xc.shape[1] * 2
             check(lib.b200q_nvfp4_gemm_reduce_scatter(xc.data_ptr(), xs.data_ptr(), xg.data_ptr(), qw[0].data_ptr(), qw[1].data_ptr(),
                                                       qw[2].data_ptr(), ref, rows, n, k, stream),
@@ -198,11 +199,12 @@ class FusedRowParallel:
     def usable(self, rows: int) -> bool:
         return rows % (self.world * 128) == 0 and rows <= self.max_rows
 
-    def partials_to_owners(self, x: torch.Tensor, qw, amax=None) -> None:
+    def partials_to_owners(self, x, qw, amax=None) -> None:
         """First half of a row-parallel linear: the partial outputs land at their owners; one of
         `reduce_norm_quantize` / `reduce_add` must follow on the same stream."""
-        if not self.usable(x.shape[0]):
-            raise ValueError(f"{x.shape[0]} rows: need a multiple of {self.world * 128} and at most {self.max_rows}")
+        rows = x[0].shape[0] if isinstance(x, tuple) else x.shape[0]
+        if not self.usable(rows):
+            raise ValueError(f"{rows} rows: need a multiple of {self.world * 128} and at most {self.max_rows}")
         self._gemm_to_owners(x, qw, amax)
 
     def reduce_norm_quantize(self, h_shard: torch.Tensor, norm_weight: torch.Tensor, eps: float, bias=None):

@@ -1,0 +1,154 @@
+"""FX rewrite of Q/DQ-wrapped linears (tensorrt_b200/fx_passes.py): graph structure and shape
+propagation on CPU (meta tensors), numerics against the unfused graph on the GPU."""
+import pytest
+import torch
+
+import oracle as o
+
+
+class QdqLinear(torch.nn.Module):
+    """linear(input_quantizer(x), weight_quantizer(W), b) as the reference's calibrated modules
+    call it (FP8: quantize_op; NVFP4: dynamic_block_quantize_op)."""
+
+    def __init__(self, n, k, mode="fp8", bias=True, seed=0, dtype=torch.bfloat16):
+        super().__init__()
+        g = torch.Generator().manual_seed(seed)
+        self.mode = mode
+        self.weight = torch.nn.Parameter((torch.randn(n, k, generator=g) * 0.02).to(dtype))
+        self.bias = torch.nn.Parameter((torch.randn(n, generator=g) * 0.01).to(dtype)) if bias else None
+        self.register_buffer("x_amax", torch.tensor(4.0))
+        self.register_buffer("w_amax", self.weight.detach().float().abs().max())
+
+    def q(self, t, amax):
+        if self.mode == "fp8":
+            return torch.ops.tensorrt.quantize_op(t, amax, 8, 4, False, False)
+        return torch.ops.tensorrt.dynamic_block_quantize_op(t, 16, amax, 4, 2, 8, 4)
+
+    def forward(self, x):
+        return torch.nn.functional.linear(self.q(x, self.x_amax), self.q(self.weight, self.w_amax), self.bias)
+
+
+class TwoLayer(torch.nn.Module):
+    def __init__(self, mode):
+        super().__init__()
+        self.a, self.b = QdqLinear(64, 32, mode, seed=1), QdqLinear(48, 64, mode, bias=False, seed=2)
+
+    def forward(self, x):
+        return self.b(torch.nn.functional.silu(self.a(x)))
+
+
+def _targets(gm):
+    return [str(n.target) for n in gm.graph.nodes if n.op == "call_function"]
+
+
+@pytest.mark.parametrize("mode", ["fp8", "nvfp4"])
+@pytest.mark.parametrize("how", ["trace", "export"])
+def test_rewrite_structure_and_meta_shapes(b200, mode, how):
+    from tensorrt_b200.fx_passes import fuse_quantized_linear
+
+    m = TwoLayer(mode)
+    if how == "trace":
+        gm = torch.fx.symbolic_trace(m)
+    else:
+        gm = torch.export.export(m, (torch.randn(4, 32).bfloat16(),)).module()
+    assert fuse_quantized_linear(gm) == 2
+    names = _targets(gm)
+    assert not any("linear" in t or "tensorrt.quantize_op" in t or "dynamic_block_quantize_op" in t for t in names), names
+    kind = "fp8" if mode == "fp8" else "nvfp4"
+    assert sum(f"b200_{kind}_gemm" in t for t in names) == 2
+    assert sum(f"b200_{kind}_quantize" in t for t in names) == 4      # CPU weights are not folded
+    assert fuse_quantized_linear(gm) == 0                              # idempotent
+    if how == "trace":
+        y = gm.to("meta")(torch.empty(3, 5, 32, dtype=torch.bfloat16, device="meta"))
+        assert y.shape == (3, 5, 48) and y.dtype == torch.bfloat16
+
+
+def test_rewrite_leaves_other_graphs_alone(b200):
+    from tensorrt_b200.fx_passes import fuse_quantized_linear
+
+    class OnlyInput(torch.nn.Module):          # weight not quantized: not the Q/DQ-linear pattern
+        def __init__(self):
+            super().__init__()
+            self.w = torch.nn.Parameter(torch.randn(16, 32).bfloat16())
+            self.register_buffer("a", torch.tensor(1.0))
+
+        def forward(self, x):
+            return torch.nn.functional.linear(torch.ops.tensorrt.quantize_op(x, self.a, 8, 4, False, False), self.w)
+
+    class Mixed(torch.nn.Module):              # FP8 input with an NVFP4 weight: no single GEMM kind
+        def __init__(self):
+            super().__init__()
+            self.w = torch.nn.Parameter(torch.randn(16, 32).bfloat16())
+            self.register_buffer("a", torch.tensor(1.0))
+
+        def forward(self, x):
+            xq = torch.ops.tensorrt.quantize_op(x, self.a, 8, 4, False, False)
+            wq = torch.ops.tensorrt.dynamic_block_quantize_op(self.w, 16, self.a, 4, 2, 8, 4)
+            return torch.nn.functional.linear(xq, wq)
+
+    class Int8(torch.nn.Module):               # (8, 0) is INT8 in the reference, not E4M3
+        def __init__(self):
+            super().__init__()
+            self.w = torch.nn.Parameter(torch.randn(16, 32).bfloat16())
+            self.register_buffer("a", torch.tensor(1.0))
+
+        def forward(self, x):
+            xq = torch.ops.tensorrt.quantize_op(x, self.a, 8, 0, False, False)
+            wq = torch.ops.tensorrt.quantize_op(self.w, self.a, 8, 0, False, False)
+            return torch.nn.functional.linear(xq, wq)
+
+    for cls in (OnlyInput, Mixed, Int8):
+        gm = torch.fx.symbolic_trace(cls())
+        before = _targets(gm)
+        assert fuse_quantized_linear(gm) == 0
+        assert _targets(gm) == before
+
+
+def test_shared_quantize_node_is_kept_for_its_other_user(b200):
+    from tensorrt_b200.fx_passes import fuse_quantized_linear
+
+    class Shared(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = QdqLinear(16, 32)
+
+        def forward(self, x):
+            xq = self.lin.q(x, self.lin.x_amax)
+            y = torch.nn.functional.linear(xq, self.lin.q(self.lin.weight, self.lin.w_amax), self.lin.bias)
+            return y, xq.sum()
+
+    gm = torch.fx.symbolic_trace(Shared())
+    assert fuse_quantized_linear(gm) == 1
+    names = _targets(gm)
+    assert sum("tensorrt.quantize_op" in t for t in names) == 1       # still feeds xq.sum()
+    assert sum("b200_fp8_gemm" in t for t in names) == 1
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["fp8", "nvfp4"])
+def test_rewritten_graph_matches_unfused_graph_on_gpu(b200, mode):
+    from tensorrt_b200.fx_passes import fuse_quantized_linear
+
+    torch.manual_seed(11)
+    m = QdqLinear(512, 256, mode, seed=3).cuda()
+    x = torch.randn(6, 40, 256, device="cuda").bfloat16()
+    m.x_amax.copy_(x.float().abs().max())
+    ref = m(x)
+    gm = torch.fx.symbolic_trace(m)
+    assert fuse_quantized_linear(gm) == 1
+    names = _targets(gm)
+    kind = "fp8" if mode == "fp8" else "nvfp4"
+    assert sum(f"b200_{kind}_quantize" in t for t in names) == 1      # the weight was folded into buffers
+    assert any(n.startswith("_b200q_w0_") for n, _ in gm.named_buffers())
+    y = gm(x)
+    assert y.shape == ref.shape and y.dtype == ref.dtype
+    assert o.rel_l2(y.float().cpu(), ref.float().cpu()) <= 1e-2
+    # fp16 input: the rewritten graph returns the linear's dtype
+    m16 = QdqLinear(128, 64, mode, seed=4, dtype=torch.float16).cuda()
+    x16 = torch.randn(32, 64, device="cuda").half()
+    ep = torch.export.export(m16, (x16,))
+    g16 = ep.module()
+    assert fuse_quantized_linear(g16) == 1
+    y16 = g16(x16)
+    assert y16.dtype == torch.float16
+    assert o.rel_l2(y16.float().cpu(), m16(x16).float().cpu()) <= 1e-2

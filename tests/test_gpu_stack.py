@@ -54,6 +54,26 @@ def test_glue_kernels(b200):
     assert torch.equal(out, v)
 
 
+@pytest.mark.parametrize("rows,f", [(1, 16), (33, 528), (64, 3584), (17, 14336), (5, 28672), (3, 32768)])
+def test_fused_silu_mul_quantize_is_bit_identical(b200, rows, f):
+    """silu(gate) * up + per-token FP8 quantize in one kernel: codes and scales equal those of the
+    two separate kernels bit for bit (same bf16 rounding point, same division), and dequantize to
+    the oracle's activation."""
+    capi = b200.capi
+    g = torch.Generator().manual_seed(rows + f)
+    gu = (torch.randn(rows, 2 * f, generator=g) * 2).bfloat16()
+    if f > 8:
+        gu[0] = 0                                     # an all-zero token: scale 1, codes 0
+    codes, scales = capi.silu_mul_fp8_quantize(gu.cuda())
+    c_ref, s_ref = capi.fp8_quantize(capi.silu_mul(gu.cuda()), None)
+    assert codes.shape == (rows, f) and scales.shape == (rows,)
+    assert torch.equal(scales, s_ref) and torch.equal(codes, c_ref)
+    ref = torch.nn.functional.silu(gu[:, :f].float()) * gu[:, f:].float()
+    assert o.rel_l2(capi.fp8_dequantize(codes, scales, torch.float32).cpu(), ref) < 4e-2
+    with pytest.raises(b200.B200QError):
+        capi.silu_mul_fp8_quantize(torch.zeros(2, 2 * 32776, dtype=torch.bfloat16, device="cuda"))
+
+
 @pytest.mark.parametrize("cols", [64, 4096, 8192, 12288])
 def test_fused_add_norm_quantize(b200, cols):
     """h + delta, RMSNorm and per-token FP8 quantize in one kernel against the three separate
