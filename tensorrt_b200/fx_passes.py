@@ -90,7 +90,8 @@ def fuse_quantized_linear(gm: fx.GraphModule, fold_weights: bool = True) -> int:
 
     ops.load_ops()
     t = torch.ops.tensorrt
-    graph, n_fused, n_const = gm.graph, 0, 0
+    graph, n_fused = gm.graph, 0
+    n_const = sum(1 for name, _ in gm.named_buffers(recurse=False) if name.startswith("_b200q_w") and name.endswith("_0"))
     for node in list(graph.nodes):
         if node.op != "call_function" or node.target not in _linear_targets() or len(node.args) < 2:
             continue
