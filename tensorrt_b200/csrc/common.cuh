@@ -21,6 +21,33 @@ inline int check_launch() {
   return e == cudaSuccess ? B200Q_OK : B200Q_ERR_CUDA;
 }
 
+// Programmatic dependent launch.  A kernel launched through `launch_pdl` may start while the kernel
+// before it on the stream is still running, once every CTA of that kernel has called
+// `pdl_launch_dependents()` (or exited).  It must call `pdl_wait()` before it touches global
+// memory that an earlier kernel may still read or write; the wait returns when the preceding
+// kernel has completed and its writes are visible.  Kernels that do neither behave as usual.
+bool pdl_enabled();  // environment variable B200Q_PDL, default on
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 // Device must be compute capability 10.x; cached per device.

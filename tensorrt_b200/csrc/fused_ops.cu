@@ -14,6 +14,8 @@ template <int ITEMS>
 __global__ void __launch_bounds__(kThreads)
 rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                 int64_t cols, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[kThreads / 32];
   const int64_t row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * cols;
@@ -74,6 +76,8 @@ __global__ void __launch_bounds__(kThreads)
 add_norm_quant_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ delta,
                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out, uint8_t* __restrict__ codes,
                       float* __restrict__ scales, int64_t cols, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[kThreads / 32];
   const int64_t row = blockIdx.x;
   const int groups = static_cast<int>(cols >> 3);
@@ -140,6 +144,8 @@ add_norm_quant_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* 
 // act[t, j] = silu(gu[t, j]) * gu[t, F + j], gu is [T, 2F] (gate columns first)
 __global__ void __launch_bounds__(kThreads)
 silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int64_t rows, int64_t f) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t groups_per_row = f >> 3;
   const int64_t total = rows * groups_per_row;
   for (int64_t g = blockIdx.x * (int64_t)kThreads + threadIdx.x; g < total; g += (int64_t)gridDim.x * kThreads) {
@@ -160,6 +166,8 @@ silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict_
 template <int ITEMS>
 __global__ void __launch_bounds__(kThreads)
 silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict__ codes, float* __restrict__ scales, int64_t f) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[kThreads / 32];
   const int64_t row = blockIdx.x;
   const int groups = static_cast<int>(f >> 3);
@@ -211,6 +219,8 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict_
 // out = a + b (bf16, fp32 add)
 __global__ void __launch_bounds__(kThreads)
 add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ out, int64_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t groups = n >> 3;
   for (int64_t g = blockIdx.x * (int64_t)kThreads + threadIdx.x; g < groups; g += (int64_t)gridDim.x * kThreads) {
     float x[8], y[8];
@@ -226,6 +236,8 @@ add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict_
 __global__ void __launch_bounds__(kThreads)
 expand_heads_kernel(const __nv_bfloat16* __restrict__ src, int64_t src_stride, int64_t src_col0, __nv_bfloat16* __restrict__ out,
                     int64_t rows, int heads_out, int rep, int head_dim) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t groups_per_head = head_dim >> 3;
   const int64_t groups_per_row = heads_out * groups_per_head;
   const int64_t total = rows * groups_per_row;
@@ -262,10 +274,10 @@ int b200q_rms_norm(const void* x, const void* weight, void* out, int64_t rows, i
   auto* yp = static_cast<__nv_bfloat16*>(out);
   const int items = static_cast<int>(((cols >> 3) + kThreads - 1) / kThreads);
   dim3 grid(static_cast<unsigned>(rows));
-  if (items <= 1) rms_norm_kernel<1><<<grid, kThreads, 0, st>>>(xp, wp, yp, cols, eps);
-  else if (items <= 2) rms_norm_kernel<2><<<grid, kThreads, 0, st>>>(xp, wp, yp, cols, eps);
-  else if (items <= 4) rms_norm_kernel<4><<<grid, kThreads, 0, st>>>(xp, wp, yp, cols, eps);
-  else rms_norm_kernel<0><<<grid, kThreads, 0, st>>>(xp, wp, yp, cols, eps);
+  if (items <= 1) launch_pdl(rms_norm_kernel<1>, dim3(grid), dim3(kThreads), 0, st, xp, wp, yp, cols, eps);
+  else if (items <= 2) launch_pdl(rms_norm_kernel<2>, dim3(grid), dim3(kThreads), 0, st, xp, wp, yp, cols, eps);
+  else if (items <= 4) launch_pdl(rms_norm_kernel<4>, dim3(grid), dim3(kThreads), 0, st, xp, wp, yp, cols, eps);
+  else launch_pdl(rms_norm_kernel<0>, dim3(grid), dim3(kThreads), 0, st, xp, wp, yp, cols, eps);
   return check_launch();
 }
 
@@ -285,10 +297,10 @@ int b200q_add_rms_norm_fp8_quantize(const void* h, const void* delta, const void
   auto* op = static_cast<__nv_bfloat16*>(h_out);
   const int items = static_cast<int>(((cols >> 3) + kThreads - 1) / kThreads);
   dim3 grid(static_cast<unsigned>(rows));
-  if (items <= 1) add_norm_quant_kernel<1><<<grid, kThreads, 0, st>>>(hp, dp, wp, op, codes_out, scales_out, cols, eps);
-  else if (items <= 2) add_norm_quant_kernel<2><<<grid, kThreads, 0, st>>>(hp, dp, wp, op, codes_out, scales_out, cols, eps);
-  else if (items <= 4) add_norm_quant_kernel<4><<<grid, kThreads, 0, st>>>(hp, dp, wp, op, codes_out, scales_out, cols, eps);
-  else add_norm_quant_kernel<8><<<grid, kThreads, 0, st>>>(hp, dp, wp, op, codes_out, scales_out, cols, eps);
+  if (items <= 1) launch_pdl(add_norm_quant_kernel<1>, dim3(grid), dim3(kThreads), 0, st, hp, dp, wp, op, codes_out, scales_out, cols, eps);
+  else if (items <= 2) launch_pdl(add_norm_quant_kernel<2>, dim3(grid), dim3(kThreads), 0, st, hp, dp, wp, op, codes_out, scales_out, cols, eps);
+  else if (items <= 4) launch_pdl(add_norm_quant_kernel<4>, dim3(grid), dim3(kThreads), 0, st, hp, dp, wp, op, codes_out, scales_out, cols, eps);
+  else launch_pdl(add_norm_quant_kernel<8>, dim3(grid), dim3(kThreads), 0, st, hp, dp, wp, op, codes_out, scales_out, cols, eps);
   return check_launch();
 }
 
@@ -298,8 +310,8 @@ int b200q_silu_mul(const void* gate_up, void* out, int64_t rows, int64_t f, b200
   if (gate_up == nullptr || out == nullptr) return B200Q_ERR_INVALID;
   if (!aligned(gate_up, 16) || !aligned(out, 16)) return B200Q_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
-  silu_mul_kernel<<<grid_for(rows * (f >> 3)), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, f);
+  launch_pdl(silu_mul_kernel, dim3(grid_for(rows * (f >> 3))), dim3(kThreads), 0, static_cast<cudaStream_t>(stream),
+             static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, f);
   return check_launch();
 }
 
@@ -314,11 +326,11 @@ int b200q_silu_mul_fp8_quantize(const void* gate_up, uint8_t* codes_out, float* 
   const auto* gp = static_cast<const __nv_bfloat16*>(gate_up);
   const int items = static_cast<int>(((f >> 3) + kThreads - 1) / kThreads);
   dim3 grid(static_cast<unsigned>(rows));
-  if (items <= 1) silu_mul_quant_kernel<1><<<grid, kThreads, 0, st>>>(gp, codes_out, scales_out, f);
-  else if (items <= 2) silu_mul_quant_kernel<2><<<grid, kThreads, 0, st>>>(gp, codes_out, scales_out, f);
-  else if (items <= 4) silu_mul_quant_kernel<4><<<grid, kThreads, 0, st>>>(gp, codes_out, scales_out, f);
-  else if (items <= 8) silu_mul_quant_kernel<8><<<grid, kThreads, 0, st>>>(gp, codes_out, scales_out, f);
-  else silu_mul_quant_kernel<16><<<grid, kThreads, 0, st>>>(gp, codes_out, scales_out, f);
+  if (items <= 1) launch_pdl(silu_mul_quant_kernel<1>, dim3(grid), dim3(kThreads), 0, st, gp, codes_out, scales_out, f);
+  else if (items <= 2) launch_pdl(silu_mul_quant_kernel<2>, dim3(grid), dim3(kThreads), 0, st, gp, codes_out, scales_out, f);
+  else if (items <= 4) launch_pdl(silu_mul_quant_kernel<4>, dim3(grid), dim3(kThreads), 0, st, gp, codes_out, scales_out, f);
+  else if (items <= 8) launch_pdl(silu_mul_quant_kernel<8>, dim3(grid), dim3(kThreads), 0, st, gp, codes_out, scales_out, f);
+  else launch_pdl(silu_mul_quant_kernel<16>, dim3(grid), dim3(kThreads), 0, st, gp, codes_out, scales_out, f);
   return check_launch();
 }
 
@@ -328,8 +340,8 @@ int b200q_add(const void* a, const void* b, void* out, int64_t n, b200q_stream_t
   if (a == nullptr || b == nullptr || out == nullptr) return B200Q_ERR_INVALID;
   if (!aligned(a, 16) || !aligned(b, 16) || !aligned(out, 16)) return B200Q_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
-  add_kernel<<<grid_for(n >> 3), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), static_cast<__nv_bfloat16*>(out), n);
+  launch_pdl(add_kernel, dim3(grid_for(n >> 3)), dim3(kThreads), 0, static_cast<cudaStream_t>(stream),
+             static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), static_cast<__nv_bfloat16*>(out), n);
   return check_launch();
 }
 
@@ -342,8 +354,8 @@ int b200q_expand_heads(const void* src, int64_t src_stride, int64_t src_col0, vo
   if (src == nullptr || out == nullptr) return B200Q_ERR_INVALID;
   if (!aligned(src, 16) || !aligned(out, 16)) return B200Q_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
-  expand_heads_kernel<<<grid_for(rows * heads_out * (head_dim >> 3)), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(src), src_stride, src_col0, static_cast<__nv_bfloat16*>(out), rows, heads_out, rep, head_dim);
+  launch_pdl(expand_heads_kernel, dim3(grid_for(rows * heads_out * (head_dim >> 3))), dim3(kThreads), 0, static_cast<cudaStream_t>(stream),
+             static_cast<const __nv_bfloat16*>(src), src_stride, src_col0, static_cast<__nv_bfloat16*>(out), rows, heads_out, rep, head_dim);
   return check_launch();
 }
 

@@ -42,6 +42,14 @@ int* device_status_word() {
 
 int forced_bn() { return g_force_bn.load(); }
 
+int sf_copier_enabled() {
+  static const int v = [] {
+    const char* e = std::getenv("B200Q_SF_COPIER");   // measured 3-4 % faster with the copier warp: on unless set to 0
+    return e != nullptr ? std::atoi(e) : 1;
+  }();
+  return v;
+}
+
 int forced_smallm_stages() {
   static const int v = [] {
     const char* e = std::getenv("B200Q_SMALLM_STAGES");

@@ -87,7 +87,8 @@ int launch_tile(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, c
   if (int rc = build_out_maps(&tout, p, rs)) return rc;
   const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_kernel<NVF4, BN><<<grid, kThreads, C::kSmemBytes, st>>>(ta, tb, tout, p);
+  const int threads = (NVF4 && p.sf_copier) ? kThreads + 32 : kThreads;   // optional scale-copier warp
+  gemm_kernel<NVF4, BN><<<grid, threads, C::kSmemBytes, st>>>(ta, tb, tout, p);
   return check_launch();
 }
 
@@ -189,13 +190,15 @@ int launch_smallm(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st,
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = static_cast<size_t>(C::smem_bytes(bt, stages));
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = static_cast<unsigned>(splits);
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see common.cuh: pdl_wait in the kernel
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   if (cudaLaunchKernelEx(&cfg, gemm_smallm_kernel<NVF4>, tw, tx, p, splits, stages, bt) != cudaSuccess) {
     cudaGetLastError();
     return B200Q_ERR_CUDA;
@@ -214,6 +217,7 @@ inline int smallm_splits(int n_tiles, int k_tiles, int sms) {
   return s;
 }
 
+int sf_copier_enabled();     // environment variable B200Q_SF_COPIER (default in gemm_fp8.cu)
 int forced_smallm_stages();  // from the environment variable B200Q_SMALLM_STAGES (0 when unset)
 
 // Tile width: 256 when that still gives every SM a tile, else 128.  `force_bn` (128 / 256)
@@ -224,6 +228,7 @@ template <bool NVF4>
 int launch(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, int force_bn, const RsTargets* rs = nullptr) {
   p.status = device_status_word();
   if (p.status == nullptr) return B200Q_ERR_CUDA;
+  p.sf_copier = NVF4 ? sf_copier_enabled() : 0;
   int bn = force_bn;
   const int k_tiles = (p.k_bytes + kBKBytes - 1) / kBKBytes;
   if (rs == nullptr && p.M <= kBM) {

@@ -84,6 +84,7 @@ struct Params {
   int rs_world;            // > 1: reduce-scatter epilogue over `rs_world` ranks (TMA stores to peer buffers)
   int rs_rank;             //      this rank
   int rs_rows;             //      rows owned by each rank (M / rs_world, a multiple of 128)
+  int sf_copier;           // NVFP4, 1-CTA kernel: 1 = a dedicated warp (warp 6 of 224 threads) issues the tcgen05.cp scale copies
   int* status;             // device status word (0 = ok)
 };
 
@@ -181,7 +182,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, float rscale, cons
 }
 
 template <bool NVF4, int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads + 32, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ OutMaps tmap_out, const Params p) {
   using C = Cfg<NVF4, BN>;
@@ -194,8 +195,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   uint64_t* empty_bar = full_bar + C::kStages;
   uint64_t* acc_full = empty_bar + C::kStages;
   uint64_t* acc_empty = acc_full + C::kAccStages;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + C::kAccStages);
+  uint64_t* sf_full = acc_empty + C::kAccStages;          // scales of a stage are in tensor memory (copier warp only)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sf_full + C::kStages);
   volatile uint32_t* abort_flag = tmem_holder + 1;
+  const bool copier = NVF4 && p.sf_copier != 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_blocks = (p.M + kBM - 1) / kBM, n_blocks = (p.N + BN - 1) / BN;
@@ -215,6 +218,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     for (int s = 0; s < C::kStages; ++s) {
       ptx::mbar_init(full_bar + s, 1);
       ptx::mbar_init(empty_bar + s, 1);
+      ptx::mbar_init(sf_full + s, 1);
     }
     for (int s = 0; s < C::kAccStages; ++s) {
       ptx::mbar_init(acc_full + s, 1);
@@ -329,6 +333,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             ok = false;
             break;
           }
+          if constexpr (NVF4) {
+            if (copier && !ptx::mbar_wait(sf_full + stage, phase)) {
+              raise_timeout(p.status, 6);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+          }
           ptx::tc_fence_after();
           const uint32_t a_lo = a_lo0 + stage * kStageStep;          // A tile; B follows at +kABytes
           const uint32_t b_lo = a_lo + (C::kABytes >> 4);
@@ -337,7 +349,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           int kblocks = kBKBytes / kMmaKBytes;
           if constexpr (NVF4) kblocks = min(4, p.sf_col_tiles - kt * 4);
           if (kblocks == 4) {
-            if constexpr (NVF4) {
+            if constexpr (NVF4) if (!copier) {
               const uint32_t sfa_lo = (b_lo & 0x3fffu) + (C::kBBytes >> 4);   // plain address field, no flags
               const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
 #pragma unroll
@@ -362,7 +374,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             // last, partial K tile of an NVFP4 problem whose K is not a multiple of 256
             const uint32_t sfa_lo = (b_lo & 0x3fffu) + (C::kBBytes >> 4);
             const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
-            for (int kb = 0; kb < kblocks; ++kb) {
+            for (int kb = 0; kb < kblocks && !copier; ++kb) {
               ptx::tmem_cp_sf<1>(tmem_sfa + kb * 4, ptx::desc_join(sfa_lo + kb * 32, ptx::kDescHiSf));
               for (int j = 0; j < BN / 128; ++j)
                 ptx::tmem_cp_sf<1>(tmem_sfb + kb * (BN / 32) + j * 4, ptx::desc_join(sfb_lo + j * 128 + kb * 32, ptx::kDescHiSf));
@@ -379,6 +391,44 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         if (ok) ptx::tc_commit<1>(acc_full + acc);  // accumulator complete
         if (++acc == C::kAccStages) acc = 0, acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------ scale copier (NVFP4, optional 7th warp)
+    // Issues the tcgen05.cp of every stage from its own thread, so that the copies of K tile
+    // i + 1 are not queued between the MMAs of tiles i and i + 1 in the MMA thread's stream.
+    // A stage's tensor-memory scale columns are free when its shared memory was refilled: the
+    // producer waited for the MMAs of the previous use before it issued the loads.
+    if constexpr (NVF4) {
+      if (copier && lane == 0) {
+        const uint32_t smem_u = ptx::smem_u32(smem);
+        const uint32_t tmem_sf0 = tmem_base + C::kAccStages * BN;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+          for (int kt = 0; kt < k_tiles; ++kt) {
+            if (!ptx::mbar_wait(full_bar + stage, phase)) {
+              raise_timeout(p.status, 7);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            const uint32_t sfa_lo = ptx::desc_lo_sf(smem_u + stage * C::kStageBytes + C::kABytes + C::kBBytes);
+            const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
+            const uint32_t tmem_sfa = tmem_sf0 + stage * C::kSfCols, tmem_sfb = tmem_sfa + 16;
+            const int kblocks = min(4, p.sf_col_tiles - kt * 4);
+            for (int kb = 0; kb < kblocks; ++kb) {
+              ptx::tmem_cp_sf<1>(tmem_sfa + kb * 4, ptx::desc_join(sfa_lo + kb * 32, ptx::kDescHiSf));
+#pragma unroll
+              for (int j = 0; j < BN / 128; ++j)
+                ptx::tmem_cp_sf<1>(tmem_sfb + kb * (BN / 32) + j * 4, ptx::desc_join(sfb_lo + j * 128 + kb * 32, ptx::kDescHiSf));
+            }
+            ptx::tc_commit<1>(sf_full + stage);
+            if (++stage == C::kStages) stage = 0, phase ^= 1u;
+          }
+        }
       }
     }
   } else {

@@ -146,30 +146,45 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  pdl_launch_dependents();   // the next kernel may be scheduled; it waits for this one before touching memory
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ TMA producer
-    int stage = 0;
-    uint32_t phase = 0;
+    // The weights do not depend on the kernel before this one on the stream: under programmatic
+    // dependent launch the first ring of weight tiles is requested before waiting for that
+    // kernel, the activation tiles (which it may still be writing) after.
     const uint8_t* sfw_src = NVF4 ? p.sfb + static_cast<int64_t>(nb) * p.sf_col_tiles * 512 : nullptr;
     const uint8_t* sfx_src = NVF4 ? p.sfa : nullptr;
-    for (int kt = kt0; kt < kt1; ++kt) {
+    auto sf_bytes_of = [&](int kt) -> uint32_t {
+      return NVF4 ? static_cast<uint32_t>(min(4, p.sf_col_tiles - kt * 4)) * 512u : 0u;
+    };
+    auto issue_w = [&](int kt, int stage) {
+      uint8_t* sw = smem + stage * stage_bytes;
+      const uint32_t sfb = sf_bytes_of(kt);
+      ptx::mbar_arrive_expect_tx(full_bar + stage, static_cast<uint32_t>(C::kWBytes + x_bytes) + 2u * sfb);
+      ptx::tma_load_2d(sw, &tmap_w, full_bar + stage, kt * kBKBytes, n_base);
+      if constexpr (NVF4) ptx::bulk_load(sw + C::kWBytes + x_bytes, sfw_src + kt * 2048, sfb, full_bar + stage);
+    };
+    auto issue_x = [&](int kt, int stage) {
+      uint8_t* sx = smem + stage * stage_bytes + C::kWBytes;
+      ptx::tma_load_2d(sx, &tmap_x, full_bar + stage, kt * kBKBytes, 0);
+      if constexpr (NVF4) ptx::bulk_load(sx + x_bytes + 2048, sfx_src + kt * 2048, sf_bytes_of(kt), full_bar + stage);
+    };
+    const int pre = min(stages, kt1 - kt0);
+    for (int i = 0; i < pre; ++i) issue_w(kt0 + i, i);
+    pdl_wait();
+    ptx::fence_proxy_async_all();
+    for (int i = 0; i < pre; ++i) issue_x(kt0 + i, i);
+    int stage = pre == stages ? 0 : pre;
+    uint32_t phase = pre == stages ? 1u : 0u;
+    for (int kt = kt0 + pre; kt < kt1; ++kt) {
       if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1u)) {
         raise_timeout(p.status, 31);
         *failed = 1;
         break;
       }
-      uint8_t* sw = smem + stage * stage_bytes;
-      uint8_t* sx = sw + C::kWBytes;
-      uint32_t sf_bytes = 0;
-      if constexpr (NVF4) sf_bytes = static_cast<uint32_t>(min(4, p.sf_col_tiles - kt * 4)) * 512u;
-      ptx::mbar_arrive_expect_tx(full_bar + stage, static_cast<uint32_t>(C::kWBytes + x_bytes) + 2u * sf_bytes);
-      ptx::tma_load_2d(sw, &tmap_w, full_bar + stage, kt * kBKBytes, n_base);
-      ptx::tma_load_2d(sx, &tmap_x, full_bar + stage, kt * kBKBytes, 0);
-      if constexpr (NVF4) {
-        ptx::bulk_load(sx + x_bytes, sfw_src + kt * 2048, sf_bytes, full_bar + stage);
-        ptx::bulk_load(sx + x_bytes + 2048, sfx_src + kt * 2048, sf_bytes, full_bar + stage);
-      }
+      issue_w(kt, stage);
+      issue_x(kt, stage);
       if (++stage == stages) stage = 0, phase ^= 1u;
     }
   } else if (warp == 1 && lane == 0) {
@@ -223,6 +238,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         if constexpr (!NVF4) ws = __ldg(p.b_scales + static_cast<int64_t>(n) * p.b_scale_stride);
         if (p.bias != nullptr) wb = __bfloat162float(p.bias[n]);
       }
+      pdl_wait();  // the activation scales come from the kernel before this one
       if (wrow < p.M) {
         if constexpr (NVF4) xs = __fmul_rn(__ldg(p.a_scales), __ldg(p.b_scales));
         else xs = __ldg(p.a_scales + static_cast<int64_t>(wrow) * p.a_scale_stride);
@@ -263,6 +279,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   ptx::tc_fence_before();
   __syncthreads();
   ptx::cluster_sync();
+  pdl_wait();  // every thread stores to global memory below (returns at once: the producer already waited)
 
   if (*failed == 0) {
     // ------------------------------------------------------------ reduce my tokens over the cluster, scale, store

@@ -44,6 +44,8 @@ template <typename T, int ITEMS, int AMAX_MODE, Out OUT>
 __global__ void __launch_bounds__(kRowThreads)
 fp8_rows_kernel(const T* __restrict__ x, const float* __restrict__ amax, uint8_t* __restrict__ codes,
                 T* __restrict__ fake, float* __restrict__ scales, int64_t rows, int64_t cols) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[kRowThreads / 32];
   const int64_t row = blockIdx.x;
   const T* xr = x + row * cols;
@@ -141,7 +143,7 @@ int launch_rows_items(const T* x, const float* amax, uint8_t* codes, T* fake, fl
   const int64_t groups = cols >> 3;
   const int items = static_cast<int>((groups + kRowThreads - 1) / kRowThreads);
   dim3 grid(static_cast<unsigned>(rows)), block(kRowThreads);
-#define B200Q_ROWS(I) fp8_rows_kernel<T, I, AMAX_MODE, OUT><<<grid, block, 0, st>>>(x, amax, codes, fake, scales, rows, cols)
+#define B200Q_ROWS(I) launch_pdl(fp8_rows_kernel<T, I, AMAX_MODE, OUT>, grid, block, 0, st, x, amax, codes, fake, scales, rows, cols)
   if (items <= 1) B200Q_ROWS(1);
   else if (items <= 2) B200Q_ROWS(2);
   else if (items <= 4) B200Q_ROWS(4);

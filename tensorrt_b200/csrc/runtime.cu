@@ -1,4 +1,5 @@
 // Library identification, status strings and per-device properties.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -32,6 +33,14 @@ int check_arch() {
   const DeviceInfo* d = info();
   if (d == nullptr) return B200Q_ERR_CUDA;
   return d->major == 10 ? B200Q_OK : B200Q_ERR_ARCH;
+}
+
+bool pdl_enabled() {
+  static const bool v = [] {
+    const char* e = std::getenv("B200Q_PDL");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  return v;
 }
 
 int sm_count() {
