@@ -384,6 +384,9 @@ def main():
     ap.add_argument("--micro-batches", type=int, default=2, dest="micro_batches",
                     help="tp_stack: token halves walking the layers on separate streams (all-reduce / GEMM overlap)")
     ap.add_argument("--fused", type=int, default=1, help="tp_stack: 1 = fused GEMM + peer-memory all-reduce, 0 = NCCL")
+    ap.add_argument("--phase", choices=["all", "prefill", "decode"], default="all",
+                    help="tp_stack: time only the prefill or only the decode step (profiling runs)")
+    ap.add_argument("--layers", type=int, default=0, help="tp_stack / nvfp4_stack: override the layer count (profiling runs; 0 = the config's)")
     ap.add_argument("--sharded", type=int, default=1,
                     help="tp_stack prefill: 1 = token-sharded residual stream (reduce-scatter + all-gather of FP8 codes), "
                          "0 = all-reduce")

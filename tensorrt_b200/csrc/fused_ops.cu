@@ -8,6 +8,18 @@ namespace {
 
 constexpr int kThreads = 256;
 
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// float at the same shared-memory address in CTA `rank` of the cluster
+__device__ __forceinline__ float ld_cluster_f32(const float* p, int rank) {
+  uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(p)), remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 // y = x * rsqrt(mean(x^2) + eps) * w, fp32 math, bf16 in/out; one CTA per row, the row stays
 // in registers (ITEMS groups of 8 per thread) or is re-read (ITEMS == 0).
 template <int ITEMS>
@@ -71,7 +83,9 @@ rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 //   scale = max|x| / 448 (0 -> 1);  code = e4m3(x / scale)
 // Same arithmetic and rounding points as add -> rms_norm -> fp8 quantize run one after the
 // other, with 1.75 bytes of traffic per element and step instead of 3.25.
-template <int ITEMS>
+// PARTS > 1: a cluster of PARTS CTAs shares one token (few tokens: a decode step); the slices'
+// sums of squares and maxima meet through distributed shared memory, summed in rank order.
+template <int ITEMS, int PARTS>
 __global__ void __launch_bounds__(kThreads)
 add_norm_quant_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ delta,
                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out, uint8_t* __restrict__ codes,
@@ -79,15 +93,24 @@ add_norm_quant_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* 
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[kThreads / 32];
-  const int64_t row = blockIdx.x;
+  __shared__ float part_val[2];
+  const int64_t row = blockIdx.x / PARTS;
+  const int part = PARTS > 1 ? static_cast<int>(blockIdx.x % PARTS) : 0;   // == rank in the cluster
   const int groups = static_cast<int>(cols >> 3);
+  const int per_part = (groups + PARTS - 1) / PARTS;
+  const int g_begin = part * per_part, g_end = min(groups, g_begin + per_part);
+  // few-token form: the norm weights are requested together with the row, ahead of the first
+  // reduction; many-token form: loaded after it (fewer live registers, more CTAs per SM)
+  constexpr bool kEarlyW = PARTS > 1;
   float v[ITEMS][8];
+  float wv[kEarlyW ? ITEMS : 1][8];
   float ss = 0.0f;
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
-    const int g = threadIdx.x + i * kThreads;
-    if (g < groups) {
+    const int g = g_begin + threadIdx.x + i * kThreads;
+    if (g < g_end) {
       Elem<__nv_bfloat16>::load8(h + row * cols + (int64_t)g * 8, v[i]);
+      if constexpr (kEarlyW) Elem<__nv_bfloat16>::load8(w + (int64_t)g * 8, wv[i]);
       if (delta != nullptr) {
         float d[8];
         Elem<__nv_bfloat16>::load8(delta + row * cols + (int64_t)g * 8, d);
@@ -102,17 +125,26 @@ add_norm_quant_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* 
       for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
     }
   }
-  const float inv = rsqrtf(block_sum<kThreads>(ss, red) / static_cast<float>(cols) + eps);
+  float total = block_sum<kThreads>(ss, red);
+  if constexpr (PARTS > 1) {
+    if (threadIdx.x == 0) part_val[0] = total;
+    cluster_barrier();
+    total = 0.0f;
+#pragma unroll
+    for (int r = 0; r < PARTS; ++r) total += ld_cluster_f32(&part_val[0], r);
+  }
+  const float inv = rsqrtf(total / static_cast<float>(cols) + eps);
   float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
-    const int g = threadIdx.x + i * kThreads;
-    if (g < groups) {
-      float wv[8];
-      Elem<__nv_bfloat16>::load8(w + (int64_t)g * 8, wv);
+    const int g = g_begin + threadIdx.x + i * kThreads;
+    if (g < g_end) {
+      float wl[8];
+      if constexpr (!kEarlyW) Elem<__nv_bfloat16>::load8(w + (int64_t)g * 8, wl);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j] * inv * wv[j]));
+        const float wj = kEarlyW ? wv[kEarlyW ? i : 0][j] : wl[j];
+        v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j] * inv * wj));
         amax = fmaxf(amax, fabsf(v[i][j]));
       }
     }
@@ -123,14 +155,22 @@ add_norm_quant_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* 
   __syncthreads();
   amax = (threadIdx.x & 31) < kThreads / 32 ? red[threadIdx.x & 31] : 0.0f;
   amax = warp_max(amax);
+  if constexpr (PARTS > 1) {
+    if (threadIdx.x == 0) part_val[1] = amax;
+    cluster_barrier();
+    float other = 0.0f;
+    if ((threadIdx.x & 31) < PARTS) other = ld_cluster_f32(&part_val[1], threadIdx.x & 31);
+    amax = warp_max(other);
+    cluster_barrier();  // nobody leaves while a peer may still read its shared memory
+  }
   const float scale = fp8_scale_from_amax(amax);
-  if (threadIdx.x == 0) scales[row] = scale;
+  if (threadIdx.x == 0 && part == 0) scales[row] = scale;
   const float y = b200q_rcp_rn(scale);
   const bool fast = b200q_div_fast_ok(scale);
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
-    const int g = threadIdx.x + i * kThreads;
-    if (g < groups) {
+    const int g = g_begin + threadIdx.x + i * kThreads;
+    if (g < g_end) {
       float q[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) q[j] = fast ? b200q_div_by_shared(v[i][j], scale, y) : __fdiv_rn(v[i][j], scale);
@@ -163,21 +203,28 @@ silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict_
 // bf16 activation [T, F] is never written.  One CTA per token; the row stays in registers as
 // packed bf16 (ITEMS groups of 8 per thread), rounded exactly as silu_mul_kernel stores it, so
 // codes and scales equal those of the two separate kernels.
-template <int ITEMS>
+// PARTS > 1: a cluster of PARTS CTAs shares one token (few tokens, long rows: a decode step would
+// otherwise run on a handful of SMs); each CTA takes a contiguous slice of the row and the slice
+// maxima meet through distributed shared memory.
+template <int ITEMS, int PARTS>
 __global__ void __launch_bounds__(kThreads)
 silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict__ codes, float* __restrict__ scales, int64_t f) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[kThreads / 32];
-  const int64_t row = blockIdx.x;
+  __shared__ float part_max;
+  const int64_t row = blockIdx.x / PARTS;
+  const int part = PARTS > 1 ? static_cast<int>(blockIdx.x % PARTS) : 0;   // == rank in the cluster
   const int groups = static_cast<int>(f >> 3);
+  const int per_part = (groups + PARTS - 1) / PARTS;
+  const int g_begin = part * per_part, g_end = min(groups, g_begin + per_part);
   uint4 y[ITEMS];
   float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
-    const int g = threadIdx.x + i * kThreads;
+    const int g = g_begin + threadIdx.x + i * kThreads;
     y[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (g < groups) {
+    if (g < g_end) {
       float a[8], b[8];
       Elem<__nv_bfloat16>::load8(gu + row * 2 * f + (int64_t)g * 8, a);
       Elem<__nv_bfloat16>::load8(gu + row * 2 * f + f + (int64_t)g * 8, b);
@@ -197,14 +244,22 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict_
   __syncthreads();
   amax = (threadIdx.x & 31) < kThreads / 32 ? red[threadIdx.x & 31] : 0.0f;
   amax = warp_max(amax);
+  if constexpr (PARTS > 1) {
+    if (threadIdx.x == 0) part_max = amax;
+    cluster_barrier();
+    float other = 0.0f;
+    if ((threadIdx.x & 31) < PARTS) other = ld_cluster_f32(&part_max, threadIdx.x & 31);
+    amax = warp_max(other);
+    cluster_barrier();  // nobody leaves (or rewrites part_max) while a peer may still read it
+  }
   const float scale = fp8_scale_from_amax(amax);
-  if (threadIdx.x == 0) scales[row] = scale;
+  if (threadIdx.x == 0 && part == 0) scales[row] = scale;
   const float rcp = b200q_rcp_rn(scale);
   const bool fast = b200q_div_fast_ok(scale);
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
-    const int g = threadIdx.x + i * kThreads;
-    if (g < groups) {
+    const int g = g_begin + threadIdx.x + i * kThreads;
+    if (g < g_end) {
       float v[8], q[8];
       Elem<__nv_bfloat16>::unpack(y[i], v);
 #pragma unroll
@@ -295,12 +350,40 @@ int b200q_add_rms_norm_fp8_quantize(const void* h, const void* delta, const void
   const auto* dp = static_cast<const __nv_bfloat16*>(delta);
   const auto* wp = static_cast<const __nv_bfloat16*>(weight);
   auto* op = static_cast<__nv_bfloat16*>(h_out);
-  const int items = static_cast<int>(((cols >> 3) + kThreads - 1) / kThreads);
-  dim3 grid(static_cast<unsigned>(rows));
-  if (items <= 1) launch_pdl(add_norm_quant_kernel<1>, dim3(grid), dim3(kThreads), 0, st, hp, dp, wp, op, codes_out, scales_out, cols, eps);
-  else if (items <= 2) launch_pdl(add_norm_quant_kernel<2>, dim3(grid), dim3(kThreads), 0, st, hp, dp, wp, op, codes_out, scales_out, cols, eps);
-  else if (items <= 4) launch_pdl(add_norm_quant_kernel<4>, dim3(grid), dim3(kThreads), 0, st, hp, dp, wp, op, codes_out, scales_out, cols, eps);
-  else launch_pdl(add_norm_quant_kernel<8>, dim3(grid), dim3(kThreads), 0, st, hp, dp, wp, op, codes_out, scales_out, cols, eps);
+  const int64_t groups = cols >> 3;
+  int parts = 1;   // few tokens: split every row over a cluster so that the launch covers more SMs
+  while (parts < 8 && rows * parts < 2 * sm_count() && groups / (parts * 2) >= kThreads / 2) parts *= 2;
+  const int items = static_cast<int>(((groups + parts - 1) / parts + kThreads - 1) / kThreads);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows * parts));
+  cfg.blockDim = dim3(kThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(parts);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+#define B200Q_ANQ(I, P) cudaLaunchKernelEx(&cfg, add_norm_quant_kernel<I, P>, hp, dp, wp, op, codes_out, scales_out, cols, eps)
+  if (parts == 1) {
+    if (items <= 1) B200Q_ANQ(1, 1);
+    else if (items <= 2) B200Q_ANQ(2, 1);
+    else if (items <= 4) B200Q_ANQ(4, 1);
+    else B200Q_ANQ(8, 1);
+  } else if (parts == 2) {
+    if (items <= 1) B200Q_ANQ(1, 2);
+    else if (items <= 2) B200Q_ANQ(2, 2);
+    else B200Q_ANQ(4, 2);
+  } else if (parts == 4) {
+    if (items <= 1) B200Q_ANQ(1, 4);
+    else B200Q_ANQ(2, 4);
+  } else {
+    B200Q_ANQ(1, 8);
+  }
+#undef B200Q_ANQ
   return check_launch();
 }
 
@@ -324,13 +407,45 @@ int b200q_silu_mul_fp8_quantize(const void* gate_up, uint8_t* codes_out, float* 
   if (int rc = check_arch()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const auto* gp = static_cast<const __nv_bfloat16*>(gate_up);
-  const int items = static_cast<int>(((f >> 3) + kThreads - 1) / kThreads);
-  dim3 grid(static_cast<unsigned>(rows));
-  if (items <= 1) launch_pdl(silu_mul_quant_kernel<1>, dim3(grid), dim3(kThreads), 0, st, gp, codes_out, scales_out, f);
-  else if (items <= 2) launch_pdl(silu_mul_quant_kernel<2>, dim3(grid), dim3(kThreads), 0, st, gp, codes_out, scales_out, f);
-  else if (items <= 4) launch_pdl(silu_mul_quant_kernel<4>, dim3(grid), dim3(kThreads), 0, st, gp, codes_out, scales_out, f);
-  else if (items <= 8) launch_pdl(silu_mul_quant_kernel<8>, dim3(grid), dim3(kThreads), 0, st, gp, codes_out, scales_out, f);
-  else launch_pdl(silu_mul_quant_kernel<16>, dim3(grid), dim3(kThreads), 0, st, gp, codes_out, scales_out, f);
+  const int64_t groups = f >> 3;
+  // few tokens: split every row over a cluster so that the launch covers the SMs
+  int parts = 1;
+  while (parts < 8 && rows * parts < 2 * sm_count() && groups / (parts * 2) >= kThreads / 2) parts *= 2;
+  const int items = static_cast<int>(((groups + parts - 1) / parts + kThreads - 1) / kThreads);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows * parts));
+  cfg.blockDim = dim3(kThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(parts);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+#define B200Q_SILU(I, P) cudaLaunchKernelEx(&cfg, silu_mul_quant_kernel<I, P>, gp, codes_out, scales_out, f)
+  if (parts == 1) {
+    if (items <= 1) B200Q_SILU(1, 1);
+    else if (items <= 2) B200Q_SILU(2, 1);
+    else if (items <= 4) B200Q_SILU(4, 1);
+    else if (items <= 8) B200Q_SILU(8, 1);
+    else B200Q_SILU(16, 1);
+  } else if (parts == 2) {
+    if (items <= 1) B200Q_SILU(1, 2);
+    else if (items <= 2) B200Q_SILU(2, 2);
+    else if (items <= 4) B200Q_SILU(4, 2);
+    else B200Q_SILU(8, 2);
+  } else if (parts == 4) {
+    if (items <= 1) B200Q_SILU(1, 4);
+    else if (items <= 2) B200Q_SILU(2, 4);
+    else B200Q_SILU(4, 4);
+  } else {
+    if (items <= 1) B200Q_SILU(1, 8);
+    else B200Q_SILU(2, 8);
+  }
+#undef B200Q_SILU
   return check_launch();
 }
 

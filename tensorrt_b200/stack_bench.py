@@ -30,6 +30,11 @@ def run(args):
     dev = torch.device("cuda", local)
     tp = args.workload == "tp_stack"
     cfg = LLAMA3_70B if tp else LLAMA3_8B
+    if getattr(args, "layers", 0):
+        import dataclasses
+
+        cfg = dataclasses.replace(cfg, layers=args.layers)   # shortened stack: profiling runs only
+    phase = getattr(args, "phase", "all") if tp else "all"
     if not tp and world > 1:
         raise SystemExit("nvfp4_stack is a single-GPU workload; use tp_stack for --gpus > 1")
     seed = 4 if tp else 3
@@ -52,7 +57,10 @@ def run(args):
     with bench.ClockSampler(local) as clocks:
         mb = args.micro_batches if world > 1 else 1
         sharded = bool(world > 1 and args.sharded and cfg.mode == "fp8")
-        ms = _fwd_time(lambda: stack.forward(h, mb, sharded), steps, warmup, world, bench)
+        if phase == "decode":
+            ms = float("nan")
+        else:
+            ms = _fwd_time(lambda: stack.forward(h, mb, sharded), steps, warmup, world, bench)
     status = capi.device_status()
     prefill_tps = tokens * steps / (ms * 1e-3)
 
@@ -61,11 +69,11 @@ def run(args):
         y = stack.forward(x, args.micro_batches if world > 1 else 1, sharded)
         return float(y.float().abs().mean().item())  # device -> host read of a scalar of the result
 
-    e2e_ms = _fwd_time(e2e, max(1, min(steps, 3)), 1, world, bench)
+    e2e_ms = _fwd_time(e2e, max(1, min(steps, 3)), 1, world, bench) if phase != "decode" else float("nan")
     e2e_steps = max(1, min(steps, 3))
 
     decode = None
-    if tp:
+    if tp and phase != "prefill":
         hd = torch.randn(64, 1, cfg.hidden, generator=g).bfloat16().to(dev)
         dsteps = 20
         decode_fn = lambda: stack(hd)  # noqa: E731
