@@ -78,11 +78,18 @@ def run(args):
         dsteps = 20
         decode_fn = lambda: stack(hd)  # noqa: E731
         graphed = False
-        if world == 1:
-            # a decode step is ~400 short launches: replay it as one CUDA graph
+        if getattr(args, "decode_graph", 1):
+            # a decode step is ~700 short launches (plus 160 small all-reduces at TP > 1): issuing them
+            # from Python costs more than running them, so the step is replayed as one CUDA graph, the
+            # way a serving loop runs it.  NCCL collectives are capturable; every rank captures the
+            # same sequence.
             for _ in range(2):
                 stack(hd)
             torch.cuda.synchronize()
+            if world > 1:
+                import torch.distributed as dist
+
+                dist.barrier()
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
