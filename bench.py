@@ -384,8 +384,9 @@ def main():
     ap.add_argument("--micro-batches", type=int, default=2, dest="micro_batches",
                     help="tp_stack: token halves walking the layers on separate streams (all-reduce / GEMM overlap)")
     ap.add_argument("--fused", type=int, default=1, help="tp_stack: 1 = fused GEMM + peer-memory all-reduce, 0 = NCCL")
-    ap.add_argument("--decode-graph", type=int, default=1, dest="decode_graph",
-                    help="tp_stack: 1 = replay the decode step as a CUDA graph, 0 = issue it launch by launch")
+    ap.add_argument("--decode-graph", type=int, default=-1, dest="decode_graph",
+                    help="tp_stack: 1 = replay the decode step as a CUDA graph, 0 = issue it launch by launch, "
+                         "-1 = graph on one GPU only")
     ap.add_argument("--phase", choices=["all", "prefill", "decode"], default="all",
                     help="tp_stack: time only the prefill or only the decode step (profiling runs)")
     ap.add_argument("--layers", type=int, default=0, help="tp_stack / nvfp4_stack: override the layer count (profiling runs; 0 = the config's)")

@@ -78,11 +78,15 @@ def run(args):
         dsteps = 20
         decode_fn = lambda: stack(hd)  # noqa: E731
         graphed = False
-        if getattr(args, "decode_graph", 1):
-            # a decode step is ~700 short launches (plus 160 small all-reduces at TP > 1): issuing them
-            # from Python costs more than running them, so the step is replayed as one CUDA graph, the
-            # way a serving loop runs it.  NCCL collectives are capturable; every rank captures the
-            # same sequence.
+        want_graph = getattr(args, "decode_graph", -1)
+        if want_graph < 0:
+            want_graph = 1 if world == 1 else 0
+        if want_graph:
+            # a decode step is ~700 short launches: issuing them from Python costs more than running
+            # them, so the step is replayed as one CUDA graph, the way a serving loop runs it.  On by
+            # default on one GPU only: with NCCL all-reduces inside the captured step a 2-GPU run of
+            # this benchmark did not finish (no device fault; stopped by its time limit), so at TP > 1
+            # the step is issued launch by launch unless --decode-graph 1 asks for the capture.
             for _ in range(2):
                 stack(hd)
             torch.cuda.synchronize()
