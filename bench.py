@@ -381,8 +381,9 @@ def main():
     ap.add_argument("--workload", default="nvfp4_quantize")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--shape", default="", help="M,N,K for the GEMM workloads (default: the whole sweep)")
-    ap.add_argument("--micro-batches", type=int, default=2, dest="micro_batches",
-                    help="tp_stack: token halves walking the layers on separate streams (all-reduce / GEMM overlap)")
+    ap.add_argument("--micro-batches", type=int, default=0, dest="micro_batches",
+                    help="tp_stack: micro-batches of tokens walking the layers on separate streams (exchange / GEMM overlap); "
+                         "0 = 4, or 8 at TP >= 8")
     ap.add_argument("--fused", type=int, default=1, help="tp_stack: 1 = fused GEMM + peer-memory all-reduce, 0 = NCCL")
     ap.add_argument("--decode-graph", type=int, default=-1, dest="decode_graph",
                     help="tp_stack: 1 = replay the decode step as a CUDA graph, 0 = issue it launch by launch, "

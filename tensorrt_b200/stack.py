@@ -11,7 +11,7 @@ sliced, partial outputs summed by `tensorrt::fused_nccl_all_reduce` semantics). 
 quantizes the activation slice it owns (per-token amax over the local slice for FP8, a
 tensor amax of the local slice for NVFP4).
 
-With `sharded=True` the residual stream itself is sharded by tokens (sequence-parallel form of
+With `forward(.., sharded=True)` the residual stream itself is sharded by tokens (sequence-parallel form of
 the same plan): a row-parallel linear ends in a reduce-scatter instead of an all-reduce, the
 residual add + RMSNorm + quantize run on the T/W tokens a rank owns, and the column-parallel
 linear that follows starts with an all-gather of the *quantized* activations (1 byte per element
@@ -359,24 +359,32 @@ class DecoderStack:
         self.layers = [DecoderLayer(cfg, shard_layer_weights(w, cfg, rank, world) if world > 1 else w, self.backend, world,
                                     row_parallel) for w in weights]
 
-    def forward(self, h: torch.Tensor, micro_batches: int = 1, sharded: bool = False) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, micro_batches: int = 1, sharded=False) -> torch.Tensor:
         """`micro_batches` = 2 (tensor-parallel, CUDA): the tokens are split in two halves that walk
         the layers on two streams, so the collectives of one half run while the other half's
         GEMMs compute.  The result is the same as with one batch: every op is row-wise.
         `sharded`: token-sharded residual stream (reduce-scatter / all-gather of quantized
-        activations instead of all-reduce); needs the token count of every micro-batch to divide
-        by the TP size."""
+        activations instead of all-reduce).  True = the fused peer-memory kernels when every
+        micro-batch has a multiple of world * 128 tokens, else the all-reduce form; "collectives" =
+        the same flow on the process group's reduce-scatter / all-gather (any token count that
+        divides by the TP size)."""
         shape = h.shape
         h = h.reshape(-1, shape[-1])
-        sharded = sharded and self.world > 1
+        if sharded not in (False, True, "collectives"):
+            raise ValueError(f"sharded must be False, True or 'collectives', got {sharded!r}")
+        if self.world == 1:
+            sharded = False
         if micro_batches > 1 and self.world > 1 and h.is_cuda and h.shape[0] >= 2 * 128 * self.world:
             return self._forward_overlapped(h, micro_batches, sharded).view(shape)
         return self._micro_batch(h, sharded).view(shape)
 
     def _micro_batch(self, h: torch.Tensor, sharded: bool) -> torch.Tensor:
         """All layers over one batch of tokens on the current stream."""
-        if sharded and self._fused is not None and self._fused.usable(h.shape[0]):
-            return self._walk_fused_sharded(h).clone()
+        if sharded is True:
+            if self._fused is not None and self._fused.usable(h.shape[0]):
+                return self._walk_fused_sharded(h).clone()
+            sharded = False
+        sharded = bool(sharded)
         return self._finish(*self._walk(self._enter(h, sharded), None, sharded), sharded)
 
     def _walk_fused_sharded(self, h: torch.Tensor) -> torch.Tensor:
@@ -421,7 +429,9 @@ class DecoderStack:
         chunks = [h[i * step:min(rows, (i + 1) * step)] for i in range(n)]
         for st in self._streams:
             st.wait_stream(main)
-        if sharded and self._fused is not None and all(self._fused.usable(c.shape[0]) for c in chunks):
+        fused = sharded is True and self._fused is not None and all(self._fused.usable(c.shape[0]) for c in chunks)
+        sharded = sharded == "collectives"
+        if fused:
             parts = self._overlapped_fused_sharded(chunks)
         else:
             parts = [self._enter(c, sharded) for c in chunks]

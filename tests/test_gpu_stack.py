@@ -142,6 +142,8 @@ def _tp_worker(rank, world, store_path, out_path, slabs, fused, micro, sharded):
     r = torch.ops.tensorrt.fused_nccl_all_reduce(t, "sum", group_name_of())
     assert torch.allclose(r.cpu(), torch.full((1, 4), world * (world + 1) / 2), atol=1e-3, rtol=1e-3)
     stack = DecoderStack(cfg, _to(ws, "cuda"), rank=rank, world=world, slabs=slabs, fused_rows=512 if fused else 0)
+    if sharded and not fused:
+        sharded = "collectives"                  # the process group's reduce-scatter / all-gather
     y = stack.forward(h.cuda(), micro, sharded)
     y2 = stack.forward(h.cuda(), micro, sharded)  # a second pass reuses the peer buffers and flag epochs
     assert torch.equal(y, y2)

@@ -103,15 +103,17 @@ def _worker_stack(rank, world, store_path, mode, out_path):
     if mode == "fp8":
         # token-sharded residual stream: reduce-scatter + all-gather of the norm outputs; every
         # token sees the same arithmetic as with the all-reduce
-        y_sharded = stack.forward(h, sharded=True)
+        y_sharded = stack.forward(h, sharded="collectives")
         assert torch.equal(y_sharded, ref_tp), o.rel_l2(y_sharded.float(), ref_tp.float())
         try:
-            stack.forward(h[:, :7], sharded=True)       # 14 tokens over 2 ranks is fine, 2 x 7 ...
-            stack.forward(h[:1, :7], sharded=True)      # ... 7 tokens are not
+            stack.forward(h[:, :7], sharded="collectives")       # 14 tokens over 2 ranks is fine, 2 x 7 ...
+            stack.forward(h[:1, :7], sharded="collectives")      # ... 7 tokens are not
         except ValueError as e:
             assert "do not divide" in str(e)
         else:
             raise AssertionError("ragged token count not rejected")
+        # sharded=True asks for the fused peer-memory kernels; without them (CPU) it is the all-reduce form
+        assert torch.equal(stack.forward(h, sharded=True), ref_tp)
     if rank == 0:
         torch.save(y, out_path)
     dist.barrier()
