@@ -55,6 +55,57 @@ def test_argument_validation_without_a_device(b200):
     assert lib.b200q_gemm_set_tile_n(0) == 0
 
 
+def test_validation_of_the_fused_and_peer_entry_points_without_a_device(b200):
+    from tensorrt_b200 import _lib
+
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(8192)
+    p = (ctypes.addressof(buf) + 255) & ~255
+    assert lib.b200q_silu_mul_fp8_quantize(None, p, p, 4, 64, None) == -1           # null input
+    assert lib.b200q_silu_mul_fp8_quantize(p, p, p, 4, 60, None) == -1              # f % 8
+    assert lib.b200q_silu_mul_fp8_quantize(p, p, p, 4, 32776, None) == -1           # f beyond 32768
+    assert lib.b200q_silu_mul_fp8_quantize(p, p, p, 0, 64, None) == 0               # empty: no-op
+    assert lib.b200q_silu_mul_fp8_quantize(p + 2, p, p, 4, 64, None) == -2          # misaligned
+    assert lib.b200q_add_rms_norm_fp8_quantize(p, None, p, None, p, p, 4, 16392, 1e-5, None) == -1   # cols beyond 16384
+    peers = _lib.Peers()
+    peers.rank, peers.world = 0, 2
+    for r in range(2):
+        peers.recv[r], peers.out[r], peers.flags[r] = p, p, p
+    ref = ctypes.byref(peers)
+    assert lib.b200q_reduce_gather(None, None, 256, 64, 1, None) == -1               # no peers
+    assert lib.b200q_reduce_gather(ref, None, 200, 64, 1, None) == -1                # M not a multiple of world * 128
+    assert lib.b200q_reduce_gather(ref, None, 256, 60, 1, None) == -1                # N % 8
+    assert lib.b200q_reduce_add_gather(ref, None, None, 256, 64, 1, None) == -1      # residual shard is required
+    peers.world = 9
+    assert lib.b200q_reduce_gather(ref, None, 9 * 128, 64, 1, None) == -1            # more than 8 ranks
+    gp = _lib.GatherPeers()
+    gp.rank, gp.world = 1, 2
+    for r in range(2):
+        gp.recv[r], gp.codes[r], gp.scales[r], gp.flags[r] = p, p, p, p
+    gref = ctypes.byref(gp)
+    f = lib.b200q_reduce_add_rms_norm_fp8_quantize_gather
+    assert f(gref, None, None, p, 1e-5, 256, 64, 1, None) == -1                      # no residual shard
+    assert f(gref, None, p, None, 1e-5, 256, 64, 1, None) == -1                      # no norm weight
+    assert f(gref, None, p, p, 1e-5, 256, 72, 1, None) == -1                         # N % 16
+    assert f(gref, None, p, p, 1e-5, 256, 16400, 1, None) == -1                      # N beyond 16384
+    assert f(gref, None, p, p, 1e-5, 384, 64, 1, None) == -1                         # M not a multiple of world * 128
+    gp.codes[1] = None
+    assert f(gref, None, p, p, 1e-5, 256, 64, 1, None) == -1                         # a peer buffer is missing
+
+
+def test_product_does_not_reach_into_test_infrastructure():
+    """Nothing under the package may import, read or run the oracle or scratch files."""
+    import pathlib
+    import re
+
+    root = pathlib.Path(__file__).resolve().parents[1]
+    bad = re.compile(r"^\s*(from|import)\s+(oracle|_work)\b|['\"/]_work/|['\"/]oracle/")
+    for path in list((root / "tensorrt_b200").rglob("*.py")) + list((root / "tensorrt_b200" / "csrc").glob("*")) + [root / "include" / "b200q.h"]:
+        if path.is_file() and path.suffix in (".py", ".cu", ".cuh", ".h", ".cpp"):
+            for n, line in enumerate(path.read_text().splitlines(), 1):
+                assert not bad.search(line), f"{path}:{n}: {line.strip()}"
+
+
 def test_product_has_no_cpu_path(b200):
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         b200.capi.fp8_quantize(torch.randn(4, 64))
