@@ -11,6 +11,8 @@ does that fusion on the graph itself:
     y  = linear(xq, wq, b)                                     wc, ws = b200_fp8_quantize(W, aw)
                                                                y = b200_fp8_gemm(xc, xs, wc, ws, b)
 
+(`mm(xq, wq.t())`, `matmul(xq, wq.t())` and `addmm(b, xq, wq.t())` are recognised as the same linear)
+
 and the same with `dynamic_block_quantize_op(.., 16, amax, 4, 2, 8, 4)` -> `b200_nvfp4_*`.
 The fake-quantized bf16 tensors are never materialised; the result differs from the unfused
 graph only by the GEMM's accumulation (fp32 over code products instead of bf16 operands).
@@ -41,6 +43,41 @@ def _is_op(node: fx.Node, packet) -> bool:
 
 def _linear_targets():
     return (torch.nn.functional.linear, torch.ops.aten.linear, torch.ops.aten.linear.default)
+
+
+def _transposed(node):
+    """W behind `W.t()` / `W.T`-style nodes (aten.t, transpose(0, 1), permute([1, 0])), else None."""
+    if not isinstance(node, fx.Node):
+        return None
+    if node.op == "call_function":
+        a = torch.ops.aten
+        if node.target in (a.t, a.t.default):
+            return node.args[0]
+        if node.target in (a.transpose, a.transpose.int, torch.transpose) and tuple(node.args[1:3]) in ((0, 1), (1, 0), (-1, -2), (-2, -1)):
+            return node.args[0]
+        if node.target in (a.permute, a.permute.default, torch.permute) and list(node.args[1]) == [1, 0]:
+            return node.args[0]
+    if node.op == "call_method" and node.target == "t":
+        return node.args[0]
+    return None
+
+
+def _as_linear(node: fx.Node):
+    """(input, weight, bias) when `node` computes input @ weight^T (+ bias) in one of the forms the
+    reference converts (aten_ops_converters.py:4197-4213 linear, :779-799 matmul, :3477-3500 addmm,
+    the form `aten.linear` decomposes to in distributed mode), else None."""
+    if node.op != "call_function":
+        return None
+    a = torch.ops.aten
+    if node.target in _linear_targets() and len(node.args) >= 2:
+        return node.args[0], node.args[1], (node.args[2] if len(node.args) > 2 else node.kwargs.get("bias"))
+    if node.target in (a.mm, a.mm.default, a.matmul, a.matmul.default, torch.matmul, torch.mm) and len(node.args) == 2:
+        w = _transposed(node.args[1])
+        return (node.args[0], w, None) if w is not None else None
+    if node.target in (a.addmm, a.addmm.default, torch.addmm) and len(node.args) == 3 and not node.kwargs:
+        w = _transposed(node.args[2])
+        return (node.args[1], w, node.args[0]) if w is not None else None
+    return None
 
 
 def _match_fp8(node: fx.Node):
@@ -93,10 +130,10 @@ def fuse_quantized_linear(gm: fx.GraphModule, fold_weights: bool = True) -> int:
     graph, n_fused = gm.graph, 0
     n_const = sum(1 for name, _ in gm.named_buffers(recurse=False) if name.startswith("_b200q_w") and name.endswith("_0"))
     for node in list(graph.nodes):
-        if node.op != "call_function" or node.target not in _linear_targets() or len(node.args) < 2:
+        form = _as_linear(node)
+        if form is None:
             continue
-        xq, wq = node.args[0], node.args[1]
-        bias = node.args[2] if len(node.args) > 2 else node.kwargs.get("bias")
+        xq, wq, bias = form
         if not isinstance(xq, fx.Node) or not isinstance(wq, fx.Node):
             continue
         mode, mx, mw = "fp8", _match_fp8(xq), _match_fp8(wq)
@@ -129,7 +166,11 @@ def fuse_quantized_linear(gm: fx.GraphModule, fold_weights: bool = True) -> int:
                 out = graph.call_method("to", (out, dtype))
         out.meta.update({k: v for k, v in node.meta.items() if k in ("val", "tensor_meta")})
         node.replace_all_uses_with(out)
+        dangling = [a for a in node.all_input_nodes if _transposed(a) is wq]
         graph.erase_node(node)
+        for tnode in dangling:
+            if not tnode.users:
+                graph.erase_node(tnode)
         for q in (xq, wq):
             if not q.users:
                 graph.erase_node(q)

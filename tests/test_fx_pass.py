@@ -152,3 +152,49 @@ def test_rewritten_graph_matches_unfused_graph_on_gpu(b200, mode):
     y16 = g16(x16)
     assert y16.dtype == torch.float16
     assert o.rel_l2(y16.float().cpu(), m16(x16).float().cpu()) <= 1e-2
+
+
+@pytest.mark.parametrize("form", ["mm", "matmul", "addmm", "method_t"])
+def test_matmul_and_addmm_forms_are_the_same_linear(b200, form):
+    """`aten.linear` reaches the converters as mm / addmm with a transposed weight in distributed
+    mode (lowering/_decompositions.py:738-745); those forms are rewritten too."""
+    from tensorrt_b200.fx_passes import fuse_quantized_linear
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = QdqLinear(48, 32)
+
+        def forward(self, x):
+            xq = self.lin.q(x, self.lin.x_amax)
+            wq = self.lin.q(self.lin.weight, self.lin.w_amax)
+            if form == "mm":
+                return torch.ops.aten.mm.default(xq, torch.ops.aten.t.default(wq))
+            if form == "matmul":
+                return torch.matmul(xq, torch.ops.aten.permute.default(wq, [1, 0]))
+            if form == "addmm":
+                return torch.ops.aten.addmm.default(self.lin.bias, xq, torch.ops.aten.transpose.int(wq, 0, 1))
+            return torch.mm(xq, wq.t())
+
+    gm = torch.fx.symbolic_trace(M())
+    assert fuse_quantized_linear(gm) == 1
+    names = _targets(gm)
+    assert sum("b200_fp8_gemm" in t for t in names) == 1
+    assert not any("quantize_op" in t or "aten.mm" in t or "addmm" in t or "matmul" in t or "aten.t." in t or "permute" in t
+                   or "transpose" in t for t in names), names
+    gemm = next(n for n in gm.graph.nodes if "b200_fp8_gemm" in str(n.target))
+    assert (gemm.args[4] is not None) == (form == "addmm")          # addmm's first argument is the bias
+    y = gm.to("meta")(torch.empty(7, 32, dtype=torch.bfloat16, device="meta"))
+    assert y.shape == (7, 48)
+    # a plain matmul of two quantized activations (no transposed weight) is not a linear
+    class Plain(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.register_buffer("a", torch.tensor(1.0))
+
+        def forward(self, x, y):
+            q = lambda t: torch.ops.tensorrt.quantize_op(t, self.a, 8, 4, False, False)  # noqa: E731
+            return torch.matmul(q(x), q(y))
+
+    gm2 = torch.fx.symbolic_trace(Plain())
+    assert fuse_quantized_linear(gm2) == 0
