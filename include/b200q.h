@@ -265,6 +265,15 @@ int b200q_expand_heads(const void* src, int64_t src_stride, int64_t src_col0, vo
  * Process-wide tuning knob; results do not depend on it beyond fp32 summation order. */
 int b200q_gemm_set_tile_n(int bn);
 
+/* Promise about the B operand (weights, their scales, the bias) of the GEMM calls that follow, process-wide:
+ * non-zero = the work that wrote it has FINISHED on the device (weights quantized at load time, followed by
+ * a synchronisation), so no kernel still in flight when a GEMM starts can be writing it.  The small-M GEMM
+ * is launched programmatically dependent on its predecessor, and through a chain of such launches may start
+ * while several earlier kernels still run; with the promise it requests its first weight tiles right away
+ * and waits for its predecessors only before reading the activations.  Without it (default) it waits before
+ * reading anything. */
+int b200q_gemm_assume_static_weights(int on);
+
 /* The GEMM kernels bound every device-side wait; a wait that gives up records it in a
  * device status word instead of hanging.  This call synchronises with the device, returns
  * B200Q_OK or B200Q_ERR_TIMEOUT, and clears the word when `reset` is non-zero. */

@@ -36,6 +36,7 @@ SIGNATURES = {
     "b200q_nvfp4_gemm": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "b200q_fp8_gemm_reduce_scatter": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _p]),
     "b200q_nvfp4_gemm_reduce_scatter": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
+    "b200q_gemm_assume_static_weights": (_c.c_int, [_c.c_int]),
     "b200q_reduce_gather": (_c.c_int, [_p, _p, _i64, _i64, _c.c_uint32, _p]),
     "b200q_reduce_add_gather": (_c.c_int, [_p, _p, _p, _i64, _i64, _c.c_uint32, _p]),
     "b200q_reduce_add_rms_norm_fp8_quantize_gather": (_c.c_int, [_p, _p, _p, _p, _c.c_float, _i64, _i64, _c.c_uint32, _p]),

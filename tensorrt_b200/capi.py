@@ -285,6 +285,12 @@ def expand_heads(src: torch.Tensor, col0: int, heads_out: int, rep: int, head_di
     return out
 
 
+def assume_static_weights(on: bool) -> None:
+    """Promise (process-wide, until revoked) that GEMM weights are older than the kernel launched just
+    before each GEMM: lets the small-M GEMM fetch weights while that kernel still runs."""
+    check(load().b200q_gemm_assume_static_weights(1 if on else 0), "b200q_gemm_assume_static_weights")
+
+
 def set_gemm_tile_n(bn: int) -> None:
     check(load().b200q_gemm_set_tile_n(bn), "b200q_gemm_set_tile_n")
 

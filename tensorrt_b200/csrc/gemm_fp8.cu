@@ -42,6 +42,9 @@ int* device_status_word() {
 
 int forced_bn() { return g_force_bn.load(); }
 
+std::atomic<int> g_static_weights{0};
+int static_weights_promised() { return g_static_weights.load(); }
+
 int sf_copier_enabled() {
   static const int v = [] {
     const char* e = std::getenv("B200Q_SF_COPIER");   // measured 3-4 % faster with the copier warp: on unless set to 0
@@ -68,6 +71,11 @@ extern "C" {
 int b200q_gemm_set_tile_n(int bn) {
   if (bn != 0 && bn != 128 && bn != 256 && bn != 512 && bn != 1001 && bn != 1002 && bn != 1004 && bn != 1008) return B200Q_ERR_INVALID;
   gemm::g_force_bn.store(bn);
+  return B200Q_OK;
+}
+
+int b200q_gemm_assume_static_weights(int on) {
+  gemm::g_static_weights.store(on ? 1 : 0);
   return B200Q_OK;
 }
 

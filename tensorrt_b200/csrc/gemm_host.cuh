@@ -217,6 +217,7 @@ inline int smallm_splits(int n_tiles, int k_tiles, int sms) {
   return s;
 }
 
+int static_weights_promised();   // b200q_gemm_assume_static_weights
 int sf_copier_enabled();     // environment variable B200Q_SF_COPIER (default in gemm_fp8.cu)
 int forced_smallm_stages();  // from the environment variable B200Q_SMALLM_STAGES (0 when unset)
 
@@ -229,6 +230,7 @@ int launch(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, int fo
   p.status = device_status_word();
   if (p.status == nullptr) return B200Q_ERR_CUDA;
   p.sf_copier = NVF4 ? sf_copier_enabled() : 0;
+  p.static_weights = static_weights_promised();
   int bn = force_bn;
   const int k_tiles = (p.k_bytes + kBKBytes - 1) / kBKBytes;
   if (rs == nullptr && p.M <= kBM) {

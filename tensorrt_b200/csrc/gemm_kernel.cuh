@@ -87,6 +87,9 @@ struct Params {
   int rs_world;            // > 1: reduce-scatter epilogue over `rs_world` ranks (TMA stores to peer buffers)
   int rs_rank;             //      this rank
   int rs_rows;             //      rows owned by each rank (M / rs_world, a multiple of 128)
+  int static_weights;      // small-M kernel under programmatic dependent launch: 1 = B (weights, their scales, bias) was
+                           // written before the preceding kernel on the stream started, so it may be read before
+                           // waiting for that kernel; 0 = wait first
   int sf_copier;           // NVFP4, 1-CTA kernel: 1 = a dedicated warp (warp 6 of 224 threads) issues the tcgen05.cp scale copies
   int* status;             // device status word (0 = ok)
 };

@@ -150,9 +150,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 
   if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------ TMA producer
-    // The weights do not depend on the kernel before this one on the stream: under programmatic
-    // dependent launch the first ring of weight tiles is requested before waiting for that
-    // kernel, the activation tiles (which it may still be writing) after.
+    // Under programmatic dependent launch this kernel may start while the kernel before it on the
+    // stream still runs.  When the caller promised that the weights are older than that kernel
+    // (static_weights), the first ring of weight tiles is requested before waiting for it and only
+    // the activation tiles (which it may still be writing) after; otherwise everything waits.
     const uint8_t* sfw_src = NVF4 ? p.sfb + static_cast<int64_t>(nb) * p.sf_col_tiles * 512 : nullptr;
     const uint8_t* sfx_src = NVF4 ? p.sfa : nullptr;
     auto sf_bytes_of = [&](int kt) -> uint32_t {
@@ -171,9 +172,15 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       if constexpr (NVF4) ptx::bulk_load(sx + x_bytes + 2048, sfx_src + kt * 2048, sf_bytes_of(kt), full_bar + stage);
     };
     const int pre = min(stages, kt1 - kt0);
+    if (!p.static_weights) {   // the weights may come from the kernel before this one: wait first
+      pdl_wait();
+      ptx::fence_proxy_async_all();
+    }
     for (int i = 0; i < pre; ++i) issue_w(kt0 + i, i);
-    pdl_wait();
-    ptx::fence_proxy_async_all();
+    if (p.static_weights) {
+      pdl_wait();
+      ptx::fence_proxy_async_all();
+    }
     for (int i = 0; i < pre; ++i) issue_x(kt0 + i, i);
     int stage = pre == stages ? 0 : pre;
     uint32_t phase = pre == stages ? 1u : 0u;
@@ -234,6 +241,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     {
       const int n = n_base + wrow;
       float ws = 1.0f, wb = 0.0f, xs = 0.0f;
+      if (!p.static_weights) pdl_wait();
       if (n < p.N) {
         if constexpr (!NVF4) ws = __ldg(p.b_scales + static_cast<int64_t>(n) * p.b_scale_stride);
         if (p.bias != nullptr) wb = __bfloat162float(p.bias[n]);

@@ -358,6 +358,11 @@ class DecoderStack:
                 row_parallel = lambda x, qw, amax=None: reduce(be.linear(x, qw, amax))  # noqa: E731
         self.layers = [DecoderLayer(cfg, shard_layer_weights(w, cfg, rank, world) if world > 1 else w, self.backend, world,
                                     row_parallel) for w in weights]
+        # every weight is quantized and resident from here on: forward() may promise the GEMMs that
+        # no kernel in flight is still writing them (capi.assume_static_weights)
+        self._static_weights = isinstance(self.backend, CudaBackend)
+        if self._static_weights and torch.cuda.is_available():
+            torch.cuda.synchronize()
 
     def forward(self, h: torch.Tensor, micro_batches: int = 1, sharded=False) -> torch.Tensor:
         """`micro_batches` = 2 (tensor-parallel, CUDA): the tokens are split in two halves that walk
@@ -374,9 +379,15 @@ class DecoderStack:
             raise ValueError(f"sharded must be False, True or 'collectives', got {sharded!r}")
         if self.world == 1:
             sharded = False
-        if micro_batches > 1 and self.world > 1 and h.is_cuda and h.shape[0] >= 2 * 128 * self.world:
-            return self._forward_overlapped(h, micro_batches, sharded).view(shape)
-        return self._micro_batch(h, sharded).view(shape)
+        if self._static_weights:
+            capi.assume_static_weights(True)
+        try:
+            if micro_batches > 1 and self.world > 1 and h.is_cuda and h.shape[0] >= 2 * 128 * self.world:
+                return self._forward_overlapped(h, micro_batches, sharded).view(shape)
+            return self._micro_batch(h, sharded).view(shape)
+        finally:
+            if self._static_weights:
+                capi.assume_static_weights(False)
 
     def _micro_batch(self, h: torch.Tensor, sharded: bool) -> torch.Tensor:
         """All layers over one batch of tokens on the current stream."""
