@@ -180,3 +180,36 @@ def fuse_quantized_linear(gm: fx.GraphModule, fold_weights: bool = True) -> int:
         graph.lint()
         gm.recompile()
     return n_fused
+
+
+def fuse_all_reduce_wait(gm: fx.GraphModule) -> int:
+    """`_c10d_functional.all_reduce(x, op, group)` whose only user is `wait_tensor` becomes one
+    `tensorrt::fused_nccl_all_reduce(x, op, group)` node, the form the reference's converters (and
+    this package's row-parallel paths) consume
+    (py/torch_tensorrt/dynamo/lowering/passes/fuse_distributed_ops.py:167-234).  An all-reduce whose
+    result is used by anything besides a single wait is left alone.  Returns the number of pairs
+    fused; the module is recompiled in place."""
+    from . import ops
+
+    ops.load_ops()
+    c10d = torch.ops._c10d_functional
+    fused_op = torch.ops.tensorrt.fused_nccl_all_reduce.default
+    graph, count = gm.graph, 0
+    for node in list(graph.nodes):
+        if node.op != "call_function" or node.target is not c10d.all_reduce.default or len(node.users) != 1:
+            continue
+        wait = next(iter(node.users))
+        if wait.op != "call_function" or wait.target is not c10d.wait_tensor.default:
+            continue
+        with graph.inserting_after(wait):
+            fused = graph.call_function(fused_op, tuple(node.args[:3]))
+        fused.meta.update(node.meta)
+        wait.replace_all_uses_with(fused)
+        graph.erase_node(wait)
+        graph.erase_node(node)
+        count += 1
+    if count:
+        graph.eliminate_dead_code()
+        graph.lint()
+        gm.recompile()
+    return count

@@ -198,3 +198,41 @@ def test_matmul_and_addmm_forms_are_the_same_linear(b200, form):
 
     gm2 = torch.fx.symbolic_trace(Plain())
     assert fuse_quantized_linear(gm2) == 0
+
+
+def _all_reduce_graph(extra_user: bool):
+    """x -> all_reduce -> wait_tensor -> relu, built node by node (functional collectives as they
+    appear in an exported tensor-parallel graph)."""
+    c10d = torch.ops._c10d_functional
+    g = torch.fx.Graph()
+    x = g.placeholder("x")
+    ar = g.call_function(c10d.all_reduce.default, (x, "sum", "0"))
+    w = g.call_function(c10d.wait_tensor.default, (ar,))
+    out = g.call_function(torch.relu, (w,))
+    if extra_user:
+        out = g.call_function(torch.add, (out, ar))
+    g.output(out)
+    return torch.fx.GraphModule(torch.nn.Module(), g)
+
+
+def test_all_reduce_plus_wait_becomes_the_fused_op(b200):
+    from tensorrt_b200.fx_passes import fuse_all_reduce_wait
+
+    gm = _all_reduce_graph(extra_user=False)
+    assert fuse_all_reduce_wait(gm) == 1
+    names = _targets(gm)
+    assert sum("tensorrt.fused_nccl_all_reduce" in t for t in names) == 1
+    assert not any("_c10d_functional" in t for t in names), names
+    node = next(n for n in gm.graph.nodes if "fused_nccl_all_reduce" in str(n.target))
+    assert node.args[1:] == ("sum", "0")                               # exactly (inp, reduce_op, group_name)
+    assert fuse_all_reduce_wait(gm) == 0
+    # without a process group the eager op is the identity (single rank), out of place
+    x = torch.randn(4, 8)
+    gm.graph.lint()
+    node.args = (node.args[0], "sum", "default")
+    gm.recompile()
+    assert torch.equal(gm(x), torch.relu(x))
+    # an all-reduce that something else also reads keeps its wait
+    gm2 = _all_reduce_graph(extra_user=True)
+    before = _targets(gm2)
+    assert fuse_all_reduce_wait(gm2) == 0 and _targets(gm2) == before
