@@ -25,6 +25,35 @@ def resolve_group(group_name: str):
     return _resolve_process_group(group_name)
 
 
+def probe_group_names(backend: str | None = "nccl", limit: int = 20) -> list[str]:
+    """Names among "0" .. str(limit - 1) that resolve to a registered process group (of `backend`
+    when given).  The reference's runtime resolves an engine's group this way when none was pinned
+    (core/runtime/TRTEngine.cpp:845-857): gaps in the numbering are skipped, and the result is only
+    usable when exactly one group is found."""
+    from torch._C._distributed_c10d import _resolve_process_group
+
+    found = []
+    for i in range(limit):
+        try:
+            group = _resolve_process_group(str(i))
+        except Exception:  # unknown name: a gap in the numbering
+            continue
+        if group is None:
+            continue
+        if backend is None or dist.get_backend(group) == backend:
+            found.append(str(i))
+    return found
+
+
+def auto_group_name(backend: str | None = "nccl") -> str:
+    """The single registered group's name; raises when there is none or more than one (a TP + DP
+    job must pin the group explicitly, as in the reference)."""
+    names = probe_group_names(backend)
+    if len(names) != 1:
+        raise RuntimeError(f"cannot pick a process group automatically: found {names or 'none'}; pass the group name")
+    return names[0]
+
+
 def all_reduce_by_group_name(inp: torch.Tensor, reduce_op: str, group_name: str) -> torch.Tensor:
     """Eager body of `tensorrt::fused_nccl_all_reduce(inp, reduce_op, group_name)`
     (py/torch_tensorrt/dynamo/lowering/passes/fuse_distributed_ops.py:57-63): out of place,

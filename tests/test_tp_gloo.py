@@ -86,6 +86,23 @@ def _worker_stack(rank, world, store_path, mode, out_path):
     r = torch.ops.tensorrt.fused_nccl_all_reduce(t, "max", group_name_of())
     assert torch.equal(r, torch.full((1, 4), float(world)))
 
+    # 1b. group resolution without a pinned name: exactly one gloo group is registered here
+    from tensorrt_b200.tp import auto_group_name, probe_group_names, resolve_group
+
+    names = probe_group_names("gloo")
+    assert names == [group_name_of()] and auto_group_name("gloo") == names[0]
+    assert probe_group_names("nccl") == []
+    assert resolve_group(names[0]) is not None
+    sub = dist.new_group(list(range(world)))                 # a second group: no automatic choice any more
+    try:
+        auto_group_name("gloo")
+    except RuntimeError as e:
+        assert "pass the group name" in str(e)
+    else:
+        raise AssertionError("two registered groups must not be resolved automatically")
+    r = torch.ops.tensorrt.fused_nccl_all_reduce(t, "sum", group_name_of(sub))
+    assert torch.allclose(r, torch.full((1, 4), world * (world + 1) / 2))
+
     # 2. the TP stack against the oracle's TP restatement (same arithmetic -> identical) and
     #    against the unsharded layer (different summation order / activation slices -> close)
     cfg = StackConfig(hidden=256, n_q=4, n_kv=2, head_dim=64, ffn=512, layers=2, mode=mode)
