@@ -77,6 +77,10 @@ int b200q_row_amax(const void* x, int dtype, int64_t rows, int64_t cols, float* 
  *   - All calls on a device share the one array: calls that can overlap on the GPU (two
  *     streams, two host threads) race with each other and give wrong results; serialise
  *     them or use b200q_amax with separate workspaces.
+ *   - The ticket counter in the array is re-armed by the last CTA of every launch.  A launch that
+ *     dies part-way (a fault elsewhere in the context) can leave it non-zero, and since the caller
+ *     cannot reach the array to clear it, later calls on that device then return wrong maxima:
+ *     after a failed launch treat the context as lost, as for any other sticky CUDA error.
  * Results are identical to b200q_amax. */
 int64_t b200q_amax_static_max_elements(void);
 int b200q_amax_static(const void* x, int dtype, int64_t n, float* amax_out, b200q_stream_t stream);
@@ -135,6 +139,35 @@ int b200q_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales_swizzled,
                            const float* global_scale, int64_t rows, int64_t cols, void* out,
                            int dtype, b200q_stream_t stream);
 
+/* ------------------------------------------------------------------ per-call options
+ * Last argument of the GEMM entry points and of the peer-memory reductions; NULL = all defaults.
+ * Nothing here is process-wide: two callers (threads, stacks, graphs) never see each other's choices.
+ *   tile_n          GEMM tile selection.  0 = chosen per problem (default); 128 or 256 = single-CTA
+ *                   tiles of 128 x tile_n; 512 = CTA-pair kernel (256 x 256 tiles, cta_group::2);
+ *                   1001 / 1002 / 1004 / 1008 = small-M kernel (weights on the tensor core's M side,
+ *                   K split over a cluster of 1 / 2 / 4 / 8 CTAs, partial tiles summed through
+ *                   distributed shared memory; chosen automatically for M <= 128, ignored for larger
+ *                   M).  Results do not depend on it beyond fp32 summation order.  Any other value:
+ *                   B200Q_ERR_INVALID.
+ *   static_weights  promise about the B operand (weights, their scales, the bias) of THIS call:
+ *                   non-zero = the work that wrote it has FINISHED on the device (weights quantized at
+ *                   load time, followed by a synchronisation), so no kernel still in flight when the
+ *                   GEMM starts can be writing it.  The small-M GEMM is launched programmatically
+ *                   dependent on its predecessor and through a chain of such launches may start while
+ *                   several earlier kernels still run; with the promise it requests its first weight
+ *                   tiles right away and waits for its predecessors only before reading the
+ *                   activations.  Without it (default) it waits before reading anything.
+ *   peer_wait_ms    limit of every device-side wait for another rank (flag words of the peer-memory
+ *                   reductions), in milliseconds; 0 = the default of 2000.  A wait that runs out sets
+ *                   the device status word (b200q_device_status) and the reduction skips its work.
+ */
+typedef struct b200q_cfg {
+  int32_t tile_n;
+  int32_t static_weights;
+  uint32_t peer_wait_ms;
+  uint32_t reserved;       /* must be 0 */
+} b200q_cfg;
+
 /* ------------------------------------------------------------------ quantized GEMMs (tcgen05)
  * Replace the IMatrixMultiplyLayer (+ bias add) TensorRT fuses with its Q/DQ neighbours
  * (impl/linear.py:40-67, impl/matmul.py:62-64):   out[m, n] = sum_k a[m,k] * b[n,k]  (+ bias[n])
@@ -149,11 +182,11 @@ int b200q_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales_swizzled,
 int b200q_fp8_gemm(const uint8_t* a_codes, const float* a_scales, int64_t a_scales_numel,
                    const uint8_t* b_codes, const float* b_scales, int64_t b_scales_numel,
                    const void* bias, void* out, int64_t M, int64_t N, int64_t K,
-                   b200q_stream_t stream);
+                   b200q_stream_t stream, const b200q_cfg* cfg);
 int b200q_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_scales, const float* a_global,
                      const uint8_t* b_codes, const uint8_t* b_scales, const float* b_global,
                      const void* bias, void* out, int64_t M, int64_t N, int64_t K,
-                     b200q_stream_t stream);
+                     b200q_stream_t stream, const b200q_cfg* cfg);
 
 /* ------------------------------------------------------------------ fused row-parallel linear (GEMM + all-reduce over peer memory)
  * Replaces "row-parallel linear, then tensorrt::fused_nccl_all_reduce" (the reference's
@@ -190,13 +223,13 @@ typedef struct b200q_peers {
 int b200q_fp8_gemm_reduce_scatter(const uint8_t* a_codes, const float* a_scales, int64_t a_scales_numel,
                                   const uint8_t* b_codes, const float* b_scales, int64_t b_scales_numel,
                                   const b200q_peers* peers, int64_t M, int64_t N, int64_t K,
-                                  b200q_stream_t stream);
+                                  b200q_stream_t stream, const b200q_cfg* cfg);
 int b200q_nvfp4_gemm_reduce_scatter(const uint8_t* a_codes, const uint8_t* a_scales, const float* a_global,
                                     const uint8_t* b_codes, const uint8_t* b_scales, const float* b_global,
                                     const b200q_peers* peers, int64_t M, int64_t N, int64_t K,
-                                    b200q_stream_t stream);
+                                    b200q_stream_t stream, const b200q_cfg* cfg);
 int b200q_reduce_gather(const b200q_peers* peers, const void* bias, int64_t M, int64_t N, uint32_t epoch,
-                        b200q_stream_t stream);
+                        b200q_stream_t stream, const b200q_cfg* cfg);
 
 /* Token-sharded residual stream (sequence-parallel form of the same TP plan,
  * tools/llm/tensor_parallel_llama_llm.py:134-157): every rank keeps the residual rows it owns
@@ -223,9 +256,9 @@ typedef struct b200q_gather_peers {
 
 int b200q_reduce_add_rms_norm_fp8_quantize_gather(const b200q_gather_peers* peers, const void* bias, void* h_shard,
                                                   const void* norm_weight, float eps, int64_t M, int64_t N,
-                                                  uint32_t epoch, b200q_stream_t stream);
+                                                  uint32_t epoch, b200q_stream_t stream, const b200q_cfg* cfg);
 int b200q_reduce_add_gather(const b200q_peers* peers, const void* bias, const void* residual_shard, int64_t M,
-                            int64_t N, uint32_t epoch, b200q_stream_t stream);
+                            int64_t N, uint32_t epoch, b200q_stream_t stream, const b200q_cfg* cfg);
 
 /* ------------------------------------------------------------------ glue of the decoder linear stack
  * The benchmark workloads wrap the quantized linears in a Llama-shaped decoder layer
@@ -256,23 +289,6 @@ int b200q_silu_mul_fp8_quantize(const void* gate_up, uint8_t* codes_out, float* 
 int b200q_add(const void* a, const void* b, void* out, int64_t n, b200q_stream_t stream);
 int b200q_expand_heads(const void* src, int64_t src_stride, int64_t src_col0, void* out, int64_t rows,
                        int heads_out, int rep, int head_dim, b200q_stream_t stream);
-
-/* Tile width of the GEMM kernels: 0 = chosen per problem (default), 128 or 256 = forced
- * single-CTA tiles of 128 x bn, 512 = forced CTA-pair kernel (256 x 256 tiles, cta_group::2),
- * 1001 / 1002 / 1004 / 1008 = forced small-M kernel (weights on the tensor core's M side, K
- * split over a cluster of 1 / 2 / 4 / 8 CTAs, partial tiles summed through distributed shared
- * memory; chosen automatically for M <= 128, ignored for larger M).
- * Process-wide tuning knob; results do not depend on it beyond fp32 summation order. */
-int b200q_gemm_set_tile_n(int bn);
-
-/* Promise about the B operand (weights, their scales, the bias) of the GEMM calls that follow, process-wide:
- * non-zero = the work that wrote it has FINISHED on the device (weights quantized at load time, followed by
- * a synchronisation), so no kernel still in flight when a GEMM starts can be writing it.  The small-M GEMM
- * is launched programmatically dependent on its predecessor, and through a chain of such launches may start
- * while several earlier kernels still run; with the promise it requests its first weight tiles right away
- * and waits for its predecessors only before reading the activations.  Without it (default) it waits before
- * reading anything. */
-int b200q_gemm_assume_static_weights(int on);
 
 /* The GEMM kernels bound every device-side wait; a wait that gives up records it in a
  * device status word instead of hanging.  This call synchronises with the device, returns

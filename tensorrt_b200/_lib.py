@@ -32,24 +32,34 @@ SIGNATURES = {
     "b200q_nvfp4_quantize": (_c.c_int, [_p, _c.c_int, _i64, _i64, _p, _p, _p, _p, _p]),
     "b200q_nvfp4_fake_quantize": (_c.c_int, [_p, _c.c_int, _i64, _i64, _p, _p, _p]),
     "b200q_nvfp4_dequantize": (_c.c_int, [_p, _p, _p, _i64, _i64, _p, _c.c_int, _p]),
-    "b200q_fp8_gemm": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _p]),
-    "b200q_nvfp4_gemm": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
-    "b200q_fp8_gemm_reduce_scatter": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _p]),
-    "b200q_nvfp4_gemm_reduce_scatter": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
-    "b200q_gemm_assume_static_weights": (_c.c_int, [_c.c_int]),
-    "b200q_reduce_gather": (_c.c_int, [_p, _p, _i64, _i64, _c.c_uint32, _p]),
-    "b200q_reduce_add_gather": (_c.c_int, [_p, _p, _p, _i64, _i64, _c.c_uint32, _p]),
-    "b200q_reduce_add_rms_norm_fp8_quantize_gather": (_c.c_int, [_p, _p, _p, _p, _c.c_float, _i64, _i64, _c.c_uint32, _p]),
+    "b200q_fp8_gemm": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _p, _p]),
+    "b200q_nvfp4_gemm": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _p]),
+    "b200q_fp8_gemm_reduce_scatter": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _p, _p]),
+    "b200q_nvfp4_gemm_reduce_scatter": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _p]),
+    "b200q_reduce_gather": (_c.c_int, [_p, _p, _i64, _i64, _c.c_uint32, _p, _p]),
+    "b200q_reduce_add_gather": (_c.c_int, [_p, _p, _p, _i64, _i64, _c.c_uint32, _p, _p]),
+    "b200q_reduce_add_rms_norm_fp8_quantize_gather": (_c.c_int, [_p, _p, _p, _p, _c.c_float, _i64, _i64, _c.c_uint32, _p, _p]),
     "b200q_rms_norm": (_c.c_int, [_p, _p, _p, _i64, _i64, _c.c_float, _p]),
     "b200q_add_rms_norm_fp8_quantize": (_c.c_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _c.c_float, _p]),
     "b200q_silu_mul": (_c.c_int, [_p, _p, _i64, _i64, _p]),
     "b200q_silu_mul_fp8_quantize": (_c.c_int, [_p, _p, _p, _i64, _i64, _p]),
     "b200q_add": (_c.c_int, [_p, _p, _p, _i64, _p]),
     "b200q_expand_heads": (_c.c_int, [_p, _i64, _i64, _p, _i64, _c.c_int, _c.c_int, _c.c_int, _p]),
-    "b200q_gemm_set_tile_n": (_c.c_int, [_c.c_int]),
     "b200q_device_status": (_c.c_int, [_c.c_int]),
 }
 
+
+
+class Cfg(ctypes.Structure):
+    """struct b200q_cfg of include/b200q.h: per-call options (NULL = defaults)."""
+    _fields_ = [("tile_n", _c.c_int32), ("static_weights", _c.c_int32), ("peer_wait_ms", _c.c_uint32), ("reserved", _c.c_uint32)]
+
+
+def cfg_ref(tile_n: int = 0, static_weights: bool = False, peer_wait_ms: int = 0):
+    """ctypes reference to a b200q_cfg, or None (NULL) when every field has its default."""
+    if not tile_n and not static_weights and not peer_wait_ms:
+        return None
+    return ctypes.byref(Cfg(int(tile_n), 1 if static_weights else 0, int(peer_wait_ms), 0))
 
 
 class Peers(ctypes.Structure):

@@ -5,9 +5,12 @@ pointers to `libb200q.so`.  These are the calls the GPU parity tests exercise.
 """
 from __future__ import annotations
 
+import contextlib
+import contextvars
+
 import torch
 
-from ._lib import check, load
+from ._lib import cfg_ref, check, load
 
 _DTYPE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
@@ -167,7 +170,30 @@ def nvfp4_dequantize(codes, scales, g, dtype=torch.float32) -> torch.Tensor:
     return out
 
 
-def fp8_gemm(a_codes, a_scales, b_codes, b_scales, bias=None) -> torch.Tensor:
+# Per-call GEMM options (struct b200q_cfg).  `gemm_config` sets the defaults the GEMM wrappers below
+# use inside a `with` block of the calling thread / task; nothing is process-wide.
+_gemm_cfg = contextvars.ContextVar("b200q_gemm_cfg", default=(0, False))
+
+
+@contextlib.contextmanager
+def gemm_config(tile_n: int | None = None, static_weights: bool | None = None):
+    """Defaults for `fp8_gemm` / `nvfp4_gemm` calls made inside the block by this thread:
+    `tile_n` forces a kernel / tile shape (b200q_cfg::tile_n), `static_weights` promises that the
+    weight operands were complete on the device before the call (b200q_cfg::static_weights)."""
+    cur = _gemm_cfg.get()
+    token = _gemm_cfg.set((cur[0] if tile_n is None else int(tile_n), cur[1] if static_weights is None else bool(static_weights)))
+    try:
+        yield
+    finally:
+        _gemm_cfg.reset(token)
+
+
+def _cfg(tile_n, static_weights):
+    cur = _gemm_cfg.get()
+    return cfg_ref(cur[0] if tile_n is None else tile_n, cur[1] if static_weights is None else static_weights)
+
+
+def fp8_gemm(a_codes, a_scales, b_codes, b_scales, bias=None, tile_n=None, static_weights=None) -> torch.Tensor:
     """bf16 [.., N] = dequant(a [.., K]) @ dequant(b [N, K])^T + bias."""
     _need_cuda(a_codes, a_scales, b_codes, b_scales, bias)
     a_codes, b_codes = a_codes.contiguous(), b_codes.contiguous()
@@ -179,11 +205,11 @@ def fp8_gemm(a_codes, a_scales, b_codes, b_scales, bias=None) -> torch.Tensor:
     with torch.cuda.device(a_codes.device):
         check(load().b200q_fp8_gemm(a_codes.data_ptr(), a_scales.data_ptr(), a_scales.numel(), b_codes.data_ptr(),
                                     b_scales.data_ptr(), b_scales.numel(), _ptr(bias), out.data_ptr(), M, N, K,
-                                    _stream(a_codes)), "b200q_fp8_gemm")
+                                    _stream(a_codes), _cfg(tile_n, static_weights)), "b200q_fp8_gemm")
     return out
 
 
-def nvfp4_gemm(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias=None) -> torch.Tensor:
+def nvfp4_gemm(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias=None, tile_n=None, static_weights=None) -> torch.Tensor:
     _need_cuda(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias)
     a_codes, b_codes = a_codes.contiguous(), b_codes.contiguous()
     N, half = b_codes.shape
@@ -195,7 +221,7 @@ def nvfp4_gemm(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias=No
     with torch.cuda.device(a_codes.device):
         check(load().b200q_nvfp4_gemm(a_codes.data_ptr(), a_scales.data_ptr(), a_global.data_ptr(), b_codes.data_ptr(),
                                       b_scales.data_ptr(), b_global.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
-                                      _stream(a_codes)), "b200q_nvfp4_gemm")
+                                      _stream(a_codes), _cfg(tile_n, static_weights)), "b200q_nvfp4_gemm")
     return out
 
 
@@ -283,16 +309,6 @@ def expand_heads(src: torch.Tensor, col0: int, heads_out: int, rep: int, head_di
         check(load().b200q_expand_heads(src.data_ptr(), width, col0, out.data_ptr(), rows, heads_out, rep, head_dim, _stream(src)),
               "b200q_expand_heads")
     return out
-
-
-def assume_static_weights(on: bool) -> None:
-    """Promise (process-wide, until revoked) that GEMM weights are older than the kernel launched just
-    before each GEMM: lets the small-M GEMM fetch weights while that kernel still runs."""
-    check(load().b200q_gemm_assume_static_weights(1 if on else 0), "b200q_gemm_assume_static_weights")
-
-
-def set_gemm_tile_n(bn: int) -> None:
-    check(load().b200q_gemm_set_tile_n(bn), "b200q_gemm_set_tile_n")
 
 
 def device_status(reset: bool = True) -> int:

@@ -1,7 +1,5 @@
 // FP8 E4M3 x E4M3 GEMM entry point (tcgen05 kind::f8f6f4) and the pieces shared by both
-// quantized GEMMs: the TMA descriptor encoder lookup, the device status word and the
-// tile-width override.
-#include <atomic>
+// quantized GEMMs: the TMA descriptor encoder lookup and the device status word.
 #include <cstdlib>
 #include <mutex>
 
@@ -12,7 +10,6 @@ namespace gemm {
 
 namespace {
 __device__ int g_device_status = 0;
-std::atomic<int> g_force_bn{0};
 std::mutex g_mu;
 int* g_status_addr[64] = {};
 }  // namespace
@@ -40,10 +37,9 @@ int* device_status_word() {
   return g_status_addr[dev];
 }
 
-int forced_bn() { return g_force_bn.load(); }
-
-std::atomic<int> g_static_weights{0};
-int static_weights_promised() { return g_static_weights.load(); }
+bool valid_tile_n(int bn) {
+  return bn == 0 || bn == 128 || bn == 256 || bn == 512 || bn == 1001 || bn == 1002 || bn == 1004 || bn == 1008;
+}
 
 int sf_copier_enabled() {
   static const int v = [] {
@@ -68,17 +64,6 @@ using namespace b200q;
 
 extern "C" {
 
-int b200q_gemm_set_tile_n(int bn) {
-  if (bn != 0 && bn != 128 && bn != 256 && bn != 512 && bn != 1001 && bn != 1002 && bn != 1004 && bn != 1008) return B200Q_ERR_INVALID;
-  gemm::g_force_bn.store(bn);
-  return B200Q_OK;
-}
-
-int b200q_gemm_assume_static_weights(int on) {
-  gemm::g_static_weights.store(on ? 1 : 0);
-  return B200Q_OK;
-}
-
 int b200q_device_status(int reset) {
   int* w = gemm::device_status_word();
   if (w == nullptr) return B200Q_ERR_CUDA;
@@ -93,9 +78,10 @@ int b200q_device_status(int reset) {
 
 int b200q_fp8_gemm(const uint8_t* a_codes, const float* a_scales, int64_t a_scales_numel, const uint8_t* b_codes,
                    const float* b_scales, int64_t b_scales_numel, const void* bias, void* out, int64_t M, int64_t N,
-                   int64_t K, b200q_stream_t stream) {
+                   int64_t K, b200q_stream_t stream, const b200q_cfg* cfg) {
   if (a_codes == nullptr || b_codes == nullptr || a_scales == nullptr || b_scales == nullptr || out == nullptr)
     return B200Q_ERR_INVALID;
+  if (cfg != nullptr && (!gemm::valid_tile_n(cfg->tile_n) || cfg->reserved != 0)) return B200Q_ERR_INVALID;
   if (M < 0 || N < 0 || K <= 0 || M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200Q_ERR_INVALID;
   if (K % 16 != 0) return B200Q_ERR_INVALID;
   if ((a_scales_numel != 1 && a_scales_numel != M) || (b_scales_numel != 1 && b_scales_numel != N)) return B200Q_ERR_INVALID;
@@ -112,7 +98,7 @@ int b200q_fp8_gemm(const uint8_t* a_codes, const float* a_scales, int64_t a_scal
   p.M = static_cast<int>(M);
   p.N = static_cast<int>(N);
   p.k_bytes = static_cast<int>(K);
-  return gemm::launch<false>(a_codes, b_codes, p, static_cast<cudaStream_t>(stream), gemm::forced_bn());
+  return gemm::launch<false>(a_codes, b_codes, p, static_cast<cudaStream_t>(stream), cfg);
 }
 
 static int fill_rs(gemm::Params& p, gemm::RsTargets& rs, const b200q_peers* peers, int64_t M) {
@@ -131,16 +117,17 @@ static int fill_rs(gemm::Params& p, gemm::RsTargets& rs, const b200q_peers* peer
 
 int b200q_fp8_gemm_reduce_scatter(const uint8_t* a_codes, const float* a_scales, int64_t a_scales_numel, const uint8_t* b_codes,
                                   const float* b_scales, int64_t b_scales_numel, const b200q_peers* peers, int64_t M, int64_t N,
-                                  int64_t K, b200q_stream_t stream) {
+                                  int64_t K, b200q_stream_t stream, const b200q_cfg* cfg) {
   if (a_codes == nullptr || b_codes == nullptr || a_scales == nullptr || b_scales == nullptr) return B200Q_ERR_INVALID;
+  if (cfg != nullptr && (!gemm::valid_tile_n(cfg->tile_n) || cfg->reserved != 0)) return B200Q_ERR_INVALID;
   if (M <= 0 || N <= 0 || K <= 0 || M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200Q_ERR_INVALID;
   if (K % 16 != 0 || N % 8 != 0) return B200Q_ERR_INVALID;
   if ((a_scales_numel != 1 && a_scales_numel != M) || (b_scales_numel != 1 && b_scales_numel != N)) return B200Q_ERR_INVALID;
   if (!aligned(a_codes, 16) || !aligned(b_codes, 16)) return B200Q_ERR_ALIGN;
-  if (int rc = check_arch()) return rc;
   gemm::Params p{};
   gemm::RsTargets rs{};
   if (int rc = fill_rs(p, rs, peers, M)) return rc;
+  if (int rc = check_arch()) return rc;
   p.a_scales = a_scales;
   p.b_scales = b_scales;
   p.a_scale_stride = a_scales_numel == 1 ? 0 : 1;
@@ -149,7 +136,7 @@ int b200q_fp8_gemm_reduce_scatter(const uint8_t* a_codes, const float* a_scales,
   p.M = static_cast<int>(M);
   p.N = static_cast<int>(N);
   p.k_bytes = static_cast<int>(K);
-  return gemm::launch<false>(a_codes, b_codes, p, static_cast<cudaStream_t>(stream), gemm::forced_bn(), &rs);
+  return gemm::launch<false>(a_codes, b_codes, p, static_cast<cudaStream_t>(stream), cfg, &rs);
 }
 
 }  // extern "C"

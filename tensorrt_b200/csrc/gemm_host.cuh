@@ -217,21 +217,21 @@ inline int smallm_splits(int n_tiles, int k_tiles, int sms) {
   return s;
 }
 
-int static_weights_promised();   // b200q_gemm_assume_static_weights
+bool valid_tile_n(int bn);    // values b200q_cfg::tile_n accepts
 int sf_copier_enabled();     // environment variable B200Q_SF_COPIER (default in gemm_fp8.cu)
 int forced_smallm_stages();  // from the environment variable B200Q_SMALLM_STAGES (0 when unset)
 
-// Tile width: 256 when that still gives every SM a tile, else 128.  `force_bn` (128 / 256)
+// Tile width: 256 when that still gives every SM a tile, else 128.  `cfg->tile_n` (128 / 256)
 // overrides the choice (used by tests to cover both instantiations); 512 forces the CTA-pair
 // kernel (256 x 256 tiles), which is otherwise used when there are at least sm_count/2 such tiles.
 // M <= 128 goes to the small-M kernel unless a tile width is forced.
 template <bool NVF4>
-int launch(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, int force_bn, const RsTargets* rs = nullptr) {
+int launch(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, const b200q_cfg* cfg, const RsTargets* rs = nullptr) {
   p.status = device_status_word();
   if (p.status == nullptr) return B200Q_ERR_CUDA;
   p.sf_copier = NVF4 ? sf_copier_enabled() : 0;
-  p.static_weights = static_weights_promised();
-  int bn = force_bn;
+  p.static_weights = (cfg != nullptr && cfg->static_weights != 0) ? 1 : 0;
+  int bn = cfg != nullptr ? cfg->tile_n : 0;
   const int k_tiles = (p.k_bytes + kBKBytes - 1) / kBKBytes;
   if (rs == nullptr && p.M <= kBM) {
     // small M: weights are streamed once; the swapped-operand cluster kernel handles it
@@ -252,8 +252,6 @@ int launch(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, int fo
   }
   return bn == 256 ? launch_tile<NVF4, 256>(a, b, p, st, rs) : launch_tile<NVF4, 128>(a, b, p, st, rs);
 }
-
-int forced_bn();  // from the environment variable B200Q_GEMM_BN (0 when unset)
 
 }  // namespace gemm
 }  // namespace b200q

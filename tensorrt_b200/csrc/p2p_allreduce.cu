@@ -12,8 +12,8 @@
 // A runs as its own single-warp launch in front of the reduction (see exchange_flags_kernel).
 // Flags are 32-bit epoch numbers in each rank's flag words (2 * world + 1 words, zeroed once):
 // word s of rank r = "rank s finished phase A", word world + s = "... phase C", last word =
-// block ticket.  Every wait is bounded (2 s); a wait that gives up records it in the device
-// status word and the kernel returns without touching the output again.
+// block ticket.  Every wait is bounded (b200q_cfg::peer_wait_ms, default 2 s); a wait that gives up
+// records it in the device status word and the kernel returns without touching the output again.
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -42,15 +42,15 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-// true when *p has reached `epoch` within the time limit
-__device__ __forceinline__ bool wait_epoch(const uint32_t* p, uint32_t epoch) {
+// true when *p has reached `epoch` within `limit_ns`
+__device__ __forceinline__ bool wait_epoch(const uint32_t* p, uint32_t epoch, uint64_t limit_ns) {
   uint64_t t0 = 0;
   for (uint32_t i = 0;; ++i) {
     if (static_cast<int32_t>(ld_acquire_sys(p) - epoch) >= 0) return true;
-    if ((i & 0xffu) == 0xffu) {
+    if ((i & 0x3fu) == 0x3fu) {
       const uint64_t now = ptx::globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > ptx::kWaitLimitNs) return false;
+      else if (now - t0 > limit_ns) return false;
     }
   }
 }
@@ -63,17 +63,17 @@ struct FlagPeers {
   uint32_t* flags[8];
 };
 
-__global__ void __launch_bounds__(32) exchange_flags_kernel(const FlagPeers fp, uint32_t epoch, int* status) {
+__global__ void __launch_bounds__(32) exchange_flags_kernel(const FlagPeers fp, uint32_t epoch, uint64_t limit_ns, int* status) {
   if (threadIdx.x < fp.world) {
     __threadfence_system();
     st_release_sys(fp.flags[threadIdx.x] + fp.rank, epoch);
-    if (!wait_epoch(fp.flags[fp.rank] + threadIdx.x, epoch)) atomicCAS(status, 0, 21);
+    if (!wait_epoch(fp.flags[fp.rank] + threadIdx.x, epoch, limit_ns)) atomicCAS(status, 0, 21);
   }
 }
 
 __global__ void __launch_bounds__(kThreads)
 reduce_gather_kernel(const Peers pr, const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
-                     int64_t rows_per, int64_t N, uint32_t epoch, int* status) {
+                     int64_t rows_per, int64_t N, uint32_t epoch, uint64_t limit_ns, int* status) {
   __shared__ int s_last;
   const int W = pr.world;
   uint32_t* my_flags = pr.flags[pr.rank];
@@ -134,11 +134,14 @@ reduce_gather_kernel(const Peers pr, const __nv_bfloat16* __restrict__ bias, con
   __syncthreads();
   if (s_last) {
     if (threadIdx.x == 0) my_flags[2 * W] = 0u;  // re-arm the ticket
-    if (ok) {
+    // Every CTA read the status word on its own; one that came late may have skipped its rows
+    // after an earlier CTA had seen 0.  The word is never cleared on the device, so reading it
+    // again here tells whether ALL CTAs did their work: only then are the peers told so.
+    if (ok && *reinterpret_cast<volatile int*>(status) == 0) {
       if (threadIdx.x < W) {
         __threadfence_system();
         st_release_sys(pr.flags[threadIdx.x] + W + pr.rank, epoch);
-        if (!wait_epoch(my_flags + W + threadIdx.x, epoch)) atomicCAS(status, 0, 22);
+        if (!wait_epoch(my_flags + W + threadIdx.x, epoch, limit_ns)) atomicCAS(status, 0, 22);
       }
     }
   }
@@ -160,7 +163,7 @@ template <int ITEMS>
 __global__ void __launch_bounds__(kThreads)
 reduce_norm_quant_gather_kernel(const GatherPeers pr, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ h,
                                 const __nv_bfloat16* __restrict__ w, int64_t rows_per, int64_t N, float eps, uint32_t epoch,
-                                int* status) {
+                                uint64_t limit_ns, int* status) {
   __shared__ int s_last;
   __shared__ float red[kThreads / 32];
   const int W = pr.world;
@@ -261,11 +264,14 @@ reduce_norm_quant_gather_kernel(const GatherPeers pr, const __nv_bfloat16* __res
   __syncthreads();
   if (s_last) {
     if (threadIdx.x == 0) my_flags[2 * W] = 0u;  // re-arm the ticket
-    if (ok) {
+    // Every CTA read the status word on its own; one that came late may have skipped its rows
+    // after an earlier CTA had seen 0.  The word is never cleared on the device, so reading it
+    // again here tells whether ALL CTAs did their work: only then are the peers told so.
+    if (ok && *reinterpret_cast<volatile int*>(status) == 0) {
       if (threadIdx.x < W) {
         __threadfence_system();
         st_release_sys(pr.flags[threadIdx.x] + W + pr.rank, epoch);
-        if (!wait_epoch(my_flags + W + threadIdx.x, epoch)) atomicCAS(status, 0, 24);
+        if (!wait_epoch(my_flags + W + threadIdx.x, epoch, limit_ns)) atomicCAS(status, 0, 24);
       }
     }
   }
@@ -278,9 +284,17 @@ using namespace b200q;
 
 extern "C" {
 
+// b200q_cfg::peer_wait_ms -> nanoseconds (0 / no cfg: the library default)
+static uint64_t peer_wait_ns(const b200q_cfg* cfg) {
+  if (cfg == nullptr || cfg->peer_wait_ms == 0) return ptx::kWaitLimitNs;
+  return static_cast<uint64_t>(cfg->peer_wait_ms) * 1000000ull;
+}
+
 static int reduce_gather_impl(const b200q_peers* peers, const void* bias, const void* residual, int64_t M, int64_t N, uint32_t epoch,
-                              b200q_stream_t stream) {
+                              b200q_stream_t stream, const b200q_cfg* cfg) {
   if (peers == nullptr || M <= 0 || N <= 0 || N % 8 != 0) return B200Q_ERR_INVALID;
+  if (cfg != nullptr && cfg->reserved != 0) return B200Q_ERR_INVALID;
+  const uint64_t limit_ns = peer_wait_ns(cfg);
   const int W = peers->world;
   if (W < 1 || W > 8 || peers->rank < 0 || peers->rank >= W || M % (static_cast<int64_t>(W) * 128) != 0) return B200Q_ERR_INVALID;
   Peers pr{};
@@ -306,27 +320,30 @@ static int reduce_gather_impl(const b200q_peers* peers, const void* bias, const 
   fp.rank = pr.rank;
   fp.world = W;
   for (int r = 0; r < W; ++r) fp.flags[r] = pr.flags[r];
-  exchange_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(fp, epoch, status);
+  exchange_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(fp, epoch, limit_ns, status);
   reduce_gather_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      pr, static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(residual), rows_per, N, epoch, status);
+      pr, static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(residual), rows_per, N, epoch, limit_ns, status);
   return check_launch();
 }
 
-int b200q_reduce_gather(const b200q_peers* peers, const void* bias, int64_t M, int64_t N, uint32_t epoch, b200q_stream_t stream) {
-  return reduce_gather_impl(peers, bias, nullptr, M, N, epoch, stream);
+int b200q_reduce_gather(const b200q_peers* peers, const void* bias, int64_t M, int64_t N, uint32_t epoch, b200q_stream_t stream,
+                        const b200q_cfg* cfg) {
+  return reduce_gather_impl(peers, bias, nullptr, M, N, epoch, stream, cfg);
 }
 
 int b200q_reduce_add_gather(const b200q_peers* peers, const void* bias, const void* residual_shard, int64_t M, int64_t N,
-                            uint32_t epoch, b200q_stream_t stream) {
+                            uint32_t epoch, b200q_stream_t stream, const b200q_cfg* cfg) {
   if (residual_shard == nullptr) return B200Q_ERR_INVALID;
-  return reduce_gather_impl(peers, bias, residual_shard, M, N, epoch, stream);
+  return reduce_gather_impl(peers, bias, residual_shard, M, N, epoch, stream, cfg);
 }
 
 int b200q_reduce_add_rms_norm_fp8_quantize_gather(const b200q_gather_peers* peers, const void* bias, void* h_shard,
                                                   const void* norm_weight, float eps, int64_t M, int64_t N, uint32_t epoch,
-                                                  b200q_stream_t stream) {
+                                                  b200q_stream_t stream, const b200q_cfg* cfg) {
   if (peers == nullptr || h_shard == nullptr || norm_weight == nullptr || M <= 0 || N <= 0 || N % 16 != 0 || N > 16384)
     return B200Q_ERR_INVALID;
+  if (cfg != nullptr && cfg->reserved != 0) return B200Q_ERR_INVALID;
+  const uint64_t limit_ns = peer_wait_ns(cfg);
   const int W = peers->world;
   if (W < 1 || W > 8 || peers->rank < 0 || peers->rank >= W || M % (static_cast<int64_t>(W) * 128) != 0) return B200Q_ERR_INVALID;
   GatherPeers pr{};
@@ -359,11 +376,11 @@ int b200q_reduce_add_rms_norm_fp8_quantize_gather(const b200q_gather_peers* peer
   fp.rank = pr.rank;
   fp.world = W;
   for (int r = 0; r < W; ++r) fp.flags[r] = pr.flags[r];
-  exchange_flags_kernel<<<1, 32, 0, st>>>(fp, epoch, status);
-  if (items <= 1) reduce_norm_quant_gather_kernel<1><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, status);
-  else if (items <= 2) reduce_norm_quant_gather_kernel<2><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, status);
-  else if (items <= 4) reduce_norm_quant_gather_kernel<4><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, status);
-  else reduce_norm_quant_gather_kernel<8><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, status);
+  exchange_flags_kernel<<<1, 32, 0, st>>>(fp, epoch, limit_ns, status);
+  if (items <= 1) reduce_norm_quant_gather_kernel<1><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, limit_ns, status);
+  else if (items <= 2) reduce_norm_quant_gather_kernel<2><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, limit_ns, status);
+  else if (items <= 4) reduce_norm_quant_gather_kernel<4><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, limit_ns, status);
+  else reduce_norm_quant_gather_kernel<8><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, limit_ns, status);
   return check_launch();
 }
 

@@ -205,7 +205,7 @@ Tensor fp8_gemm_cuda(const Tensor& a_codes, const Tensor& a_scales, const Tensor
   if (out.numel() == 0) return out;
   check_status(b200q_fp8_gemm(a.data_ptr<uint8_t>(), sa.data_ptr<float>(), sa.numel(), b.data_ptr<uint8_t>(),
                               sb.data_ptr<float>(), sb.numel(), bias.has_value() ? bs.data_ptr() : nullptr, out.data_ptr(),
-                              M, N, K, current_stream()),
+                              M, N, K, current_stream(), nullptr),
                "b200q_fp8_gemm");
   return out;
 }
@@ -239,7 +239,7 @@ Tensor nvfp4_gemm_cuda(const Tensor& a_codes, const Tensor& a_scales, const Tens
   if (out.numel() == 0) return out;
   check_status(b200q_nvfp4_gemm(a.data_ptr<uint8_t>(), sa.data_ptr<uint8_t>(), ga.data_ptr<float>(), b.data_ptr<uint8_t>(),
                                 sb.data_ptr<uint8_t>(), gb.data_ptr<float>(), bias.has_value() ? bs.data_ptr() : nullptr,
-                                out.data_ptr(), M, N, K, current_stream()),
+                                out.data_ptr(), M, N, K, current_stream(), nullptr),
                "b200q_nvfp4_gemm");
   return out;
 }
@@ -248,6 +248,107 @@ Tensor nvfp4_gemm_meta(const Tensor& a_codes, const Tensor&, const Tensor&, cons
   auto shape = a_codes.sizes().vec();
   shape.back() = b_codes.size(0);
   return at::empty(shape, a_codes.options().dtype(at::kBFloat16));
+}
+
+// Schema variants without optional arguments: the reference's plugin generator accepts only
+// Tensor / float / int / bool / str arguments
+// (py/torch_tensorrt/dynamo/conversion/plugins/_generate_plugin.py:131-158).
+Tensor fp8_gemm_nobias_cuda(const Tensor& a, const Tensor& sa, const Tensor& b, const Tensor& sb) {
+  return fp8_gemm_cuda(a, sa, b, sb, std::nullopt);
+}
+Tensor fp8_gemm_bias_cuda(const Tensor& a, const Tensor& sa, const Tensor& b, const Tensor& sb, const Tensor& bias) {
+  return fp8_gemm_cuda(a, sa, b, sb, bias);
+}
+Tensor fp8_gemm_nobias_meta(const Tensor& a, const Tensor& sa, const Tensor& b, const Tensor& sb) {
+  return fp8_gemm_meta(a, sa, b, sb, std::nullopt);
+}
+Tensor fp8_gemm_bias_meta(const Tensor& a, const Tensor& sa, const Tensor& b, const Tensor& sb, const Tensor&) {
+  return fp8_gemm_meta(a, sa, b, sb, std::nullopt);
+}
+Tensor nvfp4_gemm_nobias_cuda(const Tensor& a, const Tensor& sa, const Tensor& ga, const Tensor& b, const Tensor& sb, const Tensor& gb) {
+  return nvfp4_gemm_cuda(a, sa, ga, b, sb, gb, std::nullopt);
+}
+Tensor nvfp4_gemm_bias_cuda(const Tensor& a, const Tensor& sa, const Tensor& ga, const Tensor& b, const Tensor& sb, const Tensor& gb,
+                            const Tensor& bias) {
+  return nvfp4_gemm_cuda(a, sa, ga, b, sb, gb, bias);
+}
+Tensor nvfp4_gemm_nobias_meta(const Tensor& a, const Tensor& sa, const Tensor& ga, const Tensor& b, const Tensor& sb, const Tensor& gb) {
+  return nvfp4_gemm_meta(a, sa, ga, b, sb, gb, std::nullopt);
+}
+Tensor nvfp4_gemm_bias_meta(const Tensor& a, const Tensor& sa, const Tensor& ga, const Tensor& b, const Tensor& sb, const Tensor& gb,
+                            const Tensor&) {
+  return nvfp4_gemm_meta(a, sa, ga, b, sb, gb, std::nullopt);
+}
+
+// ------------------------------------------------------------------ one-node quantized linears (the plugin form)
+// y = linear(Q(x), W_hat, bias) with the weight already reduced to codes and scales: what the three
+// nodes quantize_op(x), quantize_op(W), aten.linear collapse to once the weight is a constant.
+// All arguments are tensors and the activation comes first, so the generated TensorRT plugin's
+// output descriptor (`tensor_args[0].like()`, plugins/_generate_plugin.py:263) has the right
+// dtype: the result is returned in x's dtype, like the DQ output of the reference
+// (impl/quantize.py:132-134).  x_amax: one value (per-tensor, impl/quantize.py:96-100), one per
+// token, or an empty tensor (per-token abs-max measured by the quantize kernel).
+Tensor fp8_linear_impl(const Tensor& x_in, const Tensor& x_amax, const Tensor& w_codes, const Tensor& w_scales,
+                       const std::optional<Tensor>& bias) {
+  const int dt = dtype_code(x_in, "b200_fp8_linear");
+  TORCH_CHECK(w_codes.dim() == 2 && x_in.dim() >= 1 && x_in.size(-1) == w_codes.size(1),
+              "b200_fp8_linear: x [.., K] and w_codes [N, K] must share K, got ", x_in.sizes(), " and ", w_codes.sizes());
+  c10::cuda::CUDAGuard guard(x_in.device());
+  Tensor x = x_in.contiguous();
+  const int64_t rows = rows_of(x), cols = cols_of(x);
+  TORCH_CHECK(cols % 16 == 0, "b200_fp8_linear: K must be a multiple of 16, got ", cols);
+  int64_t n = 0;
+  Tensor a;
+  if (x_amax.numel() > 0) {
+    a = as_f32_cuda(x_amax, x);
+    n = amax_numel_for(x, a, "b200_fp8_linear");
+  }
+  Tensor codes = at::empty(x.sizes(), x.options().dtype(at::kByte));
+  Tensor scales = at::empty({n == 1 ? 1 : rows}, x.options().dtype(at::kFloat));
+  if (x.numel() > 0)
+    check_status(b200q_fp8_quantize(x.data_ptr(), dt, rows, cols, n ? a.data_ptr<float>() : nullptr, n,
+                                    codes.data_ptr<uint8_t>(), scales.data_ptr<float>(), current_stream()),
+                 "b200q_fp8_quantize");
+  Tensor out = fp8_gemm_cuda(codes, scales, w_codes, w_scales, bias);
+  return out.scalar_type() == x.scalar_type() ? out : out.to(x.scalar_type());
+}
+Tensor fp8_linear_cuda(const Tensor& x, const Tensor& x_amax, const Tensor& w_codes, const Tensor& w_scales) {
+  return fp8_linear_impl(x, x_amax, w_codes, w_scales, std::nullopt);
+}
+Tensor fp8_linear_bias_cuda(const Tensor& x, const Tensor& x_amax, const Tensor& w_codes, const Tensor& w_scales, const Tensor& bias) {
+  return fp8_linear_impl(x, x_amax, w_codes, w_scales, bias);
+}
+Tensor linear_meta_like(const Tensor& x, const Tensor& w_codes) {
+  auto shape = x.sizes().vec();
+  shape.back() = w_codes.size(0);
+  return at::empty(shape, x.options());
+}
+Tensor fp8_linear_meta(const Tensor& x, const Tensor&, const Tensor& w_codes, const Tensor&) { return linear_meta_like(x, w_codes); }
+Tensor fp8_linear_bias_meta(const Tensor& x, const Tensor&, const Tensor& w_codes, const Tensor&, const Tensor&) {
+  return linear_meta_like(x, w_codes);
+}
+
+Tensor nvfp4_linear_impl(const Tensor& x_in, const Tensor& x_amax, const Tensor& w_codes, const Tensor& w_scales,
+                         const Tensor& w_global, const std::optional<Tensor>& bias) {
+  TORCH_CHECK(w_codes.dim() == 2 && x_in.dim() >= 1 && x_in.size(-1) == 2 * w_codes.size(1),
+              "b200_nvfp4_linear: x [.., K] and w_codes [N, K/2] must share K, got ", x_in.sizes(), " and ", w_codes.sizes());
+  TORCH_CHECK_VALUE(cols_of(x_in) % 32 == 0, "b200_nvfp4_linear: K must be a multiple of 32, got ", cols_of(x_in));
+  auto q = nvfp4_quantize_cuda(x_in, x_amax);
+  Tensor out = nvfp4_gemm_cuda(std::get<0>(q), std::get<1>(q), std::get<2>(q), w_codes, w_scales, w_global, bias);
+  return out.scalar_type() == x_in.scalar_type() ? out : out.to(x_in.scalar_type());
+}
+Tensor nvfp4_linear_cuda(const Tensor& x, const Tensor& x_amax, const Tensor& w_codes, const Tensor& w_scales, const Tensor& w_global) {
+  return nvfp4_linear_impl(x, x_amax, w_codes, w_scales, w_global, std::nullopt);
+}
+Tensor nvfp4_linear_bias_cuda(const Tensor& x, const Tensor& x_amax, const Tensor& w_codes, const Tensor& w_scales,
+                              const Tensor& w_global, const Tensor& bias) {
+  return nvfp4_linear_impl(x, x_amax, w_codes, w_scales, w_global, bias);
+}
+Tensor nvfp4_linear_meta(const Tensor& x, const Tensor&, const Tensor& w_codes, const Tensor&, const Tensor&) {
+  return linear_meta_like(x, w_codes);
+}
+Tensor nvfp4_linear_bias_meta(const Tensor& x, const Tensor&, const Tensor& w_codes, const Tensor&, const Tensor&, const Tensor&) {
+  return linear_meta_like(x, w_codes);
 }
 
 bool schema_exists(const char* name) {
@@ -292,13 +393,34 @@ TORCH_LIBRARY_FRAGMENT(tensorrt, m) {
   m.impl("b200_nvfp4_quantize", c10::DispatchKey::CUDA, TORCH_FN(nvfp4_quantize_cuda));
   m.impl("b200_nvfp4_quantize", c10::DispatchKey::Meta, TORCH_FN(nvfp4_quantize_meta));
 
-  m.def("b200_fp8_gemm(Tensor a_codes, Tensor a_scales, Tensor b_codes, Tensor b_scales, Tensor? bias) -> Tensor");
-  m.impl("b200_fp8_gemm", c10::DispatchKey::CUDA, TORCH_FN(fp8_gemm_cuda));
-  m.impl("b200_fp8_gemm", c10::DispatchKey::Meta, TORCH_FN(fp8_gemm_meta));
-
+  // GEMMs on quantized operands: a variant with and one without bias, no optional arguments
+  m.def("b200_fp8_gemm(Tensor a_codes, Tensor a_scales, Tensor b_codes, Tensor b_scales) -> Tensor");
+  m.impl("b200_fp8_gemm", c10::DispatchKey::CUDA, TORCH_FN(fp8_gemm_nobias_cuda));
+  m.impl("b200_fp8_gemm", c10::DispatchKey::Meta, TORCH_FN(fp8_gemm_nobias_meta));
+  m.def("b200_fp8_gemm_bias(Tensor a_codes, Tensor a_scales, Tensor b_codes, Tensor b_scales, Tensor bias) -> Tensor");
+  m.impl("b200_fp8_gemm_bias", c10::DispatchKey::CUDA, TORCH_FN(fp8_gemm_bias_cuda));
+  m.impl("b200_fp8_gemm_bias", c10::DispatchKey::Meta, TORCH_FN(fp8_gemm_bias_meta));
+  m.def("b200_nvfp4_gemm(Tensor a_codes, Tensor a_scales, Tensor a_global, Tensor b_codes, Tensor b_scales, Tensor b_global) -> Tensor");
+  m.impl("b200_nvfp4_gemm", c10::DispatchKey::CUDA, TORCH_FN(nvfp4_gemm_nobias_cuda));
+  m.impl("b200_nvfp4_gemm", c10::DispatchKey::Meta, TORCH_FN(nvfp4_gemm_nobias_meta));
   m.def(
-      "b200_nvfp4_gemm(Tensor a_codes, Tensor a_scales, Tensor a_global, Tensor b_codes, Tensor b_scales, Tensor b_global, "
-      "Tensor? bias) -> Tensor");
-  m.impl("b200_nvfp4_gemm", c10::DispatchKey::CUDA, TORCH_FN(nvfp4_gemm_cuda));
-  m.impl("b200_nvfp4_gemm", c10::DispatchKey::Meta, TORCH_FN(nvfp4_gemm_meta));
+      "b200_nvfp4_gemm_bias(Tensor a_codes, Tensor a_scales, Tensor a_global, Tensor b_codes, Tensor b_scales, Tensor b_global, "
+      "Tensor bias) -> Tensor");
+  m.impl("b200_nvfp4_gemm_bias", c10::DispatchKey::CUDA, TORCH_FN(nvfp4_gemm_bias_cuda));
+  m.impl("b200_nvfp4_gemm_bias", c10::DispatchKey::Meta, TORCH_FN(nvfp4_gemm_bias_meta));
+
+  // One-node quantized linears (activation first, result in the activation's dtype): the ops handed
+  // to torch_tensorrt.dynamo.conversion.plugins.custom_op.
+  m.def("b200_fp8_linear(Tensor x, Tensor x_amax, Tensor w_codes, Tensor w_scales) -> Tensor");
+  m.impl("b200_fp8_linear", c10::DispatchKey::CUDA, TORCH_FN(fp8_linear_cuda));
+  m.impl("b200_fp8_linear", c10::DispatchKey::Meta, TORCH_FN(fp8_linear_meta));
+  m.def("b200_fp8_linear_bias(Tensor x, Tensor x_amax, Tensor w_codes, Tensor w_scales, Tensor bias) -> Tensor");
+  m.impl("b200_fp8_linear_bias", c10::DispatchKey::CUDA, TORCH_FN(fp8_linear_bias_cuda));
+  m.impl("b200_fp8_linear_bias", c10::DispatchKey::Meta, TORCH_FN(fp8_linear_bias_meta));
+  m.def("b200_nvfp4_linear(Tensor x, Tensor x_amax, Tensor w_codes, Tensor w_scales, Tensor w_global) -> Tensor");
+  m.impl("b200_nvfp4_linear", c10::DispatchKey::CUDA, TORCH_FN(nvfp4_linear_cuda));
+  m.impl("b200_nvfp4_linear", c10::DispatchKey::Meta, TORCH_FN(nvfp4_linear_meta));
+  m.def("b200_nvfp4_linear_bias(Tensor x, Tensor x_amax, Tensor w_codes, Tensor w_scales, Tensor w_global, Tensor bias) -> Tensor");
+  m.impl("b200_nvfp4_linear_bias", c10::DispatchKey::CUDA, TORCH_FN(nvfp4_linear_bias_cuda));
+  m.impl("b200_nvfp4_linear_bias", c10::DispatchKey::Meta, TORCH_FN(nvfp4_linear_bias_meta));
 }

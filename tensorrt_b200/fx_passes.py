@@ -11,7 +11,15 @@ does that fusion on the graph itself:
     y  = linear(xq, wq, b)                                     wc, ws = b200_fp8_quantize(W, aw)
                                                                y = b200_fp8_gemm(xc, xs, wc, ws, b)
 
-(`mm(xq, wq.t())`, `matmul(xq, wq.t())` and `addmm(b, xq, wq.t())` are recognised as the same linear)
+(`mm(xq, wq.t())`, `matmul(xq, wq.t())` and `addmm(b, xq, wq.t(), beta=, alpha=)` are recognised as the
+same linear: they are what `aten.linear` decomposes to in the reference's distributed mode,
+py/torch_tensorrt/dynamo/lowering/_decompositions.py:738-745; with `alpha`/`beta` other than 1 the
+scaling of py/torch_tensorrt/dynamo/conversion/impl/addmm.py:12-34 is kept as separate nodes after
+the GEMM.)  Linears that share one activation quantizer (q/k/v, gate/up) share one inserted
+quantize node.  With `plugin_form=True` and a constant weight each linear becomes ONE node,
+`b200_fp8_linear[_bias](x, ax, wc, ws[, b])`, whose arguments are all tensors with the activation
+first and whose result has the activation's dtype: the form
+`torch_tensorrt.dynamo.conversion.plugins.custom_op` can turn into a TensorRT plugin.
 
 and the same with `dynamic_block_quantize_op(.., 16, amax, 4, 2, 8, 4)` -> `b200_nvfp4_*`.
 The fake-quantized bf16 tensors are never materialised; the result differs from the unfused
@@ -63,39 +71,66 @@ def _transposed(node):
 
 
 def _as_linear(node: fx.Node):
-    """(input, weight, bias) when `node` computes input @ weight^T (+ bias) in one of the forms the
-    reference converts (aten_ops_converters.py:4197-4213 linear, :779-799 matmul, :3477-3500 addmm,
-    the form `aten.linear` decomposes to in distributed mode), else None."""
+    """(input, weight, bias, alpha, beta) when `node` computes alpha * (input @ weight^T) + beta * bias in
+    one of the forms the reference converts (aten_ops_converters.py:4197-4213 linear, :779-799 matmul,
+    :3477-3500 addmm, the form `aten.linear` decomposes to in distributed mode), else None."""
     if node.op != "call_function":
         return None
     a = torch.ops.aten
     if node.target in _linear_targets() and len(node.args) >= 2:
-        return node.args[0], node.args[1], (node.args[2] if len(node.args) > 2 else node.kwargs.get("bias"))
+        return node.args[0], node.args[1], (node.args[2] if len(node.args) > 2 else node.kwargs.get("bias")), 1, 1
     if node.target in (a.mm, a.mm.default, a.matmul, a.matmul.default, torch.matmul, torch.mm) and len(node.args) == 2:
         w = _transposed(node.args[1])
-        return (node.args[0], w, None) if w is not None else None
-    if node.target in (a.addmm, a.addmm.default, torch.addmm) and len(node.args) == 3 and not node.kwargs:
+        return (node.args[0], w, None, 1, 1) if w is not None else None
+    if node.target in (a.addmm, a.addmm.default, torch.addmm) and len(node.args) == 3:
+        if set(node.kwargs) - {"alpha", "beta"}:
+            return None
+        alpha, beta = node.kwargs.get("alpha", 1), node.kwargs.get("beta", 1)
+        if not isinstance(alpha, (int, float)) or not isinstance(beta, (int, float)):
+            return None
         w = _transposed(node.args[2])
-        return (node.args[1], w, node.args[0]) if w is not None else None
+        return (node.args[1], w, node.args[0], alpha, beta) if w is not None else None
     return None
 
 
+def _bound_args(node: fx.Node, packet):
+    """Arguments of an op node by schema name (positional and keyword forms alike), or None."""
+    schema = packet.default._schema
+    names = [a.name for a in schema.arguments]
+    if len(node.args) > len(names) or set(node.kwargs) - set(names):
+        return None
+    bound = dict(zip(names, node.args))
+    for k, v in node.kwargs.items():
+        if k in bound:
+            return None
+        bound[k] = v
+    for a in schema.arguments:
+        if a.name not in bound:
+            if not a.has_default_value():
+                return None
+            bound[a.name] = a.default_value
+    return [bound[n] for n in names]
+
+
 def _match_fp8(node: fx.Node):
-    """quantize_op(input, amax, 8, 4, unsigned=False, narrow_range=False) -> (input, amax)."""
-    if not _is_op(node, torch.ops.tensorrt.quantize_op) or len(node.args) < 4:
+    """quantize_op(input, amax, 8, 4, unsigned=False, narrow_range=False) -> (input, amax).  The
+    signed, full-range E4M3 case only: anything else is left to the unfused graph."""
+    if not _is_op(node, torch.ops.tensorrt.quantize_op):
         return None
-    if tuple(node.args[2:4]) != _FP8_ARGS:
+    args = _bound_args(node, torch.ops.tensorrt.quantize_op)
+    if args is None or tuple(args[2:4]) != _FP8_ARGS or args[4] is not False or args[5] is not False:
         return None
-    return node.args[0], node.args[1]
+    return args[0], args[1]
 
 
 def _match_nvfp4(node: fx.Node):
     """dynamic_block_quantize_op(input, 16, amax, 4, 2, 8, 4) -> (input, amax)."""
-    if not _is_op(node, torch.ops.tensorrt.dynamic_block_quantize_op) or len(node.args) < 7:
+    if not _is_op(node, torch.ops.tensorrt.dynamic_block_quantize_op):
         return None
-    if (node.args[1],) + tuple(node.args[3:7]) != _NVFP4_ARGS:
+    args = _bound_args(node, torch.ops.tensorrt.dynamic_block_quantize_op)
+    if args is None or (args[1],) + tuple(args[3:7]) != _NVFP4_ARGS:
         return None
-    return node.args[0], node.args[2]
+    return args[0], args[2]
 
 
 def _const_tensor(gm: fx.GraphModule, node):
@@ -118,22 +153,45 @@ def _out_dtype(node: fx.Node):
     return getattr(tm, "dtype", None)
 
 
-def fuse_quantized_linear(gm: fx.GraphModule, fold_weights: bool = True) -> int:
+def _drop_unused_constant(gm: fx.GraphModule, node) -> None:
+    """Delete the module attribute behind a get_attr node that nothing in the graph reads any more
+    (the bf16 weight of a linear whose codes were folded in: keeping it would double weight memory)."""
+    if not isinstance(node, fx.Node) or node.op != "get_attr" or node.users:
+        return
+    target = node.target
+    gm.graph.erase_node(node)
+    if any(n.op == "get_attr" and n.target == target for n in gm.graph.nodes):
+        return
+    *path, leaf = target.split(".")
+    owner = gm
+    for part in path:
+        owner = getattr(owner, part, None)
+        if owner is None:
+            return
+    if hasattr(owner, leaf):
+        delattr(owner, leaf)
+
+
+def fuse_quantized_linear(gm: fx.GraphModule, fold_weights: bool = True, plugin_form: bool = False) -> int:
     """Rewrite every linear whose input and weight both come from matching FP8 (or both from
     NVFP4) quantize ops.  Returns the number of linears rewritten; the module is recompiled
     in place.  Quantize nodes left without users are removed; a quantize node that still feeds
-    something else is kept for that user."""
+    something else is kept for that user.  Constant weights (`fold_weights`) are quantized once,
+    here, and their bf16 originals are deleted from the module when nothing else reads them.
+    `plugin_form`: emit one `b200_*_linear[_bias]` node per linear with a folded weight (see the
+    module docstring); linears whose weight is not a constant keep the quantize + GEMM form."""
     from . import ops
 
     ops.load_ops()
     t = torch.ops.tensorrt
     graph, n_fused = gm.graph, 0
     n_const = sum(1 for name, _ in gm.named_buffers(recurse=False) if name.startswith("_b200q_w") and name.endswith("_0"))
+    act_cache: dict = {}       # (mode, input node, amax node) -> getitem nodes of the one inserted quantize
     for node in list(graph.nodes):
         form = _as_linear(node)
         if form is None:
             continue
-        xq, wq, bias = form
+        xq, wq, bias, alpha, beta = form
         if not isinstance(xq, fx.Node) or not isinstance(wq, fx.Node):
             continue
         mode, mx, mw = "fp8", _match_fp8(xq), _match_fp8(wq)
@@ -142,17 +200,17 @@ def fuse_quantized_linear(gm: fx.GraphModule, fold_weights: bool = True) -> int:
         if mx is None or mw is None:
             continue
         quant = t.b200_fp8_quantize.default if mode == "fp8" else t.b200_nvfp4_quantize.default
-        gemm = t.b200_fp8_gemm.default if mode == "fp8" else t.b200_nvfp4_gemm.default
         parts = 2 if mode == "fp8" else 3
+        epilogue_bias = bias if (bias is not None and alpha == 1 and beta == 1) else None
+        w_src = mw[0]
         with graph.inserting_before(node):
-            xs = graph.call_function(quant, (mx[0], mx[1]))
-            x_parts = [graph.call_function(operator.getitem, (xs, i)) for i in range(parts)]
             w_const, a_const = _const_tensor(gm, mw[0]), _const_tensor(gm, mw[1])
-            if fold_weights and w_const is not None and a_const is not None and w_const.is_cuda:
+            folded = fold_weights and w_const is not None and a_const is not None and w_const.is_cuda
+            if folded:
                 with torch.no_grad():
-                    folded = quant(w_const.detach(), a_const.detach().to(w_const.device))
+                    tensors = quant(w_const.detach(), a_const.detach().to(w_const.device))
                 w_parts = []
-                for i, tensor in enumerate(folded):
+                for i, tensor in enumerate(tensors):
                     name = f"_b200q_w{n_const}_{i}"
                     gm.register_buffer(name, tensor)
                     w_parts.append(graph.get_attr(name))
@@ -160,10 +218,32 @@ def fuse_quantized_linear(gm: fx.GraphModule, fold_weights: bool = True) -> int:
             else:
                 ws = graph.call_function(quant, (mw[0], mw[1]))
                 w_parts = [graph.call_function(operator.getitem, (ws, i)) for i in range(parts)]
-            out = graph.call_function(gemm, (*x_parts, *w_parts, bias))
-            dtype = _out_dtype(node)
-            if dtype is not None and dtype != torch.bfloat16:
-                out = graph.call_method("to", (out, dtype))
+            if plugin_form and folded:
+                name = f"b200_{mode}_linear" + ("_bias" if epilogue_bias is not None else "")
+                args = (mx[0], mx[1], *w_parts) + ((epilogue_bias,) if epilogue_bias is not None else ())
+                out = graph.call_function(getattr(t, name).default, args)       # result in the activation's dtype
+            else:
+                key = (mode, mx[0], mx[1])
+                x_parts = act_cache.get(key)
+                if x_parts is None:
+                    # placed right after its inputs so that every later linear sharing it can use it
+                    anchor = max((n for n in mx if isinstance(n, fx.Node)), key=lambda n: _node_index(graph, n))
+                    with graph.inserting_after(anchor):
+                        xs = graph.call_function(quant, (mx[0], mx[1]))
+                    with graph.inserting_after(xs):
+                        x_parts = [graph.call_function(operator.getitem, (xs, i)) for i in reversed(range(parts))][::-1]
+                    act_cache[key] = x_parts
+                name = f"b200_{mode}_gemm" + ("_bias" if epilogue_bias is not None else "")
+                args = (*x_parts, *w_parts) + ((epilogue_bias,) if epilogue_bias is not None else ())
+                out = graph.call_function(getattr(t, name).default, args)
+                dtype = _out_dtype(node)
+                if dtype is not None and dtype != torch.bfloat16:
+                    out = graph.call_method("to", (out, dtype))
+            if epilogue_bias is None and bias is not None:
+                # addmm with alpha / beta != 1 (impl/addmm.py:12-34): beta * input + alpha * (x @ W^T)
+                if alpha != 1:
+                    out = graph.call_function(torch.ops.aten.mul.Tensor, (out, alpha))
+                out = graph.call_function(torch.ops.aten.add.Tensor, (out, bias), {"alpha": beta})
         out.meta.update({k: v for k, v in node.meta.items() if k in ("val", "tensor_meta")})
         node.replace_all_uses_with(out)
         dangling = [a for a in node.all_input_nodes if _transposed(a) is wq]
@@ -174,12 +254,21 @@ def fuse_quantized_linear(gm: fx.GraphModule, fold_weights: bool = True) -> int:
         for q in (xq, wq):
             if not q.users:
                 graph.erase_node(q)
+        if folded:
+            _drop_unused_constant(gm, w_src)
         n_fused += 1
     if n_fused:
         graph.eliminate_dead_code()
         graph.lint()
         gm.recompile()
     return n_fused
+
+
+def _node_index(graph: fx.Graph, node: fx.Node) -> int:
+    for i, n in enumerate(graph.nodes):
+        if n is node:
+            return i
+    return -1
 
 
 def fuse_all_reduce_wait(gm: fx.GraphModule) -> int:

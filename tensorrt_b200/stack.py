@@ -339,6 +339,7 @@ class DecoderStack:
         self.cfg, self.rank, self.world, self.group = cfg, rank, world, group
         self._comm = None
         self._fused = None
+        self.check_status = True                 # forward() polls the device status word on the fused TP path
         self.backend = backend or CudaBackend(cfg.mode)
         reduce = AllReduce(group) if world > 1 else None
         row_parallel = None
@@ -358,8 +359,8 @@ class DecoderStack:
                 row_parallel = lambda x, qw, amax=None: reduce(be.linear(x, qw, amax))  # noqa: E731
         self.layers = [DecoderLayer(cfg, shard_layer_weights(w, cfg, rank, world) if world > 1 else w, self.backend, world,
                                     row_parallel) for w in weights]
-        # every weight is quantized and resident from here on: forward() may promise the GEMMs that
-        # no kernel in flight is still writing them (capi.assume_static_weights)
+        # every weight is quantized and resident from here on: forward() may promise its own GEMM
+        # calls that no kernel in flight is still writing them (b200q_cfg::static_weights, per call)
         self._static_weights = isinstance(self.backend, CudaBackend)
         if self._static_weights and torch.cuda.is_available():
             torch.cuda.synchronize()
@@ -379,15 +380,21 @@ class DecoderStack:
             raise ValueError(f"sharded must be False, True or 'collectives', got {sharded!r}")
         if self.world == 1:
             sharded = False
-        if self._static_weights:
-            capi.assume_static_weights(True)
-        try:
+        if self._fused is not None and self.check_status:
+            self.raise_if_device_error()
+        with capi.gemm_config(static_weights=self._static_weights):
             if micro_batches > 1 and self.world > 1 and h.is_cuda and h.shape[0] >= 2 * 128 * self.world:
                 return self._forward_overlapped(h, micro_batches, sharded).view(shape)
             return self._micro_batch(h, sharded).view(shape)
-        finally:
-            if self._static_weights:
-                capi.assume_static_weights(False)
+
+    def raise_if_device_error(self) -> None:
+        """The peer-memory reductions skip their work once a bounded device-side wait has run out
+        (a peer that never arrived) and the host calls still return success, so their outputs would
+        be stale from then on.  This reads the device status word (a synchronising 4-byte copy) and
+        raises; `forward` calls it before issuing a step on the fused tensor-parallel path."""
+        if capi.device_status(reset=False) != 0:
+            raise RuntimeError("a device-side wait for a tensor-parallel peer timed out in an earlier step; "
+                               "outputs since then are invalid (b200q_device_status)")
 
     def _micro_batch(self, h: torch.Tensor, sharded: bool) -> torch.Tensor:
         """All layers over one batch of tokens on the current stream."""

@@ -109,6 +109,40 @@ def check_same_shape(t: torch.Tensor, group=None) -> None:
         raise ShapeMismatchError(f"all-reduce operands differ across ranks: {seen}")
 
 
+def replicate_row_parallel_bias(bias, group=None, device=None):
+    """Bias of a row-parallel linear in the form the fused peer-memory path needs.
+
+    Two conventions meet here.  "Linear, then all-reduce" (the reference's _RowParallelLinear,
+    tools/llm/tensor_parallel_llama_export.py:109-125) sums whatever every rank adds, so the
+    checkpoint loader keeps a row-parallel bias on rank 0 only (checkpoint.load_quantized_linears).
+    The fused path (FusedRowParallel, b200q_reduce_gather and its siblings) adds the bias AFTER the
+    sum, on the rank that owns each row, so every rank must hold the full bias.  This collective
+    call converts the first form into the second: rank 0's bias is broadcast to all ranks; returns
+    None on every rank when rank 0 has none.  A rank other than 0 that holds a bias of its own is an
+    error (it would have been summed twice by the unfused path)."""
+    group = group or dist.group.WORLD
+    world = dist.get_world_size(group)
+    if world == 1:
+        return bias
+    rank = dist.get_rank(group)
+    have = [None] * world
+    dist.all_gather_object(have, None if bias is None else (tuple(bias.shape), str(bias.dtype)), group=group)
+    if have[0] is None:
+        if any(h is not None for h in have[1:]):
+            raise ValueError(f"a row-parallel bias must live on rank 0 (and optionally, identically, on every rank), got {have}")
+        return None
+    if any(h is not None and h != have[0] for h in have[1:]):
+        raise ValueError(f"row-parallel bias differs across ranks: {have}")
+    if all(h == have[0] for h in have):
+        return bias                                       # already replicated
+    shape, dtype = have[0]
+    if bias is None:
+        bias = torch.empty(shape, dtype=getattr(torch, dtype.split(".")[-1]), device=device or "cpu")
+    src = dist.get_global_rank(group, 0) if group is not dist.group.WORLD else 0
+    dist.broadcast(bias, src=src, group=group)
+    return bias
+
+
 class FusedRowParallel:
     """Row-parallel quantized linear + all-reduce as two b200q launches over peer memory
     (include/b200q.h: b200q_*_gemm_reduce_scatter, b200q_reduce_gather) instead of a GEMM followed
@@ -119,6 +153,11 @@ class FusedRowParallel:
     `max_rows` x `n_out` bf16 bounds the buffers.  Calls whose row count is not a multiple of
     world * 128 (decode steps) fall back to `fallback(x, qw, amax)`, the NCCL path.
     The returned tensor is a view of this rank's output buffer and is valid until the next call.
+
+    Bias convention: `bias` arguments are added once, after the sum, by the rank that owns each
+    row, so EVERY rank passes the same full bias (or every rank passes None).  A checkpoint-loaded
+    row-parallel linear keeps its bias on rank 0 only; convert it once with
+    `replicate_row_parallel_bias`.  The first use of a bias tensor is checked across ranks.
     """
 
     def __init__(self, mode: str, max_rows: int, n_out: int, group=None, fallback=None, sharded: bool = False):
@@ -137,6 +176,31 @@ class FusedRowParallel:
         # one set of peer buffers, flags and epoch counter per CUDA stream that calls in: calls on
         # different streams may overlap on the device and must not share them
         self._ctx: dict = {}
+        self._bias_seen: set = set()
+
+    def prepare(self, rows: int, streams=None) -> None:
+        """Allocate the peer buffers for calls of up to `rows` rows on each of `streams` (default:
+        the current stream) now.  Collective: every rank calls it with the same arguments.  Doing
+        this before a timed region or a stream capture keeps the allocation, the rendezvous and
+        the barrier they need out of the first forward."""
+        for st in (streams or [torch.cuda.current_stream()]):
+            with torch.cuda.stream(st):
+                self._context(rows)
+
+    def _checked_bias(self, bias):
+        """bf16 contiguous bias, or None; the first time a tensor is seen its presence and shape are
+        compared across ranks (a bias on some ranks only would silently bias some rows only)."""
+        if bias is not None:
+            bias = bias.to(torch.bfloat16).contiguous()
+        key = None if bias is None else (bias.data_ptr(), tuple(bias.shape))
+        if key not in self._bias_seen:
+            have = [None] * self.world
+            dist.all_gather_object(have, None if bias is None else tuple(bias.shape), group=self.group)
+            if any(h != have[0] for h in have):
+                raise ValueError(f"the fused row-parallel path needs the same full bias on every rank, got {have}; "
+                                 "see tp.replicate_row_parallel_bias")
+            self._bias_seen.add(key)
+        return bias
 
     def _context(self, rows: int):
         """Buffers of the calling stream, (re)allocated collectively: every rank reaches this point
@@ -191,11 +255,11 @@ class FusedRowParallel:
             if self.fallback is None:
                 raise ValueError(f"{rows} rows: need a multiple of {self.world * 128} and at most {self.max_rows}")
             return self.fallback(x, qw, amax)
+        b = self._checked_bias(bias)
         ctx = self._gemm_to_owners(x, qw, amax)
         lib = load()
-        b = None if bias is None else bias.to(torch.bfloat16).contiguous()
         check(lib.b200q_reduce_gather(ctx["ref"], None if b is None else b.data_ptr(), rows, n, ctx["epoch"],
-                                      torch.cuda.current_stream().cuda_stream), "b200q_reduce_gather")
+                                      torch.cuda.current_stream().cuda_stream, None), "b200q_reduce_gather")
         return ctx["out"][: rows * n * 2].view(torch.bfloat16).view(rows, n)
 
     def _gemm_to_owners(self, x, qw, amax=None):
@@ -213,12 +277,12 @@ class FusedRowParallel:
             xc, xs = x if isinstance(x, tuple) else capi.fp8_quantize(x, None)
             k = xc.shape[1]
             check(lib.b200q_fp8_gemm_reduce_scatter(xc.data_ptr(), xs.data_ptr(), xs.numel(), qw[0].data_ptr(), qw[1].data_ptr(),
-                                                    qw[1].numel(), ref, rows, n, k, stream), "b200q_fp8_gemm_reduce_scatter")
+                                                    qw[1].numel(), ref, rows, n, k, stream, None), "b200q_fp8_gemm_reduce_scatter")
         else:
             xc, xs, xg = x if isinstance(x, tuple) else capi.nvfp4_quantize(x, capi.amax(x) if amax is None else amax)
             k = xc.shape[1] * 2
             check(lib.b200q_nvfp4_gemm_reduce_scatter(xc.data_ptr(), xs.data_ptr(), xg.data_ptr(), qw[0].data_ptr(), qw[1].data_ptr(),
-                                                      qw[2].data_ptr(), ref, rows, n, k, stream),
+                                                      qw[2].data_ptr(), ref, rows, n, k, stream, None),
                   "b200q_nvfp4_gemm_reduce_scatter")
         ctx["epoch"] += 1
         ctx["pending_rows"] = rows
@@ -247,11 +311,11 @@ class FusedRowParallel:
         rows, n = ctx.pop("pending_rows"), self.n_out
         if tuple(h_shard.shape) != (rows // self.world, n) or not h_shard.is_contiguous() or h_shard.dtype != torch.bfloat16:
             raise ValueError(f"h_shard must be a contiguous bf16 [{rows // self.world}, {n}] tensor")
-        b = None if bias is None else bias.to(torch.bfloat16).contiguous()
+        b = self._checked_bias(bias)
         w = norm_weight.to(torch.bfloat16).contiguous()
         check(load().b200q_reduce_add_rms_norm_fp8_quantize_gather(
             ctx["gather_ref"], None if b is None else b.data_ptr(), h_shard.data_ptr(), w.data_ptr(), float(eps), rows, n,
-            ctx["epoch"], torch.cuda.current_stream().cuda_stream), "b200q_reduce_add_rms_norm_fp8_quantize_gather")
+            ctx["epoch"], torch.cuda.current_stream().cuda_stream, None), "b200q_reduce_add_rms_norm_fp8_quantize_gather")
         return ctx["codes"][: rows * n].view(rows, n), ctx["scales"][: rows * 4].view(torch.float32)
 
     def reduce_add(self, h_shard: torch.Tensor, bias=None) -> torch.Tensor:
@@ -263,7 +327,7 @@ class FusedRowParallel:
         rows, n = ctx.pop("pending_rows"), self.n_out
         if tuple(h_shard.shape) != (rows // self.world, n) or not h_shard.is_contiguous() or h_shard.dtype != torch.bfloat16:
             raise ValueError(f"h_shard must be a contiguous bf16 [{rows // self.world}, {n}] tensor")
-        b = None if bias is None else bias.to(torch.bfloat16).contiguous()
+        b = self._checked_bias(bias)
         check(load().b200q_reduce_add_gather(ctx["ref"], None if b is None else b.data_ptr(), h_shard.data_ptr(), rows, n,
-                                             ctx["epoch"], torch.cuda.current_stream().cuda_stream), "b200q_reduce_add_gather")
+                                             ctx["epoch"], torch.cuda.current_stream().cuda_stream, None), "b200q_reduce_add_gather")
         return ctx["out"][: rows * n * 2].view(torch.bfloat16).view(rows, n)

@@ -183,7 +183,8 @@ def test_matmul_and_addmm_forms_are_the_same_linear(b200, form):
     assert not any("quantize_op" in t or "aten.mm" in t or "addmm" in t or "matmul" in t or "aten.t." in t or "permute" in t
                    or "transpose" in t for t in names), names
     gemm = next(n for n in gm.graph.nodes if "b200_fp8_gemm" in str(n.target))
-    assert (gemm.args[4] is not None) == (form == "addmm")          # addmm's first argument is the bias
+    assert ("gemm_bias" in str(gemm.target)) == (form == "addmm")    # addmm's first argument is the bias
+    assert len(gemm.args) == (5 if form == "addmm" else 4)
     y = gm.to("meta")(torch.empty(7, 32, dtype=torch.bfloat16, device="meta"))
     assert y.shape == (7, 48)
     # a plain matmul of two quantized activations (no transposed weight) is not a linear
@@ -198,6 +199,153 @@ def test_matmul_and_addmm_forms_are_the_same_linear(b200, form):
 
     gm2 = torch.fx.symbolic_trace(Plain())
     assert fuse_quantized_linear(gm2) == 0
+
+
+def test_linears_sharing_one_input_quantizer_share_one_quantize_node(b200):
+    """q/k/v (or gate/up) projections read the same quantized activation: the rewrite inserts ONE
+    real-quant node for it, not one per linear."""
+    from tensorrt_b200.fx_passes import fuse_quantized_linear
+
+    class Qkv(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q, self.k, self.v = QdqLinear(64, 32, seed=1), QdqLinear(16, 32, seed=2), QdqLinear(16, 32, seed=3)
+
+        def forward(self, x):
+            xq = self.q.q(x, self.q.x_amax)
+            outs = [torch.nn.functional.linear(xq, m.q(m.weight, m.w_amax), m.bias) for m in (self.q, self.k, self.v)]
+            return torch.cat(outs, dim=-1)
+
+    gm = torch.fx.symbolic_trace(Qkv())
+    assert fuse_quantized_linear(gm) == 3
+    names = _targets(gm)
+    assert sum("b200_fp8_gemm_bias" in t for t in names) == 3
+    assert sum("b200_fp8_quantize" in t for t in names) == 1 + 3          # one activation quantize + 3 unfolded CPU weights
+    assert not any("tensorrt.quantize_op" in t for t in names)
+    y = gm.to("meta")(torch.empty(5, 32, dtype=torch.bfloat16, device="meta"))
+    assert y.shape == (5, 96)
+
+
+def test_keyword_arguments_and_unsigned_quantizers(b200):
+    """The quantize ops are matched by schema, so keyword forms fuse like positional ones; an
+    unsigned or narrow-range quantizer is a different arithmetic and is left alone."""
+    from tensorrt_b200.fx_passes import fuse_quantized_linear
+
+    def build(**flags):
+        class M(torch.nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.w = torch.nn.Parameter(torch.randn(16, 32).bfloat16())
+                self.register_buffer("a", torch.tensor(1.0))
+
+            def forward(self, x):
+                q = torch.ops.tensorrt.quantize_op
+                xq = q(x, self.a, num_bits=8, exponent_bits=4, unsigned=flags.get("unsigned", False),
+                       narrow_range=flags.get("narrow_range", False))
+                wq = q(self.w, amax=self.a, num_bits=8, exponent_bits=4, unsigned=False, narrow_range=False)
+                return torch.nn.functional.linear(xq, wq)
+        return torch.fx.symbolic_trace(M())
+
+    assert fuse_quantized_linear(build()) == 1
+    for flags in ({"unsigned": True}, {"narrow_range": True}):
+        gm = build(**flags)
+        before = _targets(gm)
+        assert fuse_quantized_linear(gm) == 0 and _targets(gm) == before
+
+
+def test_addmm_with_alpha_and_beta(b200):
+    """addmm = beta * input + alpha * (x @ W^T) (conversion/impl/addmm.py:12-34): with factors other
+    than 1 the bias cannot ride in the GEMM epilogue; the scaling stays as nodes behind the GEMM."""
+    from tensorrt_b200.fx_passes import fuse_quantized_linear
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = QdqLinear(48, 32)
+
+        def forward(self, x):
+            xq = self.lin.q(x, self.lin.x_amax)
+            wq = self.lin.q(self.lin.weight, self.lin.w_amax)
+            return torch.ops.aten.addmm.default(self.lin.bias, xq, torch.ops.aten.t.default(wq), beta=0.5, alpha=2.0)
+
+    gm = torch.fx.symbolic_trace(M())
+    assert fuse_quantized_linear(gm) == 1
+    names = _targets(gm)
+    assert sum("b200_fp8_gemm" in t for t in names) == 1 and not any("gemm_bias" in t or "addmm" in t for t in names)
+    assert any("aten.mul" in t for t in names) and any("aten.add" in t for t in names)
+    add = next(n for n in gm.graph.nodes if "aten.add" in str(n.target))
+    assert add.kwargs == {"alpha": 0.5}
+    mul = next(n for n in gm.graph.nodes if "aten.mul" in str(n.target))
+    assert mul.args[1] == 2.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["fp8", "nvfp4"])
+@pytest.mark.parametrize("form", ["mm", "matmul3d", "addmm", "addmm_ab"])
+def test_mm_matmul_addmm_forms_match_the_unfused_graph_on_gpu(b200, mode, form):
+    """The forms `aten.linear` decomposes to in distributed mode (lowering/_decompositions.py:738-745),
+    rewritten and run on the device, against the same graph left unfused (fake-quant ops + bf16
+    matmul).  Tolerance: rel-L2 <= 1e-2, the bar of the linear form."""
+    from tensorrt_b200.fx_passes import fuse_quantized_linear
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = QdqLinear(384, 256, mode, seed=5)
+
+        def forward(self, x):
+            xq = self.lin.q(x, self.lin.x_amax)
+            wq = self.lin.q(self.lin.weight, self.lin.w_amax)
+            if form == "mm":
+                return torch.ops.aten.mm.default(xq, torch.ops.aten.t.default(wq))
+            if form == "matmul3d":
+                return torch.matmul(xq, torch.ops.aten.permute.default(wq, [1, 0]))
+            if form == "addmm":
+                return torch.ops.aten.addmm.default(self.lin.bias, xq, torch.ops.aten.transpose.int(wq, 0, 1))
+            return torch.ops.aten.addmm.default(self.lin.bias, xq, torch.ops.aten.t.default(wq), beta=0.5, alpha=2.0)
+
+    m = M().cuda()
+    g = torch.Generator().manual_seed(17)
+    shape = (4, 50, 256) if form == "matmul3d" else (200, 256)
+    x = torch.randn(*shape, generator=g).bfloat16().cuda()
+    m.lin.x_amax.copy_(x.float().abs().max())
+    ref = m(x)
+    gm = torch.fx.symbolic_trace(m)
+    assert fuse_quantized_linear(gm) == 1
+    assert not hasattr(gm.lin, "weight")                # the folded bf16 weight is gone, only its codes remain
+    y = gm(x)
+    torch.cuda.synchronize()
+    assert b200.capi.device_status() == 0
+    assert y.shape == ref.shape and y.dtype == ref.dtype
+    assert o.rel_l2(y.float().cpu(), ref.float().cpu()) <= 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["fp8", "nvfp4"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_plugin_form_is_one_node_per_linear_and_matches_on_gpu(b200, mode, dtype):
+    """plugin_form=True: each linear with a constant weight is ONE `b200_*_linear[_bias]` node with
+    tensor-only arguments, activation first, result in the activation's dtype (what the reference's
+    plugin generator can describe); numerics as the two-node form."""
+    from tensorrt_b200.fx_passes import fuse_quantized_linear
+
+    m = TwoLayer(mode).to(dtype).cuda()
+    x = torch.randn(3, 40, 32, device="cuda").to(dtype)
+    m.a.x_amax.copy_(x.float().abs().max())
+    m.b.x_amax.copy_(torch.nn.functional.silu(m.a(x)).float().abs().max())
+    ref = m(x)
+    gm = torch.fx.symbolic_trace(m)
+    assert fuse_quantized_linear(gm, plugin_form=True) == 2
+    names = _targets(gm)
+    kind = "fp8" if mode == "fp8" else "nvfp4"
+    assert sum(f"b200_{kind}_linear_bias" in t for t in names) == 1 and sum(f"b200_{kind}_linear" in t for t in names) == 2
+    assert not any("quantize" in t or "gemm" in t for t in names), names
+    for n in gm.graph.nodes:
+        if "b200_" in str(n.target):
+            assert all(isinstance(a, torch.fx.Node) for a in n.args)
+    y = gm(x)
+    assert y.dtype == dtype and y.shape == ref.shape
+    assert o.rel_l2(y.float().cpu(), ref.float().cpu()) <= 2e-2
 
 
 def _all_reduce_graph(extra_user: bool):

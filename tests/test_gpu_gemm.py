@@ -20,9 +20,7 @@ def capi(b200):
 
 @pytest.fixture(autouse=True)
 def _status(capi):
-    capi.set_gemm_tile_n(0)
     yield
-    capi.set_gemm_tile_n(0)
     assert capi.device_status() == 0, "a GEMM reported a device-side wait that gave up"
 
 
@@ -71,8 +69,7 @@ FP8_SHAPES = [(128, 128, 128), (128, 256, 512), (1, 4096, 4096), (16, 4096, 4096
 def test_fp8_gemm(capi, M, N, K, bn):
     x, w, b = _inputs(M, N, K, seed=2 + M + N + K)
     (xc, xs, wc, ws), ref = _ref_fp8(x, w, b)
-    capi.set_gemm_tile_n(bn)
-    out = capi.fp8_gemm(xc.cuda(), xs.reshape(-1).cuda(), wc.cuda(), ws.reshape(-1).cuda(), b.cuda())
+    out = capi.fp8_gemm(xc.cuda(), xs.reshape(-1).cuda(), wc.cuda(), ws.reshape(-1).cuda(), b.cuda(), tile_n=bn)
     torch.cuda.synchronize()
     assert out.shape == (M, N) and out.dtype == torch.bfloat16
     assert o.rel_l2(out.float(), ref) <= TOL
@@ -91,14 +88,14 @@ def test_small_m_split_k(capi, M, N, K, force):
         pytest.skip("fewer K tiles than splits")
     x, w, b = _inputs(M, N, K, seed=7 + M + N + K)
     (xc, xs, wc, ws), ref = _ref_fp8(x, w, b)
-    capi.set_gemm_tile_n(force)
-    out = capi.fp8_gemm(xc.cuda(), xs.reshape(-1).cuda(), wc.cuda(), ws.reshape(-1).cuda(), b.cuda())
+    out = capi.fp8_gemm(xc.cuda(), xs.reshape(-1).cuda(), wc.cuda(), ws.reshape(-1).cuda(), b.cuda(), tile_n=force)
     torch.cuda.synchronize()
     assert o.rel_l2(out.float(), ref) <= TOL
     if K % 32 == 0:
         xq, wq, ref4 = _ref_nvfp4(x, w, b)
-        out = capi.nvfp4_gemm(xq[0].cuda(), o.swizzle_scales(xq[1]).cuda(), xq[2].cuda(),
-                              wq[0].cuda(), o.swizzle_scales(wq[1]).cuda(), wq[2].cuda(), b.cuda())
+        with capi.gemm_config(tile_n=force):           # the same selection through the per-thread default
+            out = capi.nvfp4_gemm(xq[0].cuda(), o.swizzle_scales(xq[1]).cuda(), xq[2].cuda(),
+                                  wq[0].cuda(), o.swizzle_scales(wq[1]).cuda(), wq[2].cuda(), b.cuda())
         torch.cuda.synchronize()
         assert o.rel_l2(out.float(), ref4) <= TOL
 
@@ -134,11 +131,132 @@ NVFP4_SHAPES = [(128, 128, 256), (128, 256, 512), (16, 4096, 4096), (200, 384, 1
 def test_nvfp4_gemm(capi, M, N, K, bn):
     x, w, b = _inputs(M, N, K, seed=3 + M + N + K)
     xq, wq, ref = _ref_nvfp4(x, w, b)
-    capi.set_gemm_tile_n(bn)
     out = capi.nvfp4_gemm(xq[0].cuda(), o.swizzle_scales(xq[1]).cuda(), xq[2].cuda(),
-                          wq[0].cuda(), o.swizzle_scales(wq[1]).cuda(), wq[2].cuda(), b.cuda())
+                          wq[0].cuda(), o.swizzle_scales(wq[1]).cuda(), wq[2].cuda(), b.cuda(), tile_n=bn)
     torch.cuda.synchronize()
     assert o.rel_l2(out.float(), ref) <= TOL
+
+
+# ---------------------------------------------------------------- the M = 8192 shapes of the sweep
+BIG = [(8192, 8192, 8192), (8192, 14336, 4096), (8192, 4096, 14336)]
+
+
+@pytest.mark.parametrize("bn", [0, 128, 256])
+@pytest.mark.parametrize("M,N,K", BIG[:2])
+def test_fp8_gemm_m8192(capi, M, N, K, bn):
+    """Many rounds of tiles per SM (pair): 0 = the automatic choice (CTA-pair kernel), 128 / 256 =
+    the single-CTA kernel."""
+    x, w, b = _inputs(M, N, K, seed=2 + M + N + K)
+    (xc, xs, wc, ws), ref = _ref_fp8(x, w, b)
+    out = capi.fp8_gemm(xc.cuda(), xs.reshape(-1).cuda(), wc.cuda(), ws.reshape(-1).cuda(), b.cuda(), tile_n=bn)
+    torch.cuda.synchronize()
+    assert o.rel_l2(out.float(), ref) <= TOL
+    # no row or column block may be off on its own: the tolerance holds per 512 x 512 block too
+    d, r = (out.float() - ref), ref
+    blk = lambda t: t.view(M // 512, 512, N // 512, 512).pow(2).sum(dim=(1, 3)).sqrt()  # noqa: E731
+    assert float((blk(d) / blk(r)).max()) <= 2 * TOL
+
+
+@pytest.mark.parametrize("bn", [0, 512])
+@pytest.mark.parametrize("M,N,K", BIG)
+def test_nvfp4_gemm_m8192(capi, M, N, K, bn):
+    x, w, b = _inputs(M, N, K, seed=3 + M + N + K)
+    xq, wq, ref = _ref_nvfp4(x, w, b)
+    out = capi.nvfp4_gemm(xq[0].cuda(), o.swizzle_scales(xq[1]).cuda(), xq[2].cuda(),
+                          wq[0].cuda(), o.swizzle_scales(wq[1]).cuda(), wq[2].cuda(), b.cuda(), tile_n=bn)
+    torch.cuda.synchronize()
+    assert o.rel_l2(out.float(), ref) <= TOL
+    d, r = (out.float() - ref), ref
+    blk = lambda t: t.view(M // 512, 512, N // 512, 512).pow(2).sum(dim=(1, 3)).sqrt()  # noqa: E731
+    assert float((blk(d) / blk(r)).max()) <= 2 * TOL
+
+
+def test_config1_fp8_per_tensor_linear_full_size(capi):
+    """FP8 per-tensor Q/DQ linear at the configuration's full size: x bf16 [16, 4096] ~ N(0,1),
+    W bf16 [4096, 4096] ~ N(0, 0.02), seed 0, scales amax / 448 per tensor; the device path
+    (amax, quantize, GEMM) against the oracle's linear on the same tensors."""
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(16, 4096, generator=g).bfloat16()
+    w = (torch.randn(4096, 4096, generator=g) * 0.02).bfloat16()
+    xa, wa = x.float().abs().max(), w.float().abs().max()
+    ref = o.fp8_linear_ref(x, w, None, xa, wa)
+    xd, wd = x.cuda(), w.cuda()
+    ax, aw = capi.amax(xd), capi.amax(wd)
+    assert ax.item() == xa.item() and aw.item() == wa.item()
+    xc, xs = capi.fp8_quantize(xd, ax)
+    wc, ws = capi.fp8_quantize(wd, aw)
+    assert torch.equal(xc.cpu(), o.fp8_quantize(x, xa)[0]) and torch.equal(wc.cpu(), o.fp8_quantize(w, wa)[0])
+    for tile in (0, 128, 1001, 1004):
+        y = capi.fp8_gemm(xc, xs, wc, ws, None, tile_n=tile)
+        assert y.shape == (16, 4096) and o.rel_l2(y.float().cpu(), ref) <= TOL
+
+
+# ---------------------------------------------------------------- exact cases
+# Sparse small integers: every product and every partial sum is an integer far below 2^24, so fp32
+# accumulation is exact in any order, and the totals stay within +-256, where bf16 holds every
+# integer.  The device result must EQUAL the integer matmul: a dropped or doubled 32/64-element
+# K sub-block, a tile written to the wrong place or a mis-indexed scale shows as an integer error
+# that no rel-L2 tolerance can absorb.
+def _sparse_ints(rows, cols, g, density=1 / 8, top=2):
+    v = torch.randint(1, top + 1, (rows, cols), generator=g).float()
+    v = v * (torch.randint(0, 2, (rows, cols), generator=g).float() * 2 - 1)
+    return v * (torch.rand(rows, cols, generator=g) < density)
+
+
+EXACT_FP8 = [(0, 256, 384, 256), (128, 640, 640, 4096), (256, 640, 768, 4096), (512, 4096, 2560, 4096), (0, 2304, 4352, 8192),
+             (1001, 64, 1024, 4096), (1002, 64, 1024, 4096), (1004, 128, 1152, 4096), (1008, 16, 1024, 8192), (0, 64, 8192, 8192)]
+
+
+@pytest.mark.parametrize("tile,M,N,K", EXACT_FP8)
+def test_fp8_gemm_exact_sparse_integers(capi, tile, M, N, K):
+    """Every FP8 kernel: single-CTA 128 / 256 wide, the CTA-pair kernel with more than two tile
+    rounds per SM pair (160 and 153 tiles of 256 x 256 on 74 pairs), the small-M kernel at every
+    cluster size.  Row and column scales are powers of two (exact), so scale indexing is checked
+    with the same equality."""
+    g = torch.Generator().manual_seed(5 + tile + M + N + K)
+    a, bm = _sparse_ints(M, K, g), _sparse_ints(N, K, g)
+    sa = torch.tensor([0.5, 1.0, 2.0])[torch.randint(0, 3, (M,), generator=g)]
+    sb = torch.tensor([0.5, 1.0, 2.0])[torch.randint(0, 3, (N,), generator=g)]
+    raw = a.cuda() @ bm.cuda().t()
+    assert float(raw.abs().max()) <= 256               # integers bf16 holds exactly; the power-of-two scales keep that
+    ref = raw * sa.cuda()[:, None] * sb.cuda()[None, :]
+    out = capi.fp8_gemm(o.e4m3_encode(a).cuda(), sa.cuda(), o.e4m3_encode(bm).cuda(), sb.cuda(), None, tile_n=tile)
+    torch.cuda.synchronize()
+    bad = (out.float() != ref).nonzero()
+    assert bad.numel() == 0, f"{bad.shape[0]} wrong elements, first at {bad[0].tolist()}"
+
+
+EXACT_NVFP4 = [(128, 256, 384, 4096), (256, 640, 768, 4096), (512, 1024, 1280, 4096), (0, 2304, 4352, 8192), (0, 384, 640, 4416),
+               (1001, 64, 1024, 4096), (1004, 128, 1152, 4096), (1008, 16, 1024, 8192)]
+
+
+@pytest.mark.parametrize("tile,M,N,K", EXACT_NVFP4)
+def test_nvfp4_gemm_exact_sparse_integers(capi, tile, M, N, K):
+    """NVFP4 kernels with hand-built operands: E2M1 codes 0 / +-1 / +-2, E4M3 block scales 1 or 2
+    chosen per 16-element block, global scales 1 and 0.5.  The dequantized operands are small
+    integers, so the result is exact: a scale atom read from the wrong row, column tile or K block
+    changes integers.  K = 4416 ends in a partial 256-element K tile."""
+    g = torch.Generator().manual_seed(9 + tile + M + N + K)
+
+    def operand(rows):
+        vals = _sparse_ints(rows, K, g, density=1 / 16)                       # in {0, +-1, +-2}
+        codes = o.e2m1_encode(vals)
+        blk = torch.tensor([1.0, 2.0])[torch.randint(0, 2, (rows, K // 16), generator=g)]
+        return vals.view(rows, K // 16, 16) * blk[..., None], o.pack_e2m1(codes), o.e4m3_encode(blk)
+
+    av, ac, asf = operand(M)
+    bv, bc, bsf = operand(N)
+    ga, gb = torch.tensor(1.0), torch.tensor(0.5)
+    # the oracle's dequantize reproduces the hand-built values
+    assert torch.equal(o.nvfp4_dequantize(ac, asf, ga), av.view(M, K))
+    raw = av.view(M, K).cuda() @ bv.view(N, K).cuda().t()
+    assert float(raw.abs().max()) <= 256
+    ref = raw * 0.5
+    out = capi.nvfp4_gemm(ac.cuda(), o.swizzle_scales(asf).cuda(), ga.cuda(), bc.cuda(), o.swizzle_scales(bsf).cuda(), gb.cuda(),
+                          None, tile_n=tile)
+    torch.cuda.synchronize()
+    bad = (out.float() != ref).nonzero()
+    assert bad.numel() == 0, f"{bad.shape[0]} wrong elements, first at {bad[0].tolist()}"
 
 
 def test_golden_linear(b200):
@@ -175,11 +293,19 @@ def test_torch_library_gemm_ops(b200):
     (xc, xs, wc, ws), ref = _ref_fp8(x, w, b)
     codes, scales = torch.ops.tensorrt.b200_fp8_quantize(x.cuda(), None)
     assert torch.equal(codes.cpu(), xc)
-    out = torch.ops.tensorrt.b200_fp8_gemm(codes, scales, wc.cuda(), ws.reshape(-1).cuda(), b.cuda())
+    out = torch.ops.tensorrt.b200_fp8_gemm_bias(codes, scales, wc.cuda(), ws.reshape(-1).cuda(), b.cuda())
     assert o.rel_l2(out.float(), ref) <= TOL
+    nob = torch.ops.tensorrt.b200_fp8_gemm(codes, scales, wc.cuda(), ws.reshape(-1).cuda())
+    assert o.rel_l2(nob.float(), ref - b.float().cuda()) <= TOL
+    one = torch.ops.tensorrt.b200_fp8_linear_bias(x.cuda(), torch.empty(0, device="cuda"), wc.cuda(), ws.reshape(-1).cuda(), b.cuda())
+    assert torch.equal(one, out)                       # empty amax = per-token abs-max measured by the kernel
     xq, wq, ref = _ref_nvfp4(x, w, b)
     c, s, g = torch.ops.tensorrt.b200_nvfp4_quantize(x.cuda(), x.float().abs().max().cuda())
     assert torch.equal(c.cpu(), xq[0])
     wc4, ws4, wg4 = torch.ops.tensorrt.b200_nvfp4_quantize(w.cuda(), w.float().abs().max().cuda())
-    out = torch.ops.tensorrt.b200_nvfp4_gemm(c, s, g, wc4, ws4, wg4, b.cuda())
+    out = torch.ops.tensorrt.b200_nvfp4_gemm_bias(c, s, g, wc4, ws4, wg4, b.cuda())
     assert o.rel_l2(out.float(), ref) <= TOL
+    one = torch.ops.tensorrt.b200_nvfp4_linear_bias(x.cuda(), x.float().abs().max().cuda(), wc4, ws4, wg4, b.cuda())
+    assert torch.equal(one, out)
+    half = torch.ops.tensorrt.b200_nvfp4_linear(x.half().cuda(), x.float().abs().max().cuda(), wc4, ws4, wg4)
+    assert half.dtype == torch.float16 and o.rel_l2(half.float(), ref - b.float().cuda()) <= TOL

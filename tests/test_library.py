@@ -46,13 +46,25 @@ def test_argument_validation_without_a_device(b200):
     assert lib.b200q_fp8_quantize(p, 2, 4, 64, p, 3, p, p, None) == -1             # amax_numel not 0/1/rows
     assert lib.b200q_fp8_quantize(p + 2, 2, 4, 64, p, 1, p, p, None) == -2         # misaligned
     assert lib.b200q_nvfp4_quantize(p, 2, 4, 40, p, p, p, p, None) == -1           # cols % 16
-    assert lib.b200q_nvfp4_gemm(p, p, p, p, p, p, None, p, 4, 4, 48, None) == -1   # K % 32
-    assert lib.b200q_fp8_gemm(p, p, 1, p, p, 1, None, p, 4, 4, 40, None) == -1     # K % 16
-    assert lib.b200q_fp8_gemm(p, p, 3, p, p, 1, None, p, 4, 4, 64, None) == -1     # scale count
+    assert lib.b200q_nvfp4_gemm(p, p, p, p, p, p, None, p, 4, 4, 48, None, None) == -1   # K % 32
+    assert lib.b200q_fp8_gemm(p, p, 1, p, p, 1, None, p, 4, 4, 40, None, None) == -1     # K % 16
+    assert lib.b200q_fp8_gemm(p, p, 3, p, p, 1, None, p, 4, 4, 64, None, None) == -1     # scale count
     assert lib.b200q_amax(p, 2, 64, p, None, 0, None) == -5                         # no workspace
-    assert lib.b200q_gemm_set_tile_n(64) == -1
-    assert lib.b200q_gemm_set_tile_n(1003) == -1
-    assert lib.b200q_gemm_set_tile_n(0) == 0
+    # per-call options: an unknown tile selector or a non-zero reserved field is refused before any CUDA call
+    for tile in (64, 1003, -1):
+        assert lib.b200q_fp8_gemm(p, p, 1, p, p, 1, None, p, 4, 4, 64, None, _lib.cfg_ref(tile_n=tile)) == -1
+        assert lib.b200q_nvfp4_gemm(p, p, p, p, p, p, None, p, 4, 4, 64, None, _lib.cfg_ref(tile_n=tile)) == -1
+    bad = _lib.Cfg(0, 0, 0, 7)
+    assert lib.b200q_fp8_gemm(p, p, 1, p, p, 1, None, p, 4, 4, 64, None, ctypes.byref(bad)) == -1
+    assert _lib.cfg_ref() is None and ctypes.sizeof(_lib.Cfg) == 16
+
+
+def test_the_abi_has_no_process_wide_setter(b200):
+    """Tile choice, the static-weights promise and the peer wait limit travel per call in
+    b200q_cfg; nothing in the header sets state for later calls."""
+    from tensorrt_b200 import _lib
+
+    assert not [n for n in _lib.header_symbols() if "_set_" in n or n.endswith("_assume_static_weights")]
 
 
 def test_validation_of_the_fused_and_peer_entry_points_without_a_device(b200):
@@ -72,25 +84,26 @@ def test_validation_of_the_fused_and_peer_entry_points_without_a_device(b200):
     for r in range(2):
         peers.recv[r], peers.out[r], peers.flags[r] = p, p, p
     ref = ctypes.byref(peers)
-    assert lib.b200q_reduce_gather(None, None, 256, 64, 1, None) == -1               # no peers
-    assert lib.b200q_reduce_gather(ref, None, 200, 64, 1, None) == -1                # M not a multiple of world * 128
-    assert lib.b200q_reduce_gather(ref, None, 256, 60, 1, None) == -1                # N % 8
-    assert lib.b200q_reduce_add_gather(ref, None, None, 256, 64, 1, None) == -1      # residual shard is required
+    assert lib.b200q_reduce_gather(None, None, 256, 64, 1, None, None) == -1               # no peers
+    assert lib.b200q_reduce_gather(ref, None, 200, 64, 1, None, None) == -1                # M not a multiple of world * 128
+    assert lib.b200q_reduce_gather(ref, None, 256, 60, 1, None, None) == -1                # N % 8
+    assert lib.b200q_reduce_add_gather(ref, None, None, 256, 64, 1, None, None) == -1      # residual shard is required
+    assert lib.b200q_fp8_gemm_reduce_scatter(p, p, 1, p, p, 1, ref, 200, 64, 64, None, None) == -1   # M not a multiple of world * 128
     peers.world = 9
-    assert lib.b200q_reduce_gather(ref, None, 9 * 128, 64, 1, None) == -1            # more than 8 ranks
+    assert lib.b200q_reduce_gather(ref, None, 9 * 128, 64, 1, None, None) == -1            # more than 8 ranks
     gp = _lib.GatherPeers()
     gp.rank, gp.world = 1, 2
     for r in range(2):
         gp.recv[r], gp.codes[r], gp.scales[r], gp.flags[r] = p, p, p, p
     gref = ctypes.byref(gp)
     f = lib.b200q_reduce_add_rms_norm_fp8_quantize_gather
-    assert f(gref, None, None, p, 1e-5, 256, 64, 1, None) == -1                      # no residual shard
-    assert f(gref, None, p, None, 1e-5, 256, 64, 1, None) == -1                      # no norm weight
-    assert f(gref, None, p, p, 1e-5, 256, 72, 1, None) == -1                         # N % 16
-    assert f(gref, None, p, p, 1e-5, 256, 16400, 1, None) == -1                      # N beyond 16384
-    assert f(gref, None, p, p, 1e-5, 384, 64, 1, None) == -1                         # M not a multiple of world * 128
+    assert f(gref, None, None, p, 1e-5, 256, 64, 1, None, None) == -1                      # no residual shard
+    assert f(gref, None, p, None, 1e-5, 256, 64, 1, None, None) == -1                      # no norm weight
+    assert f(gref, None, p, p, 1e-5, 256, 72, 1, None, None) == -1                         # N % 16
+    assert f(gref, None, p, p, 1e-5, 256, 16400, 1, None, None) == -1                      # N beyond 16384
+    assert f(gref, None, p, p, 1e-5, 384, 64, 1, None, None) == -1                         # M not a multiple of world * 128
     gp.codes[1] = None
-    assert f(gref, None, p, p, 1e-5, 256, 64, 1, None) == -1                         # a peer buffer is missing
+    assert f(gref, None, p, p, 1e-5, 256, 64, 1, None, None) == -1                         # a peer buffer is missing
 
 
 def test_product_does_not_reach_into_test_infrastructure():
@@ -137,9 +150,18 @@ def test_meta_kernels_shapes_and_dtypes(b200):
     codes, sf, g = torch.ops.tensorrt.b200_nvfp4_quantize(x, a)
     assert codes.shape == (3, 5, 32) and sf.shape == (512,) and g.shape == ()
     w = torch.empty(128, 64, device="meta", dtype=torch.uint8)
-    out = torch.ops.tensorrt.b200_fp8_gemm(torch.empty(3, 5, 64, device="meta", dtype=torch.uint8),
-                                           torch.empty(15, device="meta"), w, torch.empty(128, device="meta"), None)
-    assert out.shape == (3, 5, 128) and out.dtype == torch.bfloat16
+    xc, xs, ws = torch.empty(3, 5, 64, device="meta", dtype=torch.uint8), torch.empty(15, device="meta"), torch.empty(128, device="meta")
+    bias = torch.empty(128, device="meta", dtype=torch.bfloat16)
+    for out in (torch.ops.tensorrt.b200_fp8_gemm(xc, xs, w, ws), torch.ops.tensorrt.b200_fp8_gemm_bias(xc, xs, w, ws, bias)):
+        assert out.shape == (3, 5, 128) and out.dtype == torch.bfloat16
+    # one-node linears: the result has the activation's shape prefix and dtype
+    for dt in (torch.bfloat16, torch.float16):
+        xa = torch.empty(3, 5, 64, device="meta", dtype=dt)
+        for out in (torch.ops.tensorrt.b200_fp8_linear(xa, a, w, ws), torch.ops.tensorrt.b200_fp8_linear_bias(xa, a, w, ws, bias)):
+            assert out.shape == (3, 5, 128) and out.dtype == dt
+        w4, s4 = torch.empty(128, 32, device="meta", dtype=torch.uint8), torch.empty(512, device="meta", dtype=torch.uint8)
+        for out in (torch.ops.tensorrt.b200_nvfp4_linear(xa, a, w4, s4, a), torch.ops.tensorrt.b200_nvfp4_linear_bias(xa, a, w4, s4, a, bias)):
+            assert out.shape == (3, 5, 128) and out.dtype == dt
 
 
 def test_export_keeps_quantize_nodes(b200):
@@ -162,25 +184,102 @@ def test_export_keeps_quantize_nodes(b200):
     assert torch.ops.tensorrt.dynamic_block_quantize_op.default in targets
 
 
-def test_plugin_registration_with_fake_custom_op(b200):
-    calls = []
+def _generator_like_custom_op(calls):
+    """A stand-in for torch_tensorrt's `plugins.custom_op` that applies the rules of its generator
+    (py/torch_tensorrt/dynamo/conversion/plugins/_generate_plugin.py:113-185, 196-270;
+    _generate_plugin_converter.py:126,143) to the op it is given:
+      - every argument type must be exactly Tensor, float, int, bool or str ("arg type is not handled");
+      - tensor arguments come before all others (the converter slices `args[0:len(tensor_inputs)]`);
+      - the fake kernel is run on float32 fake tensors with symbolic sizes for every tensor argument;
+      - every output descriptor is `tensor_args[0].like()`: the output dtype is the first tensor
+        argument's, which must agree with what the op's fake kernel returns for real dtypes."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from torch.fx.experimental.symbolic_shapes import DimDynamic, ShapeEnv
 
-    def fake_custom_op(name, capability_validator=None, priority=None, supports_dynamic_shapes=False,
-                       requires_output_allocator=False):
+    def custom_op(name, capability_validator=None, priority=None, supports_dynamic_shapes=False,
+                  requires_output_allocator=False, *, use_aot_if_available=True, _aot_register=None):
         ns, op = name.split("::")
-        overload = getattr(getattr(torch.ops, ns), op).default
-        schema = overload._schema
-        # the generated converter slices tensors first, scalars after
+        packet = getattr(getattr(torch.ops, ns), op)
+        schema = packet._schemas[""]
         kinds = [str(a.type) for a in schema.arguments]
-        first_scalar = next((i for i, k in enumerate(kinds) if not k.startswith("Tensor")), len(kinds))
-        assert all(not k.startswith("Tensor") for k in kinds[first_scalar:]), f"{name}: tensor after scalar"
+        for k in kinds:
+            if k not in ("Tensor", "float", "int", "bool", "str"):
+                raise ValueError("arg type is not handled")
+        n_tensors = sum(k == "Tensor" for k in kinds)
+        assert all(k == "Tensor" for k in kinds[:n_tensors]), f"{name}: a tensor argument follows a scalar"
+        scalars = {"int": 16, "float": 1.0, "bool": False, "str": "sum"}
+        scalar_args = {"tensorrt::quantize_op": [8, 4, False, False],
+                       "tensorrt::b200_dynamic_block_quantize_tensors_first": [16, 4, 2, 8, 4]}.get(name, [scalars[k] for k in kinds[n_tensors:]])
+        shape_env = ShapeEnv()
+        with FakeTensorMode(shape_env=shape_env):
+            fake_args = []
+            for i in range(n_tensors):
+                # amax-like arguments are scalars in every call site; the rest get 2-D symbolic shapes
+                arg = schema.arguments[i].name
+                if "amax" in arg or "global" in arg:
+                    fake_args.append(torch.randn(()))
+                elif "scales" in arg or arg == "bias":
+                    fake_args.append(torch.randn(64))
+                else:
+                    fake_args.append(torch.randn(64, 64))
+            out = packet(*fake_args, *scalar_args)
+        outs = list(out) if isinstance(out, (tuple, list)) else [out]
+        assert len(outs) == len(schema.returns)
+        for o in outs:
+            assert o.dtype == fake_args[0].dtype, f"{name}: output dtype {o.dtype} is not the first tensor argument's"
         calls.append((name, priority, supports_dynamic_shapes))
 
-    names = b200.register_with_torch_tensorrt(custom_op=fake_custom_op, priority="HIGH")
-    assert "tensorrt::quantize_op" in names
-    assert any("dynamic_block_quantize" in n for n in names)
+    return custom_op
+
+
+def test_plugin_registration_against_the_generator_rules(b200):
+    calls, converters = [], {}
+
+    def decorator(target, *, priority=None, supports_dynamic_shapes=False, **kw):
+        def reg(fn):
+            converters[target] = (fn, priority, supports_dynamic_shapes)
+            return fn
+        return reg
+
+    seen = {}
+
+    def lookup(overload):
+        def impl(ctx, target, args, kwargs, name):
+            seen["call"] = (target, args, kwargs, name)
+            return "layer-output"
+        return impl
+
+    names = b200.register_with_torch_tensorrt(custom_op=_generator_like_custom_op(calls), priority="HIGH",
+                                              converter_decorator=decorator, lookup=lookup)
+    assert "tensorrt::quantize_op" in names and "tensorrt::b200_fp8_linear_bias" in names and "tensorrt::b200_nvfp4_linear" in names
+    assert names[-1] == "tensorrt::dynamic_block_quantize_op"
     assert all(p == "HIGH" and dyn for _, p, dyn in calls)
-    # without torch_tensorrt installed the real registration is a logged no-op
+    # the hand-written converter sits on the ORIGINAL target at HIGH priority and forwards with amax moved forward
+    target = torch.ops.tensorrt.dynamic_block_quantize_op.default
+    fn, prio, dyn = converters[target]
+    assert prio == "HIGH" and dyn
+    assert fn(None, target, ("x", 16, "amax", 4, 2, 8, 4), {}, "node7") == "layer-output"
+    alias = torch.ops.tensorrt.b200_dynamic_block_quantize_tensors_first.default
+    assert seen["call"] == (alias, ("x", "amax", 16, 4, 2, 8, 4), {}, "node7")
+    assert fn(None, target, ("x", 16, "amax"), {"num_bits": 4, "exponent_bits": 2, "scale_num_bits": 8, "scale_exponent_bits": 4},
+              "n") == "layer-output"
+    with pytest.raises(ValueError):
+        fn(None, target, ("x", 16), {}, "n")
+
+
+def test_the_generator_rules_reject_what_the_real_generator_rejects(b200):
+    """The stand-in is only worth something if it fails where the real one would: an optional
+    tensor argument, and an op whose output dtype differs from its first tensor argument's."""
+    custom_op = _generator_like_custom_op([])
+    with pytest.raises(ValueError, match="arg type is not handled"):
+        custom_op("tensorrt::b200_fp8_quantize")            # (Tensor input, Tensor? amax)
+    with pytest.raises(AssertionError, match="output dtype"):
+        custom_op("tensorrt::b200_fp8_gemm")                # bf16 out of uint8 codes
+    with pytest.raises(AssertionError, match="follows a scalar"):
+        custom_op("tensorrt::dynamic_block_quantize_op")    # (input, block_size, amax, ...)
+
+
+def test_registration_is_a_logged_no_op_without_torch_tensorrt(b200):
     try:
         import torch_tensorrt  # noqa: F401
     except Exception:

@@ -166,6 +166,43 @@ def _worker_missing_peer(rank, world, store_path):
         raise AssertionError("rendezvous with a missing peer did not fail")
 
 
+def _worker_row_parallel_bias(rank, world, store_path):
+    """A checkpoint-loaded row-parallel linear keeps its bias on rank 0 only ("linear, then all-reduce"
+    adds it once); the fused path adds the bias after the sum on the owner of each row and needs the
+    full bias everywhere.  Both routes must give the same result."""
+    _init(rank, world, store_path)
+    import oracle as o
+    from tensorrt_b200.tp import replicate_row_parallel_bias
+
+    g = torch.Generator().manual_seed(3)
+    x, w = torch.randn(8, 64, generator=g).bfloat16(), (torch.randn(16, 64, generator=g) * 0.1).bfloat16()
+    full_bias = torch.randn(16, generator=g).bfloat16()
+    ks = 64 // world
+    xs, wr = x[:, rank * ks:(rank + 1) * ks].contiguous(), w[:, rank * ks:(rank + 1) * ks].contiguous()
+    loaded = full_bias.clone() if rank == 0 else None                     # what checkpoint.load_quantized_linears returns
+    # route 1: linear (+ the bias where it lives), then all-reduce
+    part = o.fp8_linear_ref(xs, wr, loaded)
+    total = part.clone()
+    dist.all_reduce(total)
+    # route 2 (fused convention): replicate the bias, sum the bias-free partials, add the bias once
+    rep = replicate_row_parallel_bias(loaded)
+    assert rep is not None and torch.equal(rep, full_bias)
+    bare = o.fp8_linear_ref(xs, wr)
+    dist.all_reduce(bare)
+    assert torch.allclose(bare + rep.float(), total, atol=1e-5)
+    # already replicated: returned as is; absent everywhere: None; a bias on a rank other than 0 only: error
+    assert replicate_row_parallel_bias(full_bias) is full_bias
+    assert replicate_row_parallel_bias(None) is None
+    try:
+        replicate_row_parallel_bias(full_bias if rank == 1 else None)
+    except ValueError as e:
+        assert "rank 0" in str(e)
+    else:
+        raise AssertionError("a bias that lives on rank 1 only was accepted")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def _spawn(fn, world, *args):
     with tempfile.TemporaryDirectory() as d:
         store = os.path.join(d, "store")
@@ -181,6 +218,10 @@ def test_two_rank_stack_and_all_reduce_op(mode, tmp_path):
 
 def test_shape_mismatch_is_detected_on_the_host():
     _spawn(_worker_mismatch, 2)
+
+
+def test_row_parallel_bias_conventions_agree():
+    _spawn(_worker_row_parallel_bias, 2)
 
 
 def test_missing_peer_times_out_on_the_host():
