@@ -152,28 +152,26 @@ def gemm_case(capi, kind, M, N, K, seed, min_ms=500.0):
         else:
             capi.nvfp4_gemm(xa[0], xa[1], xa[2], wa[0], wa[1], wa[2], bias)
 
-    if M <= 128:
-        # decode-sized calls are shorter than the host work of issuing them: time them the way a
-        # serving loop runs them, as a CUDA graph of back-to-back launches over the operand sets,
-        # with the weights declared static per call (quantized and complete long before)
+    # Every case is timed as a CUDA graph of back-to-back launches over the operand sets, the way a
+    # serving loop runs them: below ~100 us a launch issued from Python costs more host time than the
+    # kernel takes on the device.  Decode-sized calls (M <= 128) declare their weights static per
+    # call (quantized and complete long before), which lets consecutive launches overlap their prologues.
+    torch.cuda.synchronize()
+    reps = max(nsets, 16 if M <= 2048 else 4)
+    with capi.gemm_config(static_weights=(M <= 128)):
+        for _ in range(3):
+            fn()
         torch.cuda.synchronize()
-        reps = max(nsets, 16)
-        with capi.gemm_config(static_weights=True):
-            for _ in range(3):
-                fn()
-            torch.cuda.synchronize()
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=side):
-                    for _ in range(reps):
-                        fn()
-            torch.cuda.current_stream().wait_stream(side)
-        ms, n = time_device(graph.replay, min_ms, min_iters=max(4, 50 // reps + 1))
-        ms, n = ms / reps, n * reps
-    else:
-        ms, n = time_device(fn, min_ms)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(reps):
+                    fn()
+        torch.cuda.current_stream().wait_stream(side)
+    ms, n = time_device(graph.replay, min_ms, min_iters=max(4, 50 // reps + 1))
+    ms, n = ms / reps, n * reps
     if capi.device_status() != 0:
         raise RuntimeError("device-side wait timed out")
     return ms, n
@@ -182,8 +180,8 @@ def gemm_case(capi, kind, M, N, K, seed, min_ms=500.0):
 def gemm_kernel_name(kind, M, N):
     if M <= 128:
         return f"gemm_smallm_kernel<{kind}>"
-    if kind == "fp8" and ((M + 255) // 256) * ((N + 255) // 256) >= 74:
-        return "gemm_pair_kernel<fp8>"
+    if ((M + 255) // 256) * ((N + 255) // 256) >= 74:
+        return "gemm_pair_kernel<fp8>" if kind == "fp8" else "gemm_nvf4_pair_kernel"
     return f"gemm_kernel<{kind}>"
 
 
@@ -270,8 +268,8 @@ def run_gemm(args, kind):
         "config": {"workload": f"{kind} quantized-linear GEMM sweep, headline shape M,N,K = {M},{N},{K}; x ~ N(0,1), "
                                "W ~ N(0,0.02), bias ~ N(0,0.01); operands pre-quantized and resident in HBM",
                    "l2": "operand sets rotate so that sets smaller than L2 are not re-read from L2",
-                   "small_m": "M <= 128: timed as a CUDA graph of back-to-back launches (host issue time excluded), "
-                              "weights declared static per call (b200q_cfg::static_weights)"},
+                   "timing": "every shape is timed as a CUDA graph of back-to-back launches (host issue time excluded); "
+                             "M <= 128: weights declared static per call (b200q_cfg::static_weights)"},
         "clocks": clocks.summary(), "gpu_launches": head["launches"], "roofline": head["roofline"], "shapes": results,
     }
     print(json.dumps(line))

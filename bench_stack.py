@@ -323,7 +323,7 @@ def run(args):
                      "frac": tflops / world / (peaks["bf16_tflops_sustained"] * scale),
                      "peak_source": f"{peaks['source']} sustained cuBLAS bf16 x{int(scale)} per GPU; GEMM flops only, per GPU, "
                                     "over the whole step (glue and exchange kernels included in the time)",
-                     "traffic": None, "kernel": "gemm_pair_kernel<fp8>" if cfg.mode == "fp8" else "gemm_kernel<nvfp4, 256>",
+                     "traffic": None, "kernel": "gemm_pair_kernel<fp8>" if cfg.mode == "fp8" else "gemm_nvf4_pair_kernel",
                      "algorithmic_flops_per_step_per_gpu": flops / world},
     }
     if parity is not None:

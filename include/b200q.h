@@ -143,7 +143,8 @@ int b200q_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales_swizzled,
  * Last argument of the GEMM entry points and of the peer-memory reductions; NULL = all defaults.
  * Nothing here is process-wide: two callers (threads, stacks, graphs) never see each other's choices.
  *   tile_n          GEMM tile selection.  0 = chosen per problem (default); 128 or 256 = single-CTA
- *                   tiles of 128 x tile_n; 512 = CTA-pair kernel (256 x 256 tiles, cta_group::2);
+ *                   tiles of 128 x tile_n; 512 = CTA-pair kernels (256 x 256 tiles, cta_group::2; chosen
+ *                   automatically when the problem has at least one such tile per SM pair);
  *                   1001 / 1002 / 1004 / 1008 = small-M kernel (weights on the tensor core's M side,
  *                   K split over a cluster of 1 / 2 / 4 / 8 CTAs, partial tiles summed through
  *                   distributed shared memory; chosen automatically for M <= 128, ignored for larger

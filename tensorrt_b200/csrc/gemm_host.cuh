@@ -4,6 +4,7 @@
 #include <cuda.h>
 
 #include "gemm_kernel_2cta.cuh"
+#include "gemm_kernel_nvf4_pair.cuh"
 #include "gemm_kernel_splitk.cuh"
 
 namespace b200q {
@@ -152,6 +153,44 @@ int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, c
   return B200Q_OK;
 }
 
+// NVFP4 CTA-pair kernel with the scales stored to tensor memory by warps (gemm_kernel_nvf4_pair.cuh).
+inline int launch_nvf4_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st) {
+  using C = CfgNvPair;
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200Q_ERR_CUDA;
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(gemm_nvf4_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+      return B200Q_ERR_CUDA;
+    configured[dev] = true;
+  }
+  CUtensorMap ta, tb, tsfa, tsfb;
+  if (int rc = make_operand_map(&ta, a, p.M, p.k_bytes, 128)) return rc;
+  if (int rc = make_operand_map(&tb, b, p.N, p.k_bytes, 128)) return rc;
+  if (int rc = make_scale_map(&tsfa, p.sfa, (p.M + 127) / 128, p.sf_col_tiles, 1)) return rc;
+  if (int rc = make_scale_map(&tsfb, p.sfb, (p.N + 127) / 128, p.sf_col_tiles, 2)) return rc;
+  const int tiles = ((p.M + kPairM - 1) / kPairM) * ((p.N + kPairN - 1) / kPairN);
+  const int max_pairs = sm_count() / 2;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(pairs * 2));
+  cfg.blockDim = dim3(kNvPairThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemm_nvf4_pair_kernel<0>, ta, tb, tsfa, tsfb, p) != cudaSuccess) {
+    cudaGetLastError();
+    return B200Q_ERR_CUDA;
+  }
+  return B200Q_OK;
+}
+
 // Small-M kernel (M <= 128): operands swapped, one cluster of `splits` CTAs per tile of 128
 // weight rows.  Up to one CTA per SM the operand ring takes all of shared memory; beyond that
 // the ring is sized so that two CTAs share an SM, which lets one CTA's prologue and cluster
@@ -243,9 +282,18 @@ int launch(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, const 
   }
   if (bn >= 1000) bn = 0;
   const int64_t pair_tiles = static_cast<int64_t>((p.M + kPairM - 1) / kPairM) * ((p.N + kPairN - 1) / kPairN);
-  // measured: the CTA-pair kernel wins for FP8 (2.9 vs 2.75 PFLOP/s at 8192^3); for NVFP4 the
-  // single-CTA 128 x 256 tile is faster (3.45 vs 3.2), so it is only used there when forced
-  if (bn == 512 || (bn == 0 && !NVF4 && pair_tiles >= sm_count() / 2)) return launch_pair<NVF4>(a, b, p, st, rs);
+  // CTA-pair kernels (256 x 256 tiles) whenever they fill the SM pairs: measured 2.9 vs 2.75 PFLOP/s
+  // for FP8 and 4.8 vs 3.4 for NVFP4 at 8192^3 against the single-CTA 128 x 256 tile.  The NVFP4 pair
+  // kernel with the scale warps writes local output only; the reduce-scatter epilogue keeps the
+  // generic kernels.
+  if (bn == 512 || (bn == 0 && pair_tiles >= sm_count() / 2)) {
+    if constexpr (NVF4) {
+      if (rs == nullptr) return launch_nvf4_pair(a, b, p, st);
+      if (bn == 512) return launch_pair<NVF4>(a, b, p, st, rs);
+    } else {
+      return launch_pair<NVF4>(a, b, p, st, rs);
+    }
+  }
   if (bn != 128 && bn != 256) {
     const int64_t tiles256 = static_cast<int64_t>((p.M + kBM - 1) / kBM) * ((p.N + 255) / 256);
     bn = (tiles256 >= sm_count()) ? 256 : 128;
