@@ -206,8 +206,9 @@ def run(args):
     if not tp and world > 1:
         raise SystemExit("nvfp4_stack is a single-GPU workload; use tp_stack for --gpus > 1")
     want_graph = getattr(args, "decode_graph", -1)
-    if want_graph > 0 and world > 1:
-        raise SystemExit("--decode-graph 1 is refused at TP > 1: a captured decode step with NCCL all-reduces inside is not supported")
+    pull = bool(world > 1 and args.fused and cfg.mode == "fp8")     # decode steps: pull all-reduce over peer memory, no NCCL in the step
+    if want_graph > 0 and world > 1 and not pull:
+        raise SystemExit("--decode-graph 1 is refused at TP > 1 with NCCL all-reduces inside the step: capturing those is not supported")
     tokens = batch * seq
     mb = args.micro_batches if world > 1 else 1
     if mb <= 0:
@@ -224,7 +225,7 @@ def run(args):
 
     t0 = time.time()
     stack = DecoderStack(cfg, random_layer_weights(cfg, seed, device=dev), rank=rank, world=world,
-                         slabs=args.slabs if world > 1 else 1, fused_rows=tokens if fused else 0)
+                         slabs=args.slabs if world > 1 else 1, fused_rows=tokens if fused else 0, pull_rows=64 if pull else 0)
     torch.cuda.synchronize()
     build_s = time.time() - t0
 
@@ -259,13 +260,15 @@ def run(args):
         decode_fn = lambda: stack(hd)  # noqa: E731
         graphed = False
         if want_graph < 0:
-            want_graph = 1 if world == 1 else 0
+            want_graph = 1 if (world == 1 or pull) else 0
         if want_graph:
             # a decode step is ~700 short launches: issuing them from Python costs more than running
-            # them, so on one GPU the step is replayed as one CUDA graph, the way a serving loop runs it
+            # them, so the step is replayed as one CUDA graph, the way a serving loop runs it (at TP > 1
+            # only with the pull all-reduce, whose launches are this library's own kernels)
             for _ in range(2):
                 stack(hd)
             torch.cuda.synchronize()
+            bc.barrier(world)
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
@@ -276,6 +279,7 @@ def run(args):
             decode_fn, graphed = graph.replay, True
         dms = bc.timed(lambda i: decode_fn(), dsteps, 3, world)
         decode = {"tokens_per_s": 64 * dsteps / (dms * 1e-3), "ms_per_step": dms / dsteps, "batch": 64, "cuda_graph": graphed,
+                  "all_reduce": "pull over peer memory, fused with residual add + RMSNorm + FP8 quantize" if pull else ("NCCL" if world > 1 else "none"),
                   "weight_bytes_per_rank": cfg.weights_per_layer() * cfg.layers // world,
                   "weight_stream_GBps_per_rank": cfg.weights_per_layer() * cfg.layers / world / (dms / dsteps * 1e-3) / 1e9,
                   "frac_of_measured_hbm": cfg.weights_per_layer() * cfg.layers / world / (dms / dsteps * 1e-3) / 1e9

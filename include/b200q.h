@@ -261,6 +261,39 @@ int b200q_reduce_add_rms_norm_fp8_quantize_gather(const b200q_gather_peers* peer
 int b200q_reduce_add_gather(const b200q_peers* peers, const void* bias, const void* residual_shard, int64_t M,
                             int64_t N, uint32_t epoch, b200q_stream_t stream, const b200q_cfg* cfg);
 
+/* Decode-sized all-reduce by pulling (M <= 1024 rows, meant for the few tokens of a decode step).
+ * Replaces the same ALL_REDUCE layer as above (py/torch_tensorrt/dynamo/conversion/impl/nccl_ops.py:440-451)
+ * where the message is about a megabyte and one collective call per linear costs more than the
+ * transfer.  The row-parallel GEMM (b200q_fp8_gemm / b200q_nvfp4_gemm, `out` = this rank's partial
+ * buffer) is followed by
+ *   b200q_pull_signal   tells every peer that this rank's partial is complete;
+ *   b200q_pull_reduce_add_rms_norm_fp8_quantize
+ *                       on EVERY rank: waits (bounded) for all peers' signals, reads all `world`
+ *                       partials over peer memory, sums them in rank order (fp32), adds the bias once,
+ *                       h += that (in place, the replicated residual stream [M, N] bf16), RMSNorm with
+ *                       `norm_weight`, per-token FP8 codes [M, N] and scales [M] into LOCAL buffers;
+ *   b200q_pull_reduce_add   the same without norm and quantize (end of a stack): h += sum + bias.
+ * All ranks compute identical bits.  partial[r] = rank r's partial [M, N] bf16 for THIS all-reduce;
+ * consecutive all-reduces of a group must alternate between two buffers per rank (a rank may
+ * overwrite a buffer only after the next all-reduce on the other buffer has completed).
+ * flags[r] = rank r's world + 1 uint32 words for this protocol, zeroed once; the call counter lives
+ * in them on the device, so the launches can be captured in a CUDA graph and replayed.  N % 16 == 0,
+ * N <= 16384. */
+typedef struct b200q_pull_peers {
+  int32_t rank;
+  int32_t world;
+  void* partial[8];
+  uint32_t* flags[8];
+} b200q_pull_peers;
+
+int b200q_pull_signal(const b200q_pull_peers* peers, b200q_stream_t stream);
+int b200q_pull_reduce_add_rms_norm_fp8_quantize(const b200q_pull_peers* peers, const void* bias, void* h,
+                                                const void* norm_weight, float eps, uint8_t* codes_out,
+                                                float* scales_out, int64_t M, int64_t N, b200q_stream_t stream,
+                                                const b200q_cfg* cfg);
+int b200q_pull_reduce_add(const b200q_pull_peers* peers, const void* bias, void* h, int64_t M, int64_t N,
+                          b200q_stream_t stream, const b200q_cfg* cfg);
+
 /* ------------------------------------------------------------------ glue of the decoder linear stack
  * The benchmark workloads wrap the quantized linears in a Llama-shaped decoder layer
  * (RMSNorm -> QKV -> attention replaced by identity on V -> O -> residual -> RMSNorm ->

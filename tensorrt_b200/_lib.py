@@ -39,6 +39,9 @@ SIGNATURES = {
     "b200q_reduce_gather": (_c.c_int, [_p, _p, _i64, _i64, _c.c_uint32, _p, _p]),
     "b200q_reduce_add_gather": (_c.c_int, [_p, _p, _p, _i64, _i64, _c.c_uint32, _p, _p]),
     "b200q_reduce_add_rms_norm_fp8_quantize_gather": (_c.c_int, [_p, _p, _p, _p, _c.c_float, _i64, _i64, _c.c_uint32, _p, _p]),
+    "b200q_pull_signal": (_c.c_int, [_p, _p]),
+    "b200q_pull_reduce_add_rms_norm_fp8_quantize": (_c.c_int, [_p, _p, _p, _p, _c.c_float, _p, _p, _i64, _i64, _p, _p]),
+    "b200q_pull_reduce_add": (_c.c_int, [_p, _p, _p, _i64, _i64, _p, _p]),
     "b200q_rms_norm": (_c.c_int, [_p, _p, _p, _i64, _i64, _c.c_float, _p]),
     "b200q_add_rms_norm_fp8_quantize": (_c.c_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _c.c_float, _p]),
     "b200q_silu_mul": (_c.c_int, [_p, _p, _i64, _i64, _p]),
@@ -71,6 +74,11 @@ class GatherPeers(ctypes.Structure):
     """struct b200q_gather_peers of include/b200q.h."""
     _fields_ = [("rank", _c.c_int32), ("world", _c.c_int32), ("recv", _p * 8), ("codes", _p * 8), ("scales", _p * 8),
                 ("flags", _p * 8)]
+
+
+class PullPeers(ctypes.Structure):
+    """struct b200q_pull_peers of include/b200q.h."""
+    _fields_ = [("rank", _c.c_int32), ("world", _c.c_int32), ("partial", _p * 8), ("flags", _p * 8)]
 
 
 _lib = None

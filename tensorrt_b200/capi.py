@@ -193,13 +193,21 @@ def _cfg(tile_n, static_weights):
     return cfg_ref(cur[0] if tile_n is None else tile_n, cur[1] if static_weights is None else static_weights)
 
 
-def fp8_gemm(a_codes, a_scales, b_codes, b_scales, bias=None, tile_n=None, static_weights=None) -> torch.Tensor:
-    """bf16 [.., N] = dequant(a [.., K]) @ dequant(b [N, K])^T + bias."""
+def _gemm_out(out, shape, device):
+    if out is None:
+        return torch.empty(shape, dtype=torch.bfloat16, device=device)
+    if tuple(out.shape) != tuple(shape) or out.dtype != torch.bfloat16 or not out.is_contiguous() or out.device != device:
+        raise ValueError(f"out must be a contiguous bf16 tensor of shape {tuple(shape)} on {device}")
+    return out
+
+
+def fp8_gemm(a_codes, a_scales, b_codes, b_scales, bias=None, tile_n=None, static_weights=None, out=None) -> torch.Tensor:
+    """bf16 [.., N] = dequant(a [.., K]) @ dequant(b [N, K])^T + bias (into `out` when given)."""
     _need_cuda(a_codes, a_scales, b_codes, b_scales, bias)
     a_codes, b_codes = a_codes.contiguous(), b_codes.contiguous()
     N, K = b_codes.shape
     M = a_codes.numel() // K
-    out = torch.empty(*a_codes.shape[:-1], N, dtype=torch.bfloat16, device=a_codes.device)
+    out = _gemm_out(out, (*a_codes.shape[:-1], N), a_codes.device)
     if bias is not None:
         bias = bias.to(torch.bfloat16).contiguous()
     with torch.cuda.device(a_codes.device):
@@ -209,13 +217,14 @@ def fp8_gemm(a_codes, a_scales, b_codes, b_scales, bias=None, tile_n=None, stati
     return out
 
 
-def nvfp4_gemm(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias=None, tile_n=None, static_weights=None) -> torch.Tensor:
+def nvfp4_gemm(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias=None, tile_n=None, static_weights=None,
+               out=None) -> torch.Tensor:
     _need_cuda(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias)
     a_codes, b_codes = a_codes.contiguous(), b_codes.contiguous()
     N, half = b_codes.shape
     K = half * 2
     M = a_codes.numel() // half
-    out = torch.empty(*a_codes.shape[:-1], N, dtype=torch.bfloat16, device=a_codes.device)
+    out = _gemm_out(out, (*a_codes.shape[:-1], N), a_codes.device)
     if bias is not None:
         bias = bias.to(torch.bfloat16).contiguous()
     with torch.cuda.device(a_codes.device):

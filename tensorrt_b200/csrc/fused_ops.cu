@@ -353,6 +353,9 @@ int b200q_add_rms_norm_fp8_quantize(const void* h, const void* delta, const void
   const int64_t groups = cols >> 3;
   int parts = 1;   // few tokens: split every row over a cluster so that the launch covers more SMs
   while (parts < 8 && rows * parts < 2 * sm_count() && groups / (parts * 2) >= kThreads / 2) parts *= 2;
+  // long rows: 16 groups per thread cost 92 registers (two CTAs per SM) and the kernel turns
+  // compute-bound on the exponentials; two CTAs per row at 8 groups per thread double the warps per SM
+  if (parts == 1 && groups > 8 * kThreads) parts = 2;
   const int items = static_cast<int>(((groups + parts - 1) / parts + kThreads - 1) / kThreads);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(rows * parts));
@@ -411,6 +414,9 @@ int b200q_silu_mul_fp8_quantize(const void* gate_up, uint8_t* codes_out, float* 
   // few tokens: split every row over a cluster so that the launch covers the SMs
   int parts = 1;
   while (parts < 8 && rows * parts < 2 * sm_count() && groups / (parts * 2) >= kThreads / 2) parts *= 2;
+  // long rows: 16 groups per thread cost 92 registers (two CTAs per SM) and the kernel turns
+  // compute-bound on the exponentials; two CTAs per row at 8 groups per thread double the warps per SM
+  if (parts == 1 && groups > 8 * kThreads) parts = 2;
   const int items = static_cast<int>(((groups + parts - 1) / parts + kThreads - 1) / kThreads);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(rows * parts));

@@ -277,6 +277,141 @@ reduce_norm_quant_gather_kernel(const GatherPeers pr, const __nv_bfloat16* __res
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Decode-sized all-reduce by pulling (a few tokens, M <= 128): the row-parallel GEMM leaves this
+// rank's partial [M, N] in its own symmetric buffer, a one-warp kernel tells every peer "my partial
+// number c is complete", and the reduction kernel of EVERY rank then reads all `world` partials
+// (its own and the peers', plain loads over NVLink), sums them in rank order, adds bias and residual,
+// applies RMSNorm and quantizes: the whole replicated activation of the next column-parallel GEMM,
+// with no second exchange and no library call.  All ranks compute the same sums in the same order,
+// so their results are the same bits.
+//
+// Flag words of a rank for this protocol: word s (s < world) = number of the last partial rank s has
+// completed; word `world` = this rank's own count (read and advanced on the device, so a CUDA graph
+// that contains these launches can be replayed).  Two partial buffers are used alternately by
+// consecutive all-reduces: a rank overwrites a buffer only after it has waited, in the all-reduce in
+// between, for a signal that every peer sends after it finished reading that buffer.
+struct PullPeers {
+  int rank, world;
+  const __nv_bfloat16* partial[8];   // every rank's partial [M, N] of this all-reduce (the buffer of this call)
+  uint32_t* flags[8];
+};
+
+__global__ void __launch_bounds__(32) pull_signal_kernel(const FlagPeers fp) {
+  uint32_t* mine = fp.flags[fp.rank];
+  const uint32_t c = *reinterpret_cast<volatile uint32_t*>(mine + fp.world) + 1u;
+  __syncwarp();
+  if (threadIdx.x < fp.world) {
+    __threadfence_system();
+    st_release_sys(fp.flags[threadIdx.x] + fp.rank, c);
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) *reinterpret_cast<volatile uint32_t*>(mine + fp.world) = c;
+}
+
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 r;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+  return r;
+}
+
+// One CTA per token.  QUANT: h += sum, RMSNorm, per-token FP8 codes and scales (local).  !QUANT: h += sum only.
+template <int ITEMS, bool QUANT>
+__global__ void __launch_bounds__(kThreads)
+pull_reduce_kernel(const PullPeers pr, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ h,
+                   const __nv_bfloat16* __restrict__ w, uint8_t* __restrict__ codes, float* __restrict__ scales, int64_t N, float eps,
+                   uint64_t limit_ns, int* status) {
+  __shared__ float red[kThreads / 32];
+  const int W = pr.world;
+  // every peer's partial of this all-reduce is complete (bounded wait on this rank's own flag words)
+  if (threadIdx.x < W) {
+    const uint32_t* mine = pr.flags[pr.rank];
+    const uint32_t c = *reinterpret_cast<const volatile uint32_t*>(mine + W);
+    if (!wait_epoch(mine + threadIdx.x, c, limit_ns)) atomicCAS(status, 0, 25);
+  }
+  __syncthreads();
+  if (*reinterpret_cast<volatile int*>(status) != 0) return;
+
+  const int groups = static_cast<int>(N >> 3);
+  const int64_t row = blockIdx.x;
+  float v[ITEMS][8];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int g = threadIdx.x + i * kThreads;
+    if (g < groups) {
+      const int64_t off = row * N + static_cast<int64_t>(g) * 8;
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+      for (int s = 0; s < W; ++s) {
+        const uint4 raw = ld_relaxed_sys_v4(pr.partial[s] + off);   // peer memory: never from a stale cache line
+        float q[8];
+        Elem<__nv_bfloat16>::unpack(raw, q);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += q[j];
+      }
+      if (bias != nullptr) {
+        float b[8];
+        Elem<__nv_bfloat16>::load8(bias + static_cast<int64_t>(g) * 8, b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += b[j];
+      }
+      float hv[8];
+      Elem<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(h + off), hv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[i][j] = __bfloat162float(__float2bfloat16_rn(hv[j] + __bfloat162float(__float2bfloat16_rn(acc[j]))));
+        ss = fmaf(v[i][j], v[i][j], ss);
+      }
+      Elem<__nv_bfloat16>::store8(h + off, v[i]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+    }
+  }
+  if constexpr (QUANT) {
+    const float inv = rsqrtf(block_sum<kThreads>(ss, red) / static_cast<float>(N) + eps);
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const int g = threadIdx.x + i * kThreads;
+      if (g < groups) {
+        float wv[8];
+        Elem<__nv_bfloat16>::load8(w + static_cast<int64_t>(g) * 8, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j] * inv * wv[j]));
+          amax = fmaxf(amax, fabsf(v[i][j]));
+        }
+      }
+    }
+    __syncthreads();  // every thread has left block_sum's scratch
+    amax = warp_max(amax);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = (threadIdx.x & 31) < kThreads / 32 ? red[threadIdx.x & 31] : 0.0f;
+    amax = warp_max(amax);
+    const float scale = fp8_scale_from_amax(amax);
+    if (threadIdx.x == 0) scales[row] = scale;
+    const float y = b200q_rcp_rn(scale);
+    const bool fast = b200q_div_fast_ok(scale);
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const int g = threadIdx.x + i * kThreads;
+      if (g < groups) {
+        float q[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[j] = fast ? b200q_div_by_shared(v[i][j], scale, y) : __fdiv_rn(v[i][j], scale);
+        const uint32_t lo = f32x2_to_e4m3x2(q[0], q[1]) | (f32x2_to_e4m3x2(q[2], q[3]) << 16);
+        const uint32_t hi = f32x2_to_e4m3x2(q[4], q[5]) | (f32x2_to_e4m3x2(q[6], q[7]) << 16);
+        *reinterpret_cast<uint2*>(codes + row * N + static_cast<int64_t>(g) * 8) = make_uint2(lo, hi);
+      }
+    }
+  }
+}
+
 }  // namespace
 }  // namespace b200q
 
@@ -382,6 +517,75 @@ int b200q_reduce_add_rms_norm_fp8_quantize_gather(const b200q_gather_peers* peer
   else if (items <= 4) reduce_norm_quant_gather_kernel<4><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, limit_ns, status);
   else reduce_norm_quant_gather_kernel<8><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, limit_ns, status);
   return check_launch();
+}
+
+static int fill_pull(PullPeers& pr, FlagPeers& fp, const b200q_pull_peers* peers) {
+  if (peers == nullptr) return B200Q_ERR_INVALID;
+  const int W = peers->world;
+  if (W < 1 || W > 8 || peers->rank < 0 || peers->rank >= W) return B200Q_ERR_INVALID;
+  pr.rank = fp.rank = peers->rank;
+  pr.world = fp.world = W;
+  for (int r = 0; r < W; ++r) {
+    if (peers->partial[r] == nullptr || peers->flags[r] == nullptr) return B200Q_ERR_INVALID;
+    if (!aligned(peers->partial[r], 16)) return B200Q_ERR_ALIGN;
+    pr.partial[r] = static_cast<const __nv_bfloat16*>(peers->partial[r]);
+    pr.flags[r] = fp.flags[r] = peers->flags[r];
+  }
+  return B200Q_OK;
+}
+
+int b200q_pull_signal(const b200q_pull_peers* peers, b200q_stream_t stream) {
+  PullPeers pr{};
+  FlagPeers fp{};
+  if (int rc = fill_pull(pr, fp, peers)) return rc;
+  if (int rc = check_arch()) return rc;
+  pull_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(fp);
+  return check_launch();
+}
+
+static int pull_reduce_impl(const b200q_pull_peers* peers, const void* bias, void* h, const void* norm_weight, float eps,
+                            uint8_t* codes_out, float* scales_out, int64_t M, int64_t N, bool quant, b200q_stream_t stream,
+                            const b200q_cfg* cfg) {
+  if (h == nullptr || M <= 0 || M > 1024 || N <= 0 || N % 16 != 0 || N > 16384) return B200Q_ERR_INVALID;
+  if (quant && (norm_weight == nullptr || codes_out == nullptr || scales_out == nullptr)) return B200Q_ERR_INVALID;
+  if (cfg != nullptr && cfg->reserved != 0) return B200Q_ERR_INVALID;
+  PullPeers pr{};
+  FlagPeers fp{};
+  if (int rc = fill_pull(pr, fp, peers)) return rc;
+  if (!aligned(h, 16) || (bias != nullptr && !aligned(bias, 16)) || (quant && (!aligned(norm_weight, 16) || !aligned(codes_out, 8))))
+    return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  int* status = gemm::device_status_word();
+  if (status == nullptr) return B200Q_ERR_CUDA;
+  const uint64_t limit_ns = peer_wait_ns(cfg);
+  const int items = static_cast<int>(((N >> 3) + kThreads - 1) / kThreads);
+  const unsigned grid = static_cast<unsigned>(M);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
+  __nv_bfloat16* hp = static_cast<__nv_bfloat16*>(h);
+  const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(norm_weight);
+#define B200Q_PULL(I)                                                                                                        \
+  do {                                                                                                                         \
+    if (quant) pull_reduce_kernel<I, true><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, codes_out, scales_out, N, eps, limit_ns, status); \
+    else pull_reduce_kernel<I, false><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, codes_out, scales_out, N, eps, limit_ns, status);      \
+  } while (0)
+  if (items <= 1) B200Q_PULL(1);
+  else if (items <= 2) B200Q_PULL(2);
+  else if (items <= 4) B200Q_PULL(4);
+  else B200Q_PULL(8);
+#undef B200Q_PULL
+  return check_launch();
+}
+
+int b200q_pull_reduce_add_rms_norm_fp8_quantize(const b200q_pull_peers* peers, const void* bias, void* h, const void* norm_weight,
+                                                float eps, uint8_t* codes_out, float* scales_out, int64_t M, int64_t N,
+                                                b200q_stream_t stream, const b200q_cfg* cfg) {
+  return pull_reduce_impl(peers, bias, h, norm_weight, eps, codes_out, scales_out, M, N, true, stream, cfg);
+}
+
+int b200q_pull_reduce_add(const b200q_pull_peers* peers, const void* bias, void* h, int64_t M, int64_t N, b200q_stream_t stream,
+                          const b200q_cfg* cfg) {
+  return pull_reduce_impl(peers, bias, h, nullptr, 0.0f, nullptr, nullptr, M, N, false, stream, cfg);
 }
 
 }  // extern "C"

@@ -332,13 +332,16 @@ class DecoderStack:
     of full (unsharded) bf16 weights; each is sharded, quantized and dropped."""
 
     def __init__(self, cfg: StackConfig, weights, backend=None, rank: int = 0, world: int = 1, group=None, slabs: int = 1,
-                 fused_rows: int = 0):
+                 fused_rows: int = 0, pull_rows: int = 0):
         """`fused_rows` > 0: row-parallel linears use the fused GEMM + peer-memory all-reduce
-        (tp.FusedRowParallel) for up to that many rows; other row counts use NCCL."""
+        (tp.FusedRowParallel) for up to that many rows; other row counts use NCCL.
+        `pull_rows` > 0 (FP8 stacks): forwards of at most that many tokens (decode steps) use the pull
+        all-reduce fused with residual add, RMSNorm and quantize (tp.PullRowParallel)."""
         cfg.check(world)
         self.cfg, self.rank, self.world, self.group = cfg, rank, world, group
         self._comm = None
         self._fused = None
+        self._pull = None
         self.check_status = True                 # forward() polls the device status word on the fused TP path
         self.backend = backend or CudaBackend(cfg.mode)
         reduce = AllReduce(group) if world > 1 else None
@@ -357,6 +360,10 @@ class DecoderStack:
             else:
                 be = self.backend
                 row_parallel = lambda x, qw, amax=None: reduce(be.linear(x, qw, amax))  # noqa: E731
+        if world > 1 and pull_rows > 0 and cfg.mode == "fp8":
+            from .tp import PullRowParallel
+
+            self._pull = PullRowParallel(cfg.mode, pull_rows, cfg.hidden, group)
         self.layers = [DecoderLayer(cfg, shard_layer_weights(w, cfg, rank, world) if world > 1 else w, self.backend, world,
                                     row_parallel) for w in weights]
         # every weight is quantized and resident from here on: forward() may promise its own GEMM
@@ -380,8 +387,12 @@ class DecoderStack:
             raise ValueError(f"sharded must be False, True or 'collectives', got {sharded!r}")
         if self.world == 1:
             sharded = False
-        if self._fused is not None and self.check_status:
+        if (self._fused is not None or self._pull is not None) and self.check_status and not (
+                h.is_cuda and torch.cuda.is_current_stream_capturing()):
             self.raise_if_device_error()
+        if self._pull is not None and h.is_cuda and self._pull.usable(h.shape[0]):
+            with capi.gemm_config(static_weights=self._static_weights):
+                return self._walk_pull(h).view(shape)
         with capi.gemm_config(static_weights=self._static_weights):
             if micro_batches > 1 and self.world > 1 and h.is_cuda and h.shape[0] >= 2 * 128 * self.world:
                 return self._forward_overlapped(h, micro_batches, sharded).view(shape)
@@ -404,6 +415,17 @@ class DecoderStack:
             sharded = False
         sharded = bool(sharded)
         return self._finish(*self._walk(self._enter(h, sharded), None, sharded), sharded)
+
+    def _walk_pull(self, h: torch.Tensor) -> torch.Tensor:
+        """A few tokens (decode): replicated residual stream, every row-parallel linear ends in the
+        pull all-reduce fused with the next norm + quantize."""
+        be, cfg = self.backend, self.cfg
+        h = h.clone()                                     # updated in place from here on
+        _, xq = be.add_norm_quantize(h, None, self.layers[0].norm1, cfg.eps)
+        for i, layer in enumerate(self.layers):
+            nxt = self.layers[i + 1].norm1 if i + 1 < len(self.layers) else None
+            xq = layer.forward_fused_sharded(h, xq, self._pull, nxt)
+        return xq
 
     def _walk_fused_sharded(self, h: torch.Tensor) -> torch.Tensor:
         comm, be, cfg = self._comm_obj(), self.backend, self.cfg

@@ -331,3 +331,118 @@ class FusedRowParallel:
         check(load().b200q_reduce_add_gather(ctx["ref"], None if b is None else b.data_ptr(), h_shard.data_ptr(), rows, n,
                                              ctx["epoch"], torch.cuda.current_stream().cuda_stream, None), "b200q_reduce_add_gather")
         return ctx["out"][: rows * n * 2].view(torch.bfloat16).view(rows, n)
+
+
+class PullRowParallel:
+    """Row-parallel quantized linear + all-reduce for a handful of tokens (decode steps), with the
+    following residual add, RMSNorm and FP8 quantize fused in: the GEMM writes this rank's partial into
+    its own symmetric buffer, one tiny launch signals the peers, and every rank's reduction kernel
+    pulls all partials over peer memory (include/b200q.h: b200q_pull_signal, b200q_pull_reduce_*).  No
+    collective-library call is involved and the call counter lives on the device, so a whole decode
+    step can be captured in a CUDA graph and replayed.
+
+    Same method names as the token-sharded part of `FusedRowParallel` (`partials_to_owners`,
+    `reduce_norm_quantize`, `reduce_add`), but the residual stream `h` is the full replicated [rows, n]
+    tensor here.  Two partial buffers alternate between consecutive calls; a captured step must hold an
+    even number of all-reduces so that replays start on the same buffer (a decoder layer has two)."""
+
+    def __init__(self, mode: str, max_rows: int, n_out: int, group=None):
+        import ctypes
+        import os
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        if max_rows > 1024:
+            raise ValueError("PullRowParallel serves at most 1024 rows per call")
+        self.mode, self.group = mode, group or dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        if self.world > 8:
+            raise ValueError("PullRowParallel supports at most 8 ranks")
+        self.max_rows, self.n_out = max_rows, n_out
+        dev = torch.device("cuda", torch.cuda.current_device())
+        name = self.group.group_name
+        self._bufs, self._peers, self._refs, self._partial = [], [], [], []
+        flags = symm_mem.empty(4096, dtype=torch.uint8, device=dev)
+        flags.zero_()
+        fh = symm_mem.rendezvous(flags, name)
+        self._bufs.append((flags, fh))
+        for _ in range(2):
+            t = symm_mem.empty(max_rows * n_out, dtype=torch.bfloat16, device=dev)
+            t.zero_()
+            h = symm_mem.rendezvous(t, name)
+            self._bufs.append((t, h))
+            peers = _lib.PullPeers()
+            peers.rank, peers.world = self.rank, self.world
+            for r in range(self.world):
+                peers.partial[r], peers.flags[r] = int(h.buffer_ptrs[r]), int(fh.buffer_ptrs[r])
+            self._peers.append(peers)
+            self._refs.append(ctypes.byref(peers))
+            self._partial.append(t)
+        torch.cuda.current_stream().synchronize()
+        dist.barrier(self.group)
+        self._slot = 0
+        self._pending = None
+        self._bias_seen: set = set()
+
+    _checked_bias = FusedRowParallel._checked_bias
+
+    def usable(self, rows: int) -> bool:
+        return 0 < rows <= self.max_rows
+
+    def partials_to_owners(self, x, qw, amax=None) -> None:
+        """The GEMM of a row-parallel linear into this rank's partial buffer, then the signal."""
+        from . import capi
+        from ._lib import check, load
+
+        rows = x[0].shape[0] if isinstance(x, tuple) else x.shape[0]
+        if not self.usable(rows):
+            raise ValueError(f"{rows} rows: at most {self.max_rows}")
+        slot = self._slot
+        out = self._partial[slot][: rows * self.n_out].view(rows, self.n_out)
+        if self.mode == "fp8":
+            xc, xs = x if isinstance(x, tuple) else capi.fp8_quantize(x, None)
+            capi.fp8_gemm(xc, xs, qw[0], qw[1], None, out=out)
+        else:
+            xc, xs, xg = x if isinstance(x, tuple) else capi.nvfp4_quantize(x, capi.amax(x) if amax is None else amax)
+            capi.nvfp4_gemm(xc, xs, xg, qw[0], qw[1], qw[2], None, out=out)
+        check(load().b200q_pull_signal(self._refs[slot], torch.cuda.current_stream().cuda_stream), "b200q_pull_signal")
+        self._pending = (slot, rows)
+        self._slot = slot ^ 1
+
+    def _take_pending(self, h: torch.Tensor):
+        if self._pending is None:
+            raise RuntimeError("no row-parallel GEMM is pending: call partials_to_owners first")
+        slot, rows = self._pending
+        self._pending = None
+        if tuple(h.shape) != (rows, self.n_out) or not h.is_contiguous() or h.dtype != torch.bfloat16:
+            raise ValueError(f"h must be a contiguous bf16 [{rows}, {self.n_out}] tensor")
+        return slot, rows
+
+    def reduce_norm_quantize(self, h: torch.Tensor, norm_weight: torch.Tensor, eps: float, bias=None):
+        """h (full residual rows, updated in place) += sum of all ranks' partials (+ bias); returns the
+        FP8 codes [rows, n] and per-token scales [rows] of rms_norm(h)."""
+        from ._lib import check, load
+
+        slot, rows = self._take_pending(h)
+        b = self._checked_bias(bias)
+        w = norm_weight.to(torch.bfloat16).contiguous()
+        codes = torch.empty(rows, self.n_out, dtype=torch.uint8, device=h.device)
+        scales = torch.empty(rows, dtype=torch.float32, device=h.device)
+        check(load().b200q_pull_reduce_add_rms_norm_fp8_quantize(
+            self._refs[slot], None if b is None else b.data_ptr(), h.data_ptr(), w.data_ptr(), float(eps), codes.data_ptr(),
+            scales.data_ptr(), rows, self.n_out, torch.cuda.current_stream().cuda_stream, None),
+            "b200q_pull_reduce_add_rms_norm_fp8_quantize")
+        return codes, scales
+
+    def reduce_add(self, h: torch.Tensor, bias=None) -> torch.Tensor:
+        """End of a stack: h += sum of all ranks' partials (+ bias), in place; returns h."""
+        from ._lib import check, load
+
+        slot, rows = self._take_pending(h)
+        b = self._checked_bias(bias)
+        check(load().b200q_pull_reduce_add(self._refs[slot], None if b is None else b.data_ptr(), h.data_ptr(), rows, self.n_out,
+                                           torch.cuda.current_stream().cuda_stream, None), "b200q_pull_reduce_add")
+        return h

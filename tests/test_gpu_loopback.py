@@ -249,6 +249,84 @@ def test_row_parallel_bias_is_added_once(b200):
             assert torch.equal(rk.out[r], bias.expand(M, N))
 
 
+@pytest.mark.parametrize("world,M,N,K", [(2, 64, 8192, 2048), (4, 64, 4096, 4096), (8, 64, 8192, 8192), (8, 1, 1024, 1024), (2, 128, 16384, 512)])
+def test_pull_all_reduce_loopback(b200, world, M, N, K):
+    """Decode-sized all-reduce by pulling: every virtual rank's small-M GEMM writes its partial into its
+    own buffer and signals; every rank's reduction then reads all partials, adds bias and residual,
+    applies RMSNorm and quantizes.  Launch order on the one stream: all GEMMs and signals first, then
+    the reductions, so no kernel waits for one that has not run.  Three all-reduces in a row alternate
+    between the two partial buffers and advance the on-device call counter; the third ends the stack
+    (no norm).  All ranks must produce the same bits; h is exact against the oracle's order of sums."""
+    from tensorrt_b200 import _lib
+
+    capi, lib = b200.capi, _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    partial = [[torch.zeros(M, N, dtype=torch.bfloat16, device="cuda") for _ in range(2)] for _ in range(world)]
+    flags = [torch.zeros(world + 1, dtype=torch.int32, device="cuda") for _ in range(world)]
+    peers = []
+    for slot in range(2):
+        per_rank = []
+        for r in range(world):
+            p = _lib.PullPeers()
+            p.rank, p.world = r, world
+            for s in range(world):
+                p.partial[s], p.flags[s] = partial[s][slot].data_ptr(), flags[s].data_ptr()
+            per_rank.append(p)
+        peers.append(per_rank)
+    g = torch.Generator().manual_seed(world * 1000 + N)
+    h0 = torch.randn(M, N, generator=g).bfloat16()
+    nw = (1 + 0.1 * torch.randn(N, generator=g)).bfloat16()
+    bias = (torch.randn(N, generator=g) * 0.05).bfloat16()
+    h_dev = [h0.clone().cuda() for _ in range(world)]
+    h_ref = h0.clone()
+    nw_d, bias_d = nw.cuda(), bias.cuda()
+    for call in range(3):
+        slot, last = call & 1, call == 2
+        xs, ws, parts = _problem(world, M, N, K, seed=call + world + N)
+        keep = []
+        for r in range(world):
+            xc, xsc = capi.fp8_quantize(xs[r].cuda(), None)
+            wc, wsc = capi.fp8_quantize(ws[r].cuda(), capi.row_amax(ws[r].cuda()))
+            capi.fp8_gemm(xc, xsc, wc, wsc, None, out=partial[r][slot])
+            _check(lib.b200q_pull_signal(ctypes.byref(peers[slot][r]), stream), "b200q_pull_signal")
+            keep += [xc, xsc, wc, wsc]
+        outs = []
+        for r in range(world):
+            if last:
+                _check(lib.b200q_pull_reduce_add(ctypes.byref(peers[slot][r]), bias_d.data_ptr(), h_dev[r].data_ptr(), M, N, stream, None),
+                       "b200q_pull_reduce_add")
+            else:
+                codes = torch.empty(M, N, dtype=torch.uint8, device="cuda")
+                scales = torch.empty(M, dtype=torch.float32, device="cuda")
+                _check(lib.b200q_pull_reduce_add_rms_norm_fp8_quantize(
+                    ctypes.byref(peers[slot][r]), bias_d.data_ptr(), h_dev[r].data_ptr(), nw_d.data_ptr(), 1e-5, codes.data_ptr(),
+                    scales.data_ptr(), M, N, stream, None), "b200q_pull_reduce_add_rms_norm_fp8_quantize")
+                outs.append((codes, scales))
+        torch.cuda.synchronize()
+        del keep
+        assert capi.device_status() == 0
+        # the device's own partials, summed in rank order as the kernel does
+        acc = torch.zeros(M, N, device="cuda")
+        for s in range(world):
+            acc += partial[s][slot].float()
+            assert o.rel_l2(partial[s][slot].float().cpu(), parts[s].float()) <= 1e-2
+        delta = (acc + bias_d.float()).bfloat16()
+        h_ref = (h_ref.float() + delta.float().cpu()).bfloat16()
+        for r in range(world):
+            assert torch.equal(h_dev[r].cpu(), h_ref), (call, r)
+        for words in (f.cpu().tolist() for f in flags):
+            assert words == [call + 1] * (world + 1)                  # every peer's signal and the own call counter
+        if not last:
+            for r in range(1, world):
+                assert torch.equal(outs[r][0], outs[0][0]) and torch.equal(outs[r][1], outs[0][1])
+            x_ref = o.rms_norm_ref(h_ref, nw)
+            c_ref, s_ref = o.fp8_quantize(x_ref, o.row_amax(x_ref))
+            assert torch.allclose(outs[0][1].cpu(), s_ref.reshape(-1), rtol=2e-2)
+            assert o.rel_l2(o.fp8_dequantize(outs[0][0].cpu(), outs[0][1].cpu().view(-1, 1)), x_ref.float()) <= 4e-2
+            _, c2, s2 = capi.add_rms_norm_fp8_quantize(h_ref.cuda(), None, nw_d, 1e-5)     # the unfused kernel on the same h
+            assert torch.allclose(outs[0][1], s2, rtol=1e-2) and (outs[0][0] != c2).float().mean().item() < 2e-2
+
+
 def test_a_wait_for_a_peer_that_never_arrives_runs_out(b200):
     """Rank 0 of a 2-rank group calls the reduction, rank 1 never does and nothing sets its flag.
     With a 50 ms limit (b200q_cfg::peer_wait_ms) the wait gives up by itself: the kernels return, the

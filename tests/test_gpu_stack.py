@@ -141,7 +141,8 @@ def _tp_worker(rank, world, store_path, out_path, slabs, fused, micro, sharded):
 
     r = torch.ops.tensorrt.fused_nccl_all_reduce(t, "sum", group_name_of())
     assert torch.allclose(r.cpu(), torch.full((1, 4), world * (world + 1) / 2), atol=1e-3, rtol=1e-3)
-    stack = DecoderStack(cfg, _to(ws, "cuda"), rank=rank, world=world, slabs=slabs, fused_rows=512 if fused else 0)
+    stack = DecoderStack(cfg, _to(ws, "cuda"), rank=rank, world=world, slabs=slabs, fused_rows=512 if fused else 0,
+                         pull_rows=64 if fused else 0)
     if sharded and not fused:
         sharded = "collectives"                  # the process group's reduce-scatter / all-gather
     y = stack.forward(h.cuda(), micro, sharded)
@@ -153,6 +154,29 @@ def _tp_worker(rank, world, store_path, out_path, slabs, fused, micro, sharded):
         y_ar = stack.forward(h.cuda(), micro, False)
         err = (y.float() - y_ar.float()).norm() / y_ar.float().norm()
         assert err < 2e-3, float(err)
+    if fused:
+        # a decode-sized forward takes the pull all-reduce; eagerly and as a replayed CUDA graph (no
+        # collective-library call inside the step), against the all-reduce form of the same stack
+        hd = h.cuda()[0, :48].contiguous()
+        yd = stack.forward(hd)
+        stack._pull, keep = None, stack._pull
+        yd_ref = stack.forward(hd)
+        stack._pull = keep
+        err = (yd.float() - yd_ref.float()).norm() / yd_ref.float().norm()
+        assert err < 2e-3, float(err)
+        torch.cuda.synchronize()
+        dist.barrier()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                yg = stack.forward(hd)
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(yg, yd)
     torch.cuda.synchronize()
     assert tensorrt_b200.capi.device_status() == 0
     if rank == 0:
