@@ -294,6 +294,29 @@ int b200q_pull_reduce_add_rms_norm_fp8_quantize(const b200q_pull_peers* peers, c
 int b200q_pull_reduce_add(const b200q_pull_peers* peers, const void* bias, void* h, int64_t M, int64_t N,
                           b200q_stream_t stream, const b200q_cfg* cfg);
 
+/* ------------------------------------------------------------------ FP8 attention
+ * Replaces the TensorRT attention layer the reference builds for an SDPA whose Q, K and V all come from
+ * `quantize_op(.., 8, 4, ..)` (py/torch_tensorrt/dynamo/lowering/passes/annotate_fp8_sdpa.py:34-76 marks it,
+ * py/torch_tensorrt/dynamo/conversion/impl/attention.py:272-337 builds it): softmax output quantized to FP8
+ * with the fixed scale 1/448, static `softmax_scale` (1/sqrt(D)) on the query.
+ *   S = (Q_hat K_hat^T) * softmax_scale;  P = softmax(S) over the keys (causal = lower-right aligned mask);
+ *   P_hat = e4m3(P * 448) / 448;  out = P_hat V_hat   in `out_dtype` (B200Q_BF16 / F16 / F32)
+ * q_codes [B, Hq, Sq, D], k_codes [B, Hkv, Sk, D]: E4M3 codes (b200q_fp8_quantize with a per-tensor amax);
+ * vt_codes [B, Hkv, D, vt_stride]: the codes of V TRANSPOSED per head, keys contiguous, zero beyond Sk
+ * (b200q_fp8_quantize_transpose; vt_stride >= Sk, a multiple of 16).  q/k/v_scale: one fp32 each on the
+ * device (the scales those quantize calls return).  Hq % Hkv == 0 (grouped-query attention: query head h
+ * reads kv head h / (Hq / Hkv)); D % 16 == 0, D <= 128; B * Hq <= 65535.  Rows whose keys are all masked
+ * get zeros.
+ *
+ * b200q_fp8_quantize_transpose: x [heads, S, D] (dtype) with a per-tensor amax -> codes [heads, D, s_stride],
+ * scale_out (may be NULL) receives amax / 448 (zero -> 1). */
+int b200q_fp8_quantize_transpose(const void* x, int dtype, int64_t heads, int64_t S, int64_t D, const float* amax,
+                                 uint8_t* out_t, int64_t s_stride, float* scale_out, b200q_stream_t stream);
+int b200q_fp8_sdpa(const uint8_t* q_codes, const uint8_t* k_codes, const uint8_t* vt_codes, const float* q_scale,
+                   const float* k_scale, const float* v_scale, void* out, int out_dtype, int64_t B, int64_t Hq,
+                   int64_t Hkv, int64_t Sq, int64_t Sk, int64_t vt_stride, int64_t D, float softmax_scale, int causal,
+                   b200q_stream_t stream);
+
 /* ------------------------------------------------------------------ glue of the decoder linear stack
  * The benchmark workloads wrap the quantized linears in a Llama-shaped decoder layer
  * (RMSNorm -> QKV -> attention replaced by identity on V -> O -> residual -> RMSNorm ->

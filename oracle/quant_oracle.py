@@ -56,7 +56,7 @@ __all__ = [
     "pack_e2m1", "unpack_e2m1", "swizzle_scales", "unswizzle_scales", "swizzled_scale_bytes",
     "quantize_op", "dynamic_block_quantize_op",
     "linear_ref", "fp8_linear_ref", "nvfp4_linear_ref", "rel_l2",
-    "all_reduce_ref", "rms_norm_ref", "decoder_layer_ref", "shard_decoder_layer",
+    "all_reduce_ref", "rms_norm_ref", "decoder_layer_ref", "shard_decoder_layer", "fp8_sdpa_ref",
 ]
 
 E4M3_MAX = 448.0
@@ -380,3 +380,31 @@ def decoder_layer_ref(h, layer: dict, n_q: int, n_kv: int, head_dim: int, mode: 
         act = (torch.nn.functional.silu(gu[..., :f].float()) * gu[..., f:].float()).to(dt)
         parts.append(_qlinear(act, sh["wdown"], mode).to(dt))
     return h + all_reduce_ref(parts, dt)
+
+
+# --------------------------------------------------------------------------- FP8 attention
+def fp8_sdpa_ref(q, k, v, amax_q, amax_k, amax_v, is_causal: bool = False, scale=None) -> torch.Tensor:
+    """SDPA whose Q, K, V come from `quantize_op(.., 8, 4, ..)` with per-tensor amax, as the reference
+    marks and builds it (py/torch_tensorrt/dynamo/lowering/passes/annotate_fp8_sdpa.py:34-76: softmax
+    output quantized to FP8 with the fixed scale 1/448; conversion/impl/attention.py:272-337: static
+    1/sqrt(D) factor, softmax normalization, lower-right causal mask):
+        S = Q_hat K_hat^T * scale;  P = softmax(S);  P_hat = e4m3(P * 448) / 448;  O = P_hat V_hat
+    q [B, Hq, Sq, D], k / v [B, Hkv, Sk, D]; query head h reads kv head h // (Hq // Hkv).  fp32 arithmetic
+    on the exactly dequantized operands (code x scale in fp32, as a kernel that consumes the FP8 codes
+    sees them; the unfused eager graph would round the fake-quantized tensors to the input dtype first,
+    which the reference leaves open), result in q's dtype.  Rows with every key masked give zeros."""
+    B, Hq, Sq, D = q.shape
+    Hkv, Sk = k.shape[1], k.shape[2]
+    qh, kh, vh = (fp8_dequantize(*fp8_quantize(t, a)) for t, a in ((q, amax_q), (k, amax_k), (v, amax_v)))
+    rep = Hq // Hkv
+    kh, vh = kh.repeat_interleave(rep, dim=1), vh.repeat_interleave(rep, dim=1)
+    scale = (1.0 / D ** 0.5) if scale is None else scale
+    s = (qh @ kh.transpose(-1, -2)) * scale
+    if is_causal:
+        i = torch.arange(Sq).view(-1, 1)
+        j = torch.arange(Sk).view(1, -1)
+        s = s.masked_fill(j > i + (Sk - Sq), float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    p = torch.where(torch.isnan(p), torch.zeros_like(p), p)             # fully masked rows
+    p_hat = e4m3_decode(e4m3_encode(p * E4M3_MAX)) / E4M3_MAX
+    return (p_hat @ vh).to(q.dtype)

@@ -42,6 +42,8 @@ SIGNATURES = {
     "b200q_pull_signal": (_c.c_int, [_p, _p]),
     "b200q_pull_reduce_add_rms_norm_fp8_quantize": (_c.c_int, [_p, _p, _p, _p, _c.c_float, _p, _p, _i64, _i64, _p, _p]),
     "b200q_pull_reduce_add": (_c.c_int, [_p, _p, _p, _i64, _i64, _p, _p]),
+    "b200q_fp8_quantize_transpose": (_c.c_int, [_p, _c.c_int, _i64, _i64, _i64, _p, _p, _i64, _p, _p]),
+    "b200q_fp8_sdpa": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _c.c_int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _c.c_float, _c.c_int, _p]),
     "b200q_rms_norm": (_c.c_int, [_p, _p, _p, _i64, _i64, _c.c_float, _p]),
     "b200q_add_rms_norm_fp8_quantize": (_c.c_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _c.c_float, _p]),
     "b200q_silu_mul": (_c.c_int, [_p, _p, _i64, _i64, _p]),

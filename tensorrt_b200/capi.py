@@ -234,6 +234,41 @@ def nvfp4_gemm(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias=No
     return out
 
 
+def fp8_sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, amax_q, amax_k, amax_v, is_causal: bool = False,
+             scale: float | None = None) -> torch.Tensor:
+    """FP8 attention on q [B, Hq, Sq, D], k / v [B, Hkv, Sk, D] (bf16 / fp16 / fp32) with per-tensor amax
+    each: Q, K, V are quantized to E4M3 (V transposed per head on the way), the softmax output is quantized
+    with the fixed scale 1/448, both contractions run on FP8 tensor cores; result in q's dtype."""
+    import math
+
+    _need_cuda(q, k, v)
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4 or k.shape != v.shape or q.shape[0] != k.shape[0] or q.shape[3] != k.shape[3]:
+        raise ValueError(f"expected q [B, Hq, Sq, D] and k, v [B, Hkv, Sk, D], got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    B, Hq, Sq, D = q.shape
+    _, Hkv, Sk, _ = k.shape
+    if Hq % Hkv or D % 16 or D > 128:
+        raise ValueError(f"need Hq % Hkv == 0 and a head dimension that is a multiple of 16 up to 128, got Hq={Hq}, Hkv={Hkv}, D={D}")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    dev = q.device
+    amaxes = [a.to(device=dev, dtype=torch.float32).reshape(1) for a in (amax_q, amax_k, amax_v)]
+    qc, qs = fp8_quantize(q, amaxes[0])
+    kc, ks = fp8_quantize(k, amaxes[1])
+    stride = (Sk + 15) // 16 * 16
+    vt = torch.empty(B, Hkv, D, max(stride, 16), dtype=torch.uint8, device=dev)
+    vs = torch.empty(1, dtype=torch.float32, device=dev)
+    out = torch.empty_like(q)
+    lib = load()
+    with torch.cuda.device(dev):
+        check(lib.b200q_fp8_quantize_transpose(v.data_ptr(), _dt(v), B * Hkv, Sk, D, amaxes[2].data_ptr(), vt.data_ptr(), max(stride, 16),
+                                               vs.data_ptr(), _stream(q)), "b200q_fp8_quantize_transpose")
+        if Sk == 0:
+            vs.fill_(1.0)
+        check(lib.b200q_fp8_sdpa(qc.data_ptr(), kc.data_ptr(), vt.data_ptr(), qs.data_ptr(), ks.data_ptr(), vs.data_ptr(), out.data_ptr(),
+                                 _dt(q), B, Hq, Hkv, Sq, Sk, max(stride, 16), D, float(scale if scale is not None else 1.0 / math.sqrt(D)),
+                                 1 if is_causal else 0, _stream(q)), "b200q_fp8_sdpa")
+    return out
+
+
 def _bf16(*ts):
     for t in ts:
         if t.dtype != torch.bfloat16:

@@ -17,6 +17,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include <cmath>
 #include <optional>
 #include <tuple>
 
@@ -351,6 +352,46 @@ Tensor nvfp4_linear_bias_meta(const Tensor& x, const Tensor&, const Tensor& w_co
   return linear_meta_like(x, w_codes);
 }
 
+// ------------------------------------------------------------------ FP8 attention (Q, K, V from quantize_op)
+Tensor fp8_sdpa_cuda(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in, const Tensor& amax_q, const Tensor& amax_k,
+                     const Tensor& amax_v, bool is_causal, double scale) {
+  const int dt = dtype_code(q_in, "b200_fp8_sdpa");
+  TORCH_CHECK(q_in.dim() == 4 && k_in.dim() == 4 && v_in.dim() == 4 && k_in.sizes() == v_in.sizes() && q_in.size(0) == k_in.size(0) &&
+                  q_in.size(3) == k_in.size(3),
+              "b200_fp8_sdpa: expected q [B, Hq, Sq, D] and k, v [B, Hkv, Sk, D], got ", q_in.sizes(), ", ", k_in.sizes(), ", ", v_in.sizes());
+  TORCH_CHECK(k_in.scalar_type() == q_in.scalar_type() && v_in.scalar_type() == q_in.scalar_type(), "b200_fp8_sdpa: q, k, v must share a dtype");
+  TORCH_CHECK(amax_q.numel() == 1 && amax_k.numel() == 1 && amax_v.numel() == 1, "b200_fp8_sdpa: amax must be per-tensor (one value each)");
+  const int64_t B = q_in.size(0), Hq = q_in.size(1), Sq = q_in.size(2), D = q_in.size(3), Hkv = k_in.size(1), Sk = k_in.size(2);
+  TORCH_CHECK_VALUE(Hq % Hkv == 0 && D % 16 == 0 && D <= 128, "b200_fp8_sdpa: need Hq % Hkv == 0 and a head dimension that is a multiple of 16 up to 128");
+  c10::cuda::CUDAGuard guard(q_in.device());
+  Tensor q = q_in.contiguous(), k = k_in.contiguous(), v = v_in.contiguous();
+  Tensor out = at::empty_like(q);
+  if (out.numel() == 0) return out;
+  auto bytes = q.options().dtype(at::kByte);
+  auto f32 = q.options().dtype(at::kFloat);
+  Tensor aq = as_f32_cuda(amax_q, q).reshape({1}), ak = as_f32_cuda(amax_k, q).reshape({1}), av = as_f32_cuda(amax_v, q).reshape({1});
+  Tensor qc = at::empty(q.sizes(), bytes), kc = at::empty(k.sizes(), bytes);
+  Tensor sq = at::empty({1}, f32), sk = at::ones({1}, f32), sv = at::ones({1}, f32);
+  const int64_t stride = std::max<int64_t>((Sk + 15) / 16 * 16, 16);
+  Tensor vt = at::empty({B, Hkv, D, stride}, bytes);
+  check_status(b200q_fp8_quantize(q.data_ptr(), dt, B * Hq * Sq, D, aq.data_ptr<float>(), 1, qc.data_ptr<uint8_t>(), sq.data_ptr<float>(),
+                                  current_stream()), "b200q_fp8_quantize");
+  if (Sk > 0) {
+    check_status(b200q_fp8_quantize(k.data_ptr(), dt, B * Hkv * Sk, D, ak.data_ptr<float>(), 1, kc.data_ptr<uint8_t>(), sk.data_ptr<float>(),
+                                    current_stream()), "b200q_fp8_quantize");
+    check_status(b200q_fp8_quantize_transpose(v.data_ptr(), dt, B * Hkv, Sk, D, av.data_ptr<float>(), vt.data_ptr<uint8_t>(), stride,
+                                              sv.data_ptr<float>(), current_stream()), "b200q_fp8_quantize_transpose");
+  }
+  const float sm = scale > 0.0 ? static_cast<float>(scale) : 1.0f / std::sqrt(static_cast<float>(D));
+  check_status(b200q_fp8_sdpa(qc.data_ptr<uint8_t>(), kc.data_ptr<uint8_t>(), vt.data_ptr<uint8_t>(), sq.data_ptr<float>(), sk.data_ptr<float>(),
+                              sv.data_ptr<float>(), out.data_ptr(), dt, B, Hq, Hkv, Sq, Sk, stride, D, sm, is_causal ? 1 : 0, current_stream()),
+               "b200q_fp8_sdpa");
+  return out;
+}
+Tensor fp8_sdpa_meta(const Tensor& q, const Tensor&, const Tensor&, const Tensor&, const Tensor&, const Tensor&, bool, double) {
+  return at::empty_like(q);
+}
+
 bool schema_exists(const char* name) {
   return c10::Dispatcher::singleton().findSchema({name, ""}).has_value();
 }
@@ -408,6 +449,11 @@ TORCH_LIBRARY_FRAGMENT(tensorrt, m) {
       "Tensor bias) -> Tensor");
   m.impl("b200_nvfp4_gemm_bias", c10::DispatchKey::CUDA, TORCH_FN(nvfp4_gemm_bias_cuda));
   m.impl("b200_nvfp4_gemm_bias", c10::DispatchKey::Meta, TORCH_FN(nvfp4_gemm_bias_meta));
+
+  // SDPA whose Q, K, V are FP8 fake-quantized with per-tensor amax; scale <= 0 = 1 / sqrt(head_dim)
+  m.def("b200_fp8_sdpa(Tensor q, Tensor k, Tensor v, Tensor amax_q, Tensor amax_k, Tensor amax_v, bool is_causal, float scale) -> Tensor");
+  m.impl("b200_fp8_sdpa", c10::DispatchKey::CUDA, TORCH_FN(fp8_sdpa_cuda));
+  m.impl("b200_fp8_sdpa", c10::DispatchKey::Meta, TORCH_FN(fp8_sdpa_meta));
 
   // One-node quantized linears (activation first, result in the activation's dtype): the ops handed
   // to torch_tensorrt.dynamo.conversion.plugins.custom_op.

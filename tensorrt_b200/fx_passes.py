@@ -271,6 +271,58 @@ def _node_index(graph: fx.Graph, node: fx.Node) -> int:
     return -1
 
 
+def fuse_fp8_sdpa(gm: fx.GraphModule) -> int:
+    """`scaled_dot_product_attention(quantize_op(q), quantize_op(k), quantize_op(v), ..)` with all three
+    quantizers FP8 E4M3 becomes one `tensorrt::b200_fp8_sdpa` node: the pattern the reference detects in
+    py/torch_tensorrt/dynamo/lowering/passes/annotate_fp8_sdpa.py:34-76 (it marks the node with the softmax
+    quantization scale 1/448 and lets TensorRT fuse an FP8 attention kernel; here the kernel is the node).
+    Left alone: an explicit attn_mask, dropout, quantizers with a per-row amax the graph can prove
+    (constant amax with more than one element).  Returns the number of nodes rewritten."""
+    from . import ops
+
+    ops.load_ops()
+    a = torch.ops.aten
+    targets = (torch.nn.functional.scaled_dot_product_attention, a.scaled_dot_product_attention,
+               a.scaled_dot_product_attention.default)
+    names = ("query", "key", "value", "attn_mask", "dropout_p", "is_causal", "scale", "enable_gqa")
+    graph, count = gm.graph, 0
+    for node in list(graph.nodes):
+        if node.op != "call_function" or node.target not in targets or len(node.args) < 3:
+            continue
+        bound = dict(zip(names, node.args))
+        bound.update(node.kwargs)
+        if bound.get("attn_mask") is not None or bound.get("dropout_p", 0.0) not in (0, 0.0):
+            continue
+        qkv = [bound["query"], bound["key"], bound["value"]]
+        if not all(isinstance(n, fx.Node) for n in qkv):
+            continue
+        matches = [_match_fp8(n) for n in qkv]
+        if any(m is None for m in matches):
+            continue
+        amaxes = [_const_tensor(gm, m[1]) for m in matches]
+        if any(t is not None and t.numel() != 1 for t in amaxes):
+            continue
+        scale = bound.get("scale")
+        if scale is not None and not isinstance(scale, (int, float)):
+            continue
+        with graph.inserting_before(node):
+            out = graph.call_function(torch.ops.tensorrt.b200_fp8_sdpa.default,
+                                      (matches[0][0], matches[1][0], matches[2][0], matches[0][1], matches[1][1], matches[2][1],
+                                       bool(bound.get("is_causal", False)), float(scale) if scale is not None else -1.0))
+        out.meta.update({k: v for k, v in node.meta.items() if k in ("val", "tensor_meta")})
+        node.replace_all_uses_with(out)
+        graph.erase_node(node)
+        for qn in qkv:
+            if not qn.users:
+                graph.erase_node(qn)
+        count += 1
+    if count:
+        graph.eliminate_dead_code()
+        graph.lint()
+        gm.recompile()
+    return count
+
+
 def fuse_all_reduce_wait(gm: fx.GraphModule) -> int:
     """`_c10d_functional.all_reduce(x, op, group)` whose only user is `wait_tensor` becomes one
     `tensorrt::fused_nccl_all_reduce(x, op, group)` node, the form the reference's converters (and
