@@ -232,6 +232,34 @@ def library_comparators(peaks, min_ms=300.0):
     return out
 
 
+def attention_case(capi, peaks, min_ms=300.0):
+    """FP8 attention of the 70B-shaped stack's prefill (32 sequences of 1024 tokens, 64 q / 8 kv heads of
+    128, causal), operands already quantized: device time of b200q_fp8_sdpa alone.  Flops counted as the
+    algorithmic 4 B H S^2 D / 2 of a causal attention (the kernel computes Q K^T twice: see its header)."""
+    import tensorrt_b200
+
+    lib = tensorrt_b200.load_library()
+    B, Hq, Hkv, S, D = 32, 64, 8, 1024, 128
+    qc = torch.randint(0, 120, (B, Hq, S, D), dtype=torch.uint8, device="cuda")
+    kc = torch.randint(0, 120, (B, Hkv, S, D), dtype=torch.uint8, device="cuda")
+    vt = torch.randint(0, 120, (B, Hkv, D, S), dtype=torch.uint8, device="cuda")
+    sc = torch.full((1,), 0.01, device="cuda")
+    out = torch.empty(B, Hq, S, D, dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def fn():
+        rc = lib.b200q_fp8_sdpa(qc.data_ptr(), kc.data_ptr(), vt.data_ptr(), sc.data_ptr(), sc.data_ptr(), sc.data_ptr(), out.data_ptr(), 2,
+                                B, Hq, Hkv, S, S, S, D, 1.0 / D ** 0.5, 1, stream)
+        if rc != 0:
+            raise RuntimeError(f"b200q_fp8_sdpa returned {rc}")
+
+    ms, n = time_device(fn, min_ms, min_iters=10)
+    flops = 4.0 * B * Hq * S * S * D / 2
+    tf = flops / ms / 1e9
+    return {"ms": ms, "launches": n, "tflops": tf, "shape": f"B{B} Hq{Hq} Hkv{Hkv} S{S} D{D} causal",
+            "roofline": tensor_roofline(tf, peaks, "fp8", "fp8_sdpa_kernel", flops)}
+
+
 def full_sweep_shapes():
     return [(m, n, k) for (n, k) in SWEEP_NK for m in SWEEP_M]
 
@@ -244,6 +272,10 @@ def extras(capi, peaks, min_ms=500.0):
         out = {"quantize": quantize_suite(capi, peaks, min_ms)}
         for kind in ("fp8", "nvfp4"):
             out[kind + "_gemm"] = gemm_sweep(capi, peaks, kind, full_sweep_shapes(), min_ms)
+        try:
+            out["fp8_attention"] = attention_case(capi, peaks)
+        except Exception as exc:
+            out["fp8_attention"] = {"error": str(exc)[:200]}
         out["library"] = library_comparators(peaks)
     out["clocks"] = clocks.summary()
     return out

@@ -232,6 +232,23 @@ int b200q_nvfp4_gemm_reduce_scatter(const uint8_t* a_codes, const uint8_t* a_sca
 int b200q_reduce_gather(const b200q_peers* peers, const void* bias, int64_t M, int64_t N, uint32_t epoch,
                         b200q_stream_t stream, const b200q_cfg* cfg);
 
+/* Native communication context: where the peer pointers of b200q_peers / b200q_gather_peers /
+ * b200q_pull_peers come from when the host is C or C++ (one process per GPU on one node).  Takes the place
+ * of TRTEngine::bind_nccl_comm (core/runtime/TRTEngine.cpp:821-928), which hands the process group's
+ * communicator to the engine: these kernels need no communicator, only a pointer valid in this process for
+ * every rank's copy of a buffer.  b200q_comm_alloc allocates `bytes` (zeroed) on the current device on
+ * every rank, exchanges CUDA IPC handles through the host's own all-gather and opens the peers' handles:
+ * ptrs[r] is rank r's buffer (ptrs[rank] the local one).  Collective: every rank calls it in the same
+ * order with the same size.  This is set-up code: it allocates and synchronises; the compute entry points
+ * never do.  b200q_comm_destroy (collective) unmaps and frees everything the context allocated.
+ * `allgather(user, send, recv, bytes)`: every rank contributes `bytes` bytes, recv receives world * bytes
+ * in rank order; returns 0 on success.  May be NULL when world == 1. */
+typedef int (*b200q_allgather_fn)(void* user, const void* send, void* recv, size_t bytes);
+typedef struct b200q_comm b200q_comm;
+int b200q_comm_create(int rank, int world, b200q_allgather_fn allgather, void* user, b200q_comm** out);
+int b200q_comm_alloc(b200q_comm* comm, size_t bytes, void* ptrs[8]);
+int b200q_comm_destroy(b200q_comm* comm);
+
 /* Token-sharded residual stream (sequence-parallel form of the same TP plan,
  * tools/llm/tensor_parallel_llama_llm.py:134-157): every rank keeps the residual rows it owns
  * ([M/world, N] bf16) and the reduction of a row-parallel linear is fused with what follows it.

@@ -22,7 +22,7 @@ LIB = PKG / "libb200q.so"
 TORCH_LIB = PKG / "libb200q_torch.so"
 
 CUDA_SOURCES = ["runtime.cu", "quantize_fp8.cu", "quantize_nvfp4.cu", "gemm_fp8.cu", "gemm_nvfp4.cu",
-                "fused_ops.cu", "p2p_allreduce.cu", "attention_fp8.cu"]
+                "fused_ops.cu", "p2p_allreduce.cu", "attention_fp8.cu", "comm_context.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 

@@ -36,6 +36,9 @@ SIGNATURES = {
     "b200q_nvfp4_gemm": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _p]),
     "b200q_fp8_gemm_reduce_scatter": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _p, _p]),
     "b200q_nvfp4_gemm_reduce_scatter": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _p]),
+    "b200q_comm_create": (_c.c_int, [_c.c_int, _c.c_int, _p, _p, _p]),
+    "b200q_comm_alloc": (_c.c_int, [_p, _c.c_size_t, _p]),
+    "b200q_comm_destroy": (_c.c_int, [_p]),
     "b200q_reduce_gather": (_c.c_int, [_p, _p, _i64, _i64, _c.c_uint32, _p, _p]),
     "b200q_reduce_add_gather": (_c.c_int, [_p, _p, _p, _i64, _i64, _c.c_uint32, _p, _p]),
     "b200q_reduce_add_rms_norm_fp8_quantize_gather": (_c.c_int, [_p, _p, _p, _p, _c.c_float, _i64, _i64, _c.c_uint32, _p, _p]),
@@ -76,6 +79,9 @@ class GatherPeers(ctypes.Structure):
     """struct b200q_gather_peers of include/b200q.h."""
     _fields_ = [("rank", _c.c_int32), ("world", _c.c_int32), ("recv", _p * 8), ("codes", _p * 8), ("scales", _p * 8),
                 ("flags", _p * 8)]
+
+
+ALLGATHER_FN = ctypes.CFUNCTYPE(_c.c_int, _p, _p, _p, _c.c_size_t)   # b200q_allgather_fn
 
 
 class PullPeers(ctypes.Structure):

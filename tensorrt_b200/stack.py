@@ -332,8 +332,9 @@ class DecoderStack:
     of full (unsharded) bf16 weights; each is sharded, quantized and dropped."""
 
     def __init__(self, cfg: StackConfig, weights, backend=None, rank: int = 0, world: int = 1, group=None, slabs: int = 1,
-                 fused_rows: int = 0, pull_rows: int = 0):
-        """`fused_rows` > 0: row-parallel linears use the fused GEMM + peer-memory all-reduce
+                 fused_rows: int = 0, pull_rows: int = 0, comm=None):
+        """`comm`: a tp.CommContext whose CUDA-IPC buffers the fused paths use for their peer memory
+        (default: torch's symmetric-memory allocator).  `fused_rows` > 0: row-parallel linears use the fused GEMM + peer-memory all-reduce
         (tp.FusedRowParallel) for up to that many rows; other row counts use NCCL.
         `pull_rows` > 0 (FP8 stacks): forwards of at most that many tokens (decode steps) use the pull
         all-reduce fused with residual add, RMSNorm and quantize (tp.PullRowParallel)."""
@@ -352,7 +353,7 @@ class DecoderStack:
             be = self.backend
             row_parallel = FusedRowParallel(cfg.mode, fused_rows, cfg.hidden, group,
                                             fallback=lambda x, qw, amax=None: reduce(be.linear(x, qw, amax)),
-                                            sharded=cfg.mode == "fp8")
+                                            sharded=cfg.mode == "fp8", comm=comm)
             self._fused = row_parallel
         elif world > 1:
             if slabs > 1:
@@ -363,7 +364,7 @@ class DecoderStack:
         if world > 1 and pull_rows > 0 and cfg.mode == "fp8":
             from .tp import PullRowParallel
 
-            self._pull = PullRowParallel(cfg.mode, pull_rows, cfg.hidden, group)
+            self._pull = PullRowParallel(cfg.mode, pull_rows, cfg.hidden, group, comm=comm)
         self.layers = [DecoderLayer(cfg, shard_layer_weights(w, cfg, rank, world) if world > 1 else w, self.backend, world,
                                     row_parallel) for w in weights]
         # every weight is quantized and resident from here on: forward() may promise its own GEMM

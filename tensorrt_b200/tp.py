@@ -143,6 +143,84 @@ def replicate_row_parallel_bias(bias, group=None, device=None):
     return bias
 
 
+class CommContext:
+    """The library's own communication context (include/b200q.h: b200q_comm_*): symmetric device buffers
+    whose peer mappings come from CUDA IPC, exchanged through an all-gather the host supplies.  This
+    wrapper supplies `torch.distributed.all_gather_object` on `group` (any backend; gloo works) as that
+    all-gather; a C or C++ host passes its own.  `alloc(nbytes)` is collective and returns the list of
+    `world` device pointers valid in this process plus a uint8 tensor view of the local buffer."""
+
+    def __init__(self, group=None):
+        import ctypes
+
+        from . import _lib
+
+        self.group = group or dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        lib = _lib.load()
+
+        def allgather(user, send, recv, nbytes):
+            try:
+                mine = ctypes.string_at(send, nbytes)
+                parts = [None] * self.world
+                dist.all_gather_object(parts, mine, group=self.group)
+                ctypes.memmove(recv, b"".join(parts), nbytes * self.world)
+                return 0
+            except Exception:  # reported as a status code: nothing may propagate through the C caller
+                return 1
+
+        self._cb = _lib.ALLGATHER_FN(allgather)          # kept alive as long as the context
+        handle = ctypes.c_void_p()
+        _lib.check(lib.b200q_comm_create(self.rank, self.world, self._cb, None, ctypes.byref(handle)), "b200q_comm_create")
+        self._handle, self._lib = handle, lib
+
+    def alloc(self, nbytes: int):
+        import ctypes
+
+        from . import _lib
+
+        ptrs = (ctypes.c_void_p * 8)()
+        _lib.check(self._lib.b200q_comm_alloc(self._handle, nbytes, ptrs), "b200q_comm_alloc")
+        addrs = [int(ptrs[r]) for r in range(self.world)]
+        return addrs, _device_view(addrs[self.rank], nbytes)
+
+    def close(self) -> None:
+        if self._handle is not None:
+            from . import _lib
+
+            _lib.check(self._lib.b200q_comm_destroy(self._handle), "b200q_comm_destroy")
+            self._handle = None
+
+
+def _device_view(ptr: int, nbytes: int) -> torch.Tensor:
+    """uint8 tensor over `nbytes` of device memory at `ptr` (memory owned by someone else)."""
+    class _Raw:
+        __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+    return torch.as_tensor(_Raw(), device=torch.device("cuda", torch.cuda.current_device()))
+
+
+def _symmetric_buffers(sizes, group, comm: "CommContext | None"):
+    """For every size a zeroed uint8 buffer on each rank plus its `world` peer pointers: through the
+    library's own context when one is given, else through torch's symmetric-memory allocator."""
+    if comm is not None:
+        out = []
+        for size in sizes:
+            addrs, local = comm.alloc(size)
+            out.append((local, addrs))
+        return out
+    import torch.distributed._symmetric_memory as symm_mem
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = []
+    for size in sizes:
+        t = symm_mem.empty(size, dtype=torch.uint8, device=dev)
+        t.zero_()
+        h = symm_mem.rendezvous(t, group.group_name)
+        out.append((t, [int(p) for p in h.buffer_ptrs], h))
+    return out
+
+
 class FusedRowParallel:
     """Row-parallel quantized linear + all-reduce as two b200q launches over peer memory
     (include/b200q.h: b200q_*_gemm_reduce_scatter, b200q_reduce_gather) instead of a GEMM followed
@@ -160,9 +238,11 @@ class FusedRowParallel:
     `replicate_row_parallel_bias`.  The first use of a bias tensor is checked across ranks.
     """
 
-    def __init__(self, mode: str, max_rows: int, n_out: int, group=None, fallback=None, sharded: bool = False):
+    def __init__(self, mode: str, max_rows: int, n_out: int, group=None, fallback=None, sharded: bool = False, comm=None):
         """`sharded`: also allocate the gathered-activation buffers of the token-sharded residual
-        stream (`partials_to_owners` / `reduce_norm_quantize` / `reduce_add`)."""
+        stream (`partials_to_owners` / `reduce_norm_quantize` / `reduce_add`).  `comm`: a `CommContext`
+        to take the peer buffers from (the library's own CUDA-IPC context) instead of torch's
+        symmetric-memory allocator."""
         import os
 
         # plain peer mappings are all this path needs; keep the allocator from also binding the
@@ -172,7 +252,7 @@ class FusedRowParallel:
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         if self.world > 8:
             raise ValueError("FusedRowParallel supports at most 8 ranks")
-        self.max_rows, self.n_out, self.sharded = max_rows, n_out, sharded
+        self.max_rows, self.n_out, self.sharded, self.comm = max_rows, n_out, sharded, comm
         # one set of peer buffers, flags and epoch counter per CUDA stream that calls in: calls on
         # different streams may overlap on the device and must not share them
         self._ctx: dict = {}
@@ -207,27 +287,18 @@ class FusedRowParallel:
         with the same stream order and the same `rows`."""
         import ctypes
 
-        import torch.distributed._symmetric_memory as symm_mem
-
         from . import _lib
 
         key = torch.cuda.current_stream().cuda_stream
         ctx = self._ctx.get(key)
         if ctx is not None and ctx["rows"] >= rows:
             return ctx
-        dev = torch.device("cuda", torch.cuda.current_device())
-        name = self.group.group_name
         nbytes = rows * self.n_out * 2
-        bufs, ptrs = [], []
         sizes = [nbytes, nbytes, 4096]
         if self.sharded:
             sizes += [rows * self.n_out, rows * 4]           # gathered FP8 codes and per-token scales
-        for size in sizes:
-            t = symm_mem.empty(size, dtype=torch.uint8, device=dev)
-            t.zero_()
-            h = symm_mem.rendezvous(t, name)
-            bufs.append((t, h))
-            ptrs.append([int(p) for p in h.buffer_ptrs])
+        bufs = _symmetric_buffers(sizes, self.group, self.comm)
+        ptrs = [b[1] for b in bufs]
         torch.cuda.current_stream().synchronize()
         dist.barrier(self.group)
         peers = _lib.Peers()
@@ -346,11 +417,9 @@ class PullRowParallel:
     tensor here.  Two partial buffers alternate between consecutive calls; a captured step must hold an
     even number of all-reduces so that replays start on the same buffer (a decoder layer has two)."""
 
-    def __init__(self, mode: str, max_rows: int, n_out: int, group=None):
+    def __init__(self, mode: str, max_rows: int, n_out: int, group=None, comm=None):
         import ctypes
         import os
-
-        import torch.distributed._symmetric_memory as symm_mem
 
         from . import _lib
 
@@ -362,25 +431,18 @@ class PullRowParallel:
         if self.world > 8:
             raise ValueError("PullRowParallel supports at most 8 ranks")
         self.max_rows, self.n_out = max_rows, n_out
-        dev = torch.device("cuda", torch.cuda.current_device())
-        name = self.group.group_name
-        self._bufs, self._peers, self._refs, self._partial = [], [], [], []
-        flags = symm_mem.empty(4096, dtype=torch.uint8, device=dev)
-        flags.zero_()
-        fh = symm_mem.rendezvous(flags, name)
-        self._bufs.append((flags, fh))
-        for _ in range(2):
-            t = symm_mem.empty(max_rows * n_out, dtype=torch.bfloat16, device=dev)
-            t.zero_()
-            h = symm_mem.rendezvous(t, name)
-            self._bufs.append((t, h))
+        nbytes = max_rows * n_out * 2
+        self._bufs = _symmetric_buffers([4096, nbytes, nbytes], self.group, comm)
+        self._peers, self._refs, self._partial = [], [], []
+        flag_ptrs = self._bufs[0][1]
+        for local, ptrs, *_ in self._bufs[1:]:
             peers = _lib.PullPeers()
             peers.rank, peers.world = self.rank, self.world
             for r in range(self.world):
-                peers.partial[r], peers.flags[r] = int(h.buffer_ptrs[r]), int(fh.buffer_ptrs[r])
+                peers.partial[r], peers.flags[r] = ptrs[r], flag_ptrs[r]
             self._peers.append(peers)
             self._refs.append(ctypes.byref(peers))
-            self._partial.append(t)
+            self._partial.append(local.view(torch.bfloat16))
         torch.cuda.current_stream().synchronize()
         dist.barrier(self.group)
         self._slot = 0

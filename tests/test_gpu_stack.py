@@ -141,8 +141,14 @@ def _tp_worker(rank, world, store_path, out_path, slabs, fused, micro, sharded):
 
     r = torch.ops.tensorrt.fused_nccl_all_reduce(t, "sum", group_name_of())
     assert torch.allclose(r.cpu(), torch.full((1, 4), world * (world + 1) / 2), atol=1e-3, rtol=1e-3)
+    comm = None
+    if fused == "comm":
+        # peer buffers from the library's own CUDA-IPC context instead of torch's symmetric memory
+        from tensorrt_b200.tp import CommContext
+
+        comm = CommContext()
     stack = DecoderStack(cfg, _to(ws, "cuda"), rank=rank, world=world, slabs=slabs, fused_rows=512 if fused else 0,
-                         pull_rows=64 if fused else 0)
+                         pull_rows=64 if fused else 0, comm=comm)
     if sharded and not fused:
         sharded = "collectives"                  # the process group's reduce-scatter / all-gather
     y = stack.forward(h.cuda(), micro, sharded)
@@ -182,12 +188,15 @@ def _tp_worker(rank, world, store_path, out_path, slabs, fused, micro, sharded):
     if rank == 0:
         torch.save(y.cpu(), out_path)
     dist.barrier()
+    if comm is not None:
+        del stack
+        comm.close()
     dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("slabs,fused,micro,sharded", [
     (1, False, 1, False), (2, False, 1, False), (1, True, 1, False), (1, False, 2, False), (1, True, 2, False),
-    (1, False, 1, True), (1, True, 1, True), (1, False, 2, True), (1, True, 2, True)])
+    (1, False, 1, True), (1, True, 1, True), (1, False, 2, True), (1, True, 2, True), (1, "comm", 2, True)])
 def test_tp2_stack_matches_oracle(b200, slabs, fused, micro, sharded):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

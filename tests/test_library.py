@@ -284,3 +284,20 @@ def test_registration_is_a_logged_no_op_without_torch_tensorrt(b200):
         import torch_tensorrt  # noqa: F401
     except Exception:
         assert b200.register_with_torch_tensorrt() == []
+
+
+def test_comm_context_argument_validation():
+    """b200q_comm_create rejects impossible rank / world values before touching a device."""
+    import ctypes
+
+    from tensorrt_b200 import _lib
+
+    lib = _lib.load()
+    h = ctypes.c_void_p()
+    null_cb = _lib.ALLGATHER_FN(0)
+    for rank, world in [(-1, 2), (2, 2), (0, 0), (0, 9)]:
+        assert lib.b200q_comm_create(rank, world, null_cb, None, ctypes.byref(h)) == -1
+    assert lib.b200q_comm_create(0, 2, null_cb, None, ctypes.byref(h)) == -1     # several ranks need the all-gather
+    assert lib.b200q_comm_create(0, 1, null_cb, None, None) == -1
+    assert lib.b200q_comm_alloc(None, 16, (ctypes.c_void_p * 8)()) == -1
+    assert lib.b200q_comm_destroy(None) == 0
