@@ -52,6 +52,25 @@ def time_device(fn, min_ms: float = 500.0, min_iters: int = 50, warmup: int = 3,
         n = int(min(max_iters - total_n, max(min_iters, (min_ms - total_ms) / max(per, 1e-4) * 1.1)))
 
 
+def time_graphed(fn, reps: int, min_ms: float = 500.0):
+    """ms per call of `fn()` with `reps` calls captured into one CUDA graph and the graph replayed
+    (time_device's rules): a launch of a few tens of microseconds issued from Python is otherwise
+    timed by the host, not by the device."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(reps):
+                fn()
+    torch.cuda.current_stream().wait_stream(side)
+    ms, n = time_device(graph.replay, min_ms, min_iters=max(4, 50 // reps + 1))
+    return ms / reps, n * reps
+
+
 def hbm_roofline(gbs: float, peaks, alg_bytes: float, kernel: str, traffic=None):
     return {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
             "peak_source": f"{peaks['source']} HBM copy bandwidth", "traffic": traffic, "kernel": kernel,
@@ -112,17 +131,42 @@ def quantize_suite(capi, peaks, min_ms=500.0):
             it[0] += 1
             return xs[it[0] % 3]
 
-        ms, k = time_device(lambda: capi.fp8_quantize(rot(), None), min_ms)
+        ms, k = time_graphed(lambda: capi.fp8_quantize(rot(), None), 12, min_ms)
         alg = 3.0 * n + 4.0 * rows
         out[f"fp8_per_token_quantize_{rows}x{cols}"] = {"ms": ms, "launches": k, "roofline": hbm_roofline(alg / ms / 1e6, peaks, alg, "fp8_rows_kernel<bf16>")}
-        ms, k = time_device(lambda: capi.amax(rot()), min_ms)
+        ms, k = time_graphed(lambda: capi.amax(rot()), 12, min_ms)
         out[f"amax_{rows}x{cols}"] = {"ms": ms, "launches": k, "roofline": hbm_roofline(2.0 * n / ms / 1e6, peaks, 2.0 * n, "amax_kernel<bf16>")}
         am = capi.amax(xs[0])
-        ms, k = time_device(lambda: capi.nvfp4_quantize(rot(), am), min_ms)
+        ms, k = time_graphed(lambda: capi.nvfp4_quantize(rot(), am), 12, min_ms)
         alg = bc.ALG_BYTES_PER_ELEM * n
         out[f"nvfp4_quantize_{rows}x{cols}"] = {"ms": ms, "launches": k,
                                                "roofline": hbm_roofline(alg / ms / 1e6, peaks, alg, "nvfp4_quantize_kernel<bf16, codes>")}
         del xs
+    return out
+
+
+def glue_suite(capi, peaks, min_ms=300.0, tokens=32768, hidden=8192, ffn=28672):
+    """The element-wise kernels between the GEMMs of one decoder layer at the stack workload's shape,
+    each against the HBM roofline (algorithmic bytes = every operand read once, every result written once)."""
+    out = {}
+    gu = [torch.randn(tokens, 2 * ffn, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    it = [0]
+
+    def rot(xs):
+        it[0] += 1
+        return xs[it[0] % len(xs)]
+
+    ms, k = time_device(lambda: capi.silu_mul_fp8_quantize(rot(gu)), min_ms)
+    alg = tokens * ffn * (4.0 + 1.0) + 4.0 * tokens
+    out[f"silu_mul_fp8_quantize_{tokens}x{ffn}"] = {"ms": ms, "launches": k, "roofline": hbm_roofline(alg / ms / 1e6, peaks, alg, "silu_mul_quant_kernel")}
+    del gu
+    hs = [torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16) for _ in range(3)]
+    ds = [torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16) for _ in range(3)]
+    w = torch.ones(hidden, device="cuda", dtype=torch.bfloat16)
+    ms, k = time_device(lambda: capi.add_rms_norm_fp8_quantize(rot(hs), rot(ds), w), min_ms)
+    alg = tokens * hidden * (2.0 + 2.0 + 2.0 + 1.0) + 4.0 * tokens      # h, delta in; h, codes out
+    out[f"add_rms_norm_fp8_quantize_{tokens}x{hidden}"] = {"ms": ms, "launches": k,
+                                                           "roofline": hbm_roofline(alg / ms / 1e6, peaks, alg, "add_norm_quant_kernel")}
     return out
 
 
@@ -270,6 +314,7 @@ def extras(capi, peaks, min_ms=500.0):
     the region they ran in."""
     with bc.ClockSampler(torch.cuda.current_device()) as clocks:
         out = {"quantize": quantize_suite(capi, peaks, min_ms)}
+        out["layer_glue"] = glue_suite(capi, peaks)
         for kind in ("fp8", "nvfp4"):
             out[kind + "_gemm"] = gemm_sweep(capi, peaks, kind, full_sweep_shapes(), min_ms)
         try:

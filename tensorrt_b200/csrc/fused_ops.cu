@@ -1,9 +1,15 @@
 // Elementwise / row-wise kernels either side of the quantized linears in the decoder
 // linear stack: RMSNorm, silu(gate) * up, residual add, and the "attention = identity on V"
 // head expansion.  All are HBM-bound streaming kernels over bf16 with 128-bit accesses.
+#include <type_traits>
+
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace b200q {
+namespace gemm {
+int* device_status_word();
+}
 namespace {
 
 constexpr int kThreads = 256;
@@ -181,6 +187,136 @@ add_norm_quant_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* 
   }
 }
 
+// Many-token form of add_norm_quant_kernel: persistent CTAs (two per SM) walk the rows with a stride
+// of the grid, and the rows of h and delta arrive through a ring of shared-memory stages filled by
+// bulk asynchronous copies that one thread issues `stages` rows ahead.  One CTA per row keeps too few
+// bytes in flight to cover the HBM latency (its loads stop while it reduces and stores); here the
+// copies of the next rows run during all of that.  Thread-to-element mapping, arithmetic and
+// reduction order are those of add_norm_quant_kernel, so the results are bit-identical.
+constexpr int kStreamStagesMax = 8;
+constexpr int kStreamRingBytes = 96 * 1024;
+
+template <int ITEMS, bool HAS_DELTA>
+__global__ void __launch_bounds__(kThreads, 2)
+add_norm_quant_stream_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ delta,
+                             const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out, uint8_t* __restrict__ codes,
+                             float* __restrict__ scales, int rows, int cols, float eps, int stages, int* __restrict__ status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(128) unsigned char ring[];
+  __shared__ uint64_t full[kStreamStagesMax];
+  __shared__ float red[kThreads / 32];
+  const uint32_t row_bytes = static_cast<uint32_t>(cols) * 2u;
+  const uint32_t stage_bytes = row_bytes * (HAS_DELTA ? 2u : 1u);
+  const int groups = cols >> 3;
+  const int step = static_cast<int>(gridDim.x);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) ptx::mbar_init(&full[s], 1);
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  auto issue = [&](int row, int s) {
+    ptx::mbar_arrive_expect_tx(&full[s], stage_bytes);
+    ptx::bulk_load(ring + (size_t)s * stage_bytes, h + (int64_t)row * cols, row_bytes, &full[s]);
+    if constexpr (HAS_DELTA) ptx::bulk_load(ring + (size_t)s * stage_bytes + row_bytes, delta + (int64_t)row * cols, row_bytes, &full[s]);
+  };
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      const int64_t row = (int64_t)blockIdx.x + (int64_t)s * step;
+      if (row < rows) issue(static_cast<int>(row), s);
+    }
+  }
+  // the norm weights of this thread's groups are the same for every row
+  uint4 wp[ITEMS];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int g = threadIdx.x + i * kThreads;
+    wp[i] = g < groups ? ld_nc_128(w + (int64_t)g * 8) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  int k = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += step, ++k) {
+    const int s = k % stages;
+    const bool arrived = ptx::mbar_wait(&full[s], static_cast<uint32_t>(k / stages) & 1u);
+    // also separates this row's use of `red` from the previous row's last read of it
+    if (__syncthreads_or(!arrived)) {
+      if (threadIdx.x == 0) atomicCAS(status, 0, 81);
+      break;
+    }
+    const unsigned char* st = ring + (size_t)s * stage_bytes;
+    float v[ITEMS][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const int g = threadIdx.x + i * kThreads;
+      if (g < groups) {
+        Elem<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(st + (size_t)g * 16), v[i]);
+        if constexpr (HAS_DELTA) {
+          float d[8];
+          Elem<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(st + row_bytes + (size_t)g * 16), d);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j] + d[j]));
+          Elem<__nv_bfloat16>::store8(h_out + row * cols + (int64_t)g * 8, v[i]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+      }
+    }
+    const float total = block_sum<kThreads>(ss, red);
+    // every thread has taken its part of the stage: refill it with the row `stages` steps ahead
+    if (threadIdx.x == 0) {
+      const int64_t next = row + (int64_t)stages * step;
+      if (next < rows) issue(static_cast<int>(next), s);
+    }
+    const float inv = rsqrtf(total / static_cast<float>(cols) + eps);
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const int g = threadIdx.x + i * kThreads;
+      if (g < groups) {
+        float wl[8];
+        Elem<__nv_bfloat16>::unpack(wp[i], wl);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j] * inv * wl[j]));
+          amax = fmaxf(amax, fabsf(v[i][j]));
+        }
+      }
+    }
+    amax = warp_max(amax);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = (threadIdx.x & 31) < kThreads / 32 ? red[threadIdx.x & 31] : 0.0f;
+    amax = warp_max(amax);
+    const float scale = fp8_scale_from_amax(amax);
+    if (threadIdx.x == 0) scales[row] = scale;
+    const float y = b200q_rcp_rn(scale);
+    auto emit = [&](auto fast_tag) {
+      constexpr bool kFast = decltype(fast_tag)::value;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int g = threadIdx.x + i * kThreads;
+        if (g < groups) {
+          float q[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) q[j] = kFast ? b200q_div_by_shared(v[i][j], scale, y) : __fdiv_rn(v[i][j], scale);
+          const uint32_t lo = f32x2_to_e4m3x2(q[0], q[1]) | (f32x2_to_e4m3x2(q[2], q[3]) << 16);
+          const uint32_t hi = f32x2_to_e4m3x2(q[4], q[5]) | (f32x2_to_e4m3x2(q[6], q[7]) << 16);
+          *reinterpret_cast<uint2*>(codes + row * cols + (int64_t)g * 8) = make_uint2(lo, hi);
+        }
+      }
+    };
+    if (b200q_div_fast_ok(scale)) emit(std::true_type{});   // one branch per row, not one select per element
+    else emit(std::false_type{});
+  }
+}
+
+// silu(a) * b = a / (1 + exp(-a)) * b with the hardware exponential and reciprocal (a few ulp in fp32,
+// below the bf16 rounding that follows); both kernels below use exactly this expression.
+__device__ __forceinline__ float silu_mul_f32(float a, float b) { return __fdividef(a, 1.0f + __expf(-a)) * b; }
+
 // act[t, j] = silu(gu[t, j]) * gu[t, F + j], gu is [T, 2F] (gate columns first)
 __global__ void __launch_bounds__(kThreads)
 silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int64_t rows, int64_t f) {
@@ -194,7 +330,7 @@ silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict_
     Elem<__nv_bfloat16>::load8(gu + row * 2 * f + c, a);
     Elem<__nv_bfloat16>::load8(gu + row * 2 * f + f + c, b);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = a[j] / (1.0f + __expf(-a[j])) * b[j];
+    for (int j = 0; j < 8; ++j) o[j] = silu_mul_f32(a[j], b[j]);
     Elem<__nv_bfloat16>::store8(act + row * f + c, o);
   }
 }
@@ -219,7 +355,7 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict_
   const int per_part = (groups + PARTS - 1) / PARTS;
   const int g_begin = part * per_part, g_end = min(groups, g_begin + per_part);
   uint4 y[ITEMS];
-  float amax = 0.0f;
+  __nv_bfloat162 m2 = __floats2bfloat162_rn(0.0f, 0.0f);   // running max |.| of the packed results (exact in bf16)
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
     const int g = g_begin + threadIdx.x + i * kThreads;
@@ -231,14 +367,13 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict_
       uint32_t* u = &y[i].x;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float o0 = a[2 * j] / (1.0f + __expf(-a[2 * j])) * b[2 * j];
-        const float o1 = a[2 * j + 1] / (1.0f + __expf(-a[2 * j + 1])) * b[2 * j + 1];
-        __nv_bfloat162 h = __floats2bfloat162_rn(o0, o1);
-        u[j] = *reinterpret_cast<uint32_t*>(&h);
-        amax = fmaxf(amax, fmaxf(fabsf(__low2float(h)), fabsf(__high2float(h))));
+        const __nv_bfloat162 h = __floats2bfloat162_rn(silu_mul_f32(a[2 * j], b[2 * j]), silu_mul_f32(a[2 * j + 1], b[2 * j + 1]));
+        u[j] = *reinterpret_cast<const uint32_t*>(&h);
+        m2 = __hmax2(m2, __habs2(h));
       }
     }
   }
+  float amax = fmaxf(__low2float(m2), __high2float(m2));
   amax = warp_max(amax);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
   __syncthreads();
@@ -255,20 +390,25 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict_
   const float scale = fp8_scale_from_amax(amax);
   if (threadIdx.x == 0 && part == 0) scales[row] = scale;
   const float rcp = b200q_rcp_rn(scale);
-  const bool fast = b200q_div_fast_ok(scale);
+  auto emit = [&](auto fast_tag) {
+    constexpr bool kFast = decltype(fast_tag)::value;
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    const int g = g_begin + threadIdx.x + i * kThreads;
-    if (g < g_end) {
-      float v[8], q[8];
-      Elem<__nv_bfloat16>::unpack(y[i], v);
+    for (int i = 0; i < ITEMS; ++i) {
+      const int g = g_begin + threadIdx.x + i * kThreads;
+      if (g < g_end) {
+        float v[8], q[8];
+        Elem<__nv_bfloat16>::unpack(y[i], v);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) q[j] = fast ? b200q_div_by_shared(v[j], scale, rcp) : __fdiv_rn(v[j], scale);
-      const uint32_t lo = f32x2_to_e4m3x2(q[0], q[1]) | (f32x2_to_e4m3x2(q[2], q[3]) << 16);
-      const uint32_t hi = f32x2_to_e4m3x2(q[4], q[5]) | (f32x2_to_e4m3x2(q[6], q[7]) << 16);
-      *reinterpret_cast<uint2*>(codes + row * f + (int64_t)g * 8) = make_uint2(lo, hi);
+        for (int j = 0; j < 8; ++j) q[j] = kFast ? b200q_div_by_shared(v[j], scale, rcp) : __fdiv_rn(v[j], scale);
+        const uint32_t lo = f32x2_to_e4m3x2(q[0], q[1]) | (f32x2_to_e4m3x2(q[2], q[3]) << 16);
+        const uint32_t hi = f32x2_to_e4m3x2(q[4], q[5]) | (f32x2_to_e4m3x2(q[6], q[7]) << 16);
+        *reinterpret_cast<uint2*>(codes + row * f + (int64_t)g * 8) = make_uint2(lo, hi);
+      }
     }
-  }
+  };
+  // one branch per row, not one select per element: the true division is an order of magnitude longer
+  if (b200q_div_fast_ok(scale)) emit(std::true_type{});
+  else emit(std::false_type{});
 }
 
 // out = a + b (bf16, fp32 add)
@@ -353,10 +493,35 @@ int b200q_add_rms_norm_fp8_quantize(const void* h, const void* delta, const void
   const int64_t groups = cols >> 3;
   int parts = 1;   // few tokens: split every row over a cluster so that the launch covers more SMs
   while (parts < 8 && rows * parts < 2 * sm_count() && groups / (parts * 2) >= kThreads / 2) parts *= 2;
-  // long rows: 16 groups per thread cost 92 registers (two CTAs per SM) and the kernel turns
-  // compute-bound on the exponentials; two CTAs per row at 8 groups per thread double the warps per SM
-  if (parts == 1 && groups > 8 * kThreads) parts = 2;
   const int items = static_cast<int>(((groups + parts - 1) / parts + kThreads - 1) / kThreads);
+  // many tokens: persistent CTAs fed through a shared-memory ring of rows
+  const int64_t stage_bytes = cols * 2 * (delta != nullptr ? 2 : 1);
+  if (parts == 1 && items <= 4 && rows >= 8 * sm_count() && kStreamRingBytes / stage_bytes >= 2) {
+    int stages = static_cast<int>(kStreamRingBytes / stage_bytes);
+    if (stages > kStreamStagesMax) stages = kStreamStagesMax;
+    int* status = gemm::device_status_word();
+    if (status == nullptr) return B200Q_ERR_CUDA;
+    const size_t smem = static_cast<size_t>(stages) * static_cast<size_t>(stage_bytes);
+    const dim3 grid(static_cast<unsigned>(2 * sm_count()));
+    const int r32 = static_cast<int>(rows), c32 = static_cast<int>(cols);
+#define B200Q_ANQS(I, D)                                                                                                     \
+  do {                                                                                                                        \
+    cudaFuncSetAttribute(add_norm_quant_stream_kernel<I, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamRingBytes); \
+    launch_pdl(add_norm_quant_stream_kernel<I, D>, grid, dim3(kThreads), smem, st, hp, dp, wp, op, codes_out, scales_out,     \
+               r32, c32, eps, stages, status);                                                                                \
+  } while (0)
+    if (delta != nullptr) {
+      if (items <= 1) B200Q_ANQS(1, true);
+      else if (items <= 2) B200Q_ANQS(2, true);
+      else B200Q_ANQS(4, true);
+    } else {
+      if (items <= 1) B200Q_ANQS(1, false);
+      else if (items <= 2) B200Q_ANQS(2, false);
+      else B200Q_ANQS(4, false);
+    }
+#undef B200Q_ANQS
+    return check_launch();
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(rows * parts));
   cfg.blockDim = dim3(kThreads);

@@ -205,15 +205,73 @@ constexpr int kAmaxThreads = 256;
 // Single-pass tensor abs-max.  Every CTA writes its partial maximum to `partials`, takes a
 // ticket; the last CTA to arrive reduces the partials, writes the result and re-arms the
 // ticket counter (so the workspace is zero again when the kernel ends).
+// Running abs-max over 32-byte chunks as they come from memory.  16-bit types stay packed: the
+// maximum of absolute values is exact in the input format, so two elements cost one instruction.
+template <typename T>
+struct ChunkMax;
+template <>
+struct ChunkMax<__nv_bfloat16> {
+  static constexpr int kElems = 16;
+  __nv_bfloat162 m = __floats2bfloat162_rn(0.0f, 0.0f);
+  __device__ __forceinline__ void add(const U32x8& r) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = __hmax2(m, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&r.v[i])));
+  }
+  __device__ __forceinline__ float get() const { return fmaxf(__low2float(m), __high2float(m)); }
+};
+template <>
+struct ChunkMax<__half> {
+  static constexpr int kElems = 16;
+  __half2 m = __floats2half2_rn(0.0f, 0.0f);
+  __device__ __forceinline__ void add(const U32x8& r) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = __hmax2(m, __habs2(*reinterpret_cast<const __half2*>(&r.v[i])));
+  }
+  __device__ __forceinline__ float get() const { return fmaxf(__low2float(m), __high2float(m)); }
+};
+template <>
+struct ChunkMax<float> {
+  static constexpr int kElems = 8;
+  float m = 0.0f;
+  __device__ __forceinline__ void add(const U32x8& r) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(__uint_as_float(r.v[i])));
+  }
+  __device__ __forceinline__ float get() const { return m; }
+};
+
+// `wide`: x is 32-byte aligned; the bulk then goes through 256-bit loads, four in flight per thread.
 template <typename T>
 __global__ void __launch_bounds__(kAmaxThreads)
 amax_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ out, float* __restrict__ partials,
-            unsigned int* __restrict__ ticket) {
+            unsigned int* __restrict__ ticket, bool wide) {
   __shared__ float red[kAmaxThreads / 32];
   __shared__ bool last;
   float local = 0.0f;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t done = 0;  // elements covered by the wide part
+  if (wide) {
+    constexpr int kE = ChunkMax<T>::kElems;
+    const int64_t chunks = n / kE;
+    ChunkMax<T> acc;
+    int64_t c = tid;
+    for (; c + 3 * stride < chunks; c += 4 * stride) {
+      const U32x8 r0 = ld_nc_256(x + c * kE);
+      const U32x8 r1 = ld_nc_256(x + (c + stride) * kE);
+      const U32x8 r2 = ld_nc_256(x + (c + 2 * stride) * kE);
+      const U32x8 r3 = ld_nc_256(x + (c + 3 * stride) * kE);
+      acc.add(r0);
+      acc.add(r1);
+      acc.add(r2);
+      acc.add(r3);
+    }
+    for (; c < chunks; c += stride) acc.add(ld_nc_256(x + c * kE));
+    local = acc.get();
+    done = chunks * kE;
+  }
   const int64_t groups = n >> 3;
-  for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < groups; g += (int64_t)gridDim.x * blockDim.x) {
+  for (int64_t g = (done >> 3) + tid; g < groups; g += stride) {
     float t[8];
     Elem<T>::load8(x + g * 8, t);
 #pragma unroll
@@ -265,18 +323,19 @@ row_amax_kernel(const T* __restrict__ x, float* __restrict__ out, int64_t rows, 
 // launcher used by the entry points below and by the no-scratch variants elsewhere
 int launch_amax(const void* x, int dtype, int64_t n, float* out, float* partials, unsigned int* ticket,
                 cudaStream_t st) {
-  const int64_t groups = n >> 3;
-  int blocks = static_cast<int>(groups / kAmaxThreads);
+  const bool wide = aligned(x, 32);
+  // one CTA per kAmaxThreads x 4 chunks of 32 bytes (16 bytes without the alignment), up to 8 CTAs per SM
+  int blocks = static_cast<int>((n >> 3) / (kAmaxThreads * (wide ? 8 : 1)));
   blocks = blocks < 1 ? 1 : (blocks > kAmaxBlocks ? kAmaxBlocks : blocks);
   switch (dtype) {
     case B200Q_BF16:
-      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), n, out, partials, ticket);
+      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), n, out, partials, ticket, wide);
       break;
     case B200Q_F16:
-      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __half*>(x), n, out, partials, ticket);
+      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __half*>(x), n, out, partials, ticket, wide);
       break;
     case B200Q_F32:
-      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const float*>(x), n, out, partials, ticket);
+      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const float*>(x), n, out, partials, ticket, wide);
       break;
     default:
       return B200Q_ERR_INVALID;
@@ -316,17 +375,18 @@ int static_scratch_address(unsigned char** out) {
 
 int launch_amax_static(const void* x, int dtype, int64_t n, float* out, float* partials, unsigned int* ticket,
                        cudaStream_t st) {
+  const bool wide = aligned(x, 32);
   int blocks = static_cast<int>((n + kStaticAmaxElemsPerBlock - 1) / kStaticAmaxElemsPerBlock);
   if (blocks < 1) blocks = 1;
   switch (dtype) {
     case B200Q_BF16:
-      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), n, out, partials, ticket);
+      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), n, out, partials, ticket, wide);
       break;
     case B200Q_F16:
-      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __half*>(x), n, out, partials, ticket);
+      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __half*>(x), n, out, partials, ticket, wide);
       break;
     case B200Q_F32:
-      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const float*>(x), n, out, partials, ticket);
+      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const float*>(x), n, out, partials, ticket, wide);
       break;
     default:
       return B200Q_ERR_INVALID;

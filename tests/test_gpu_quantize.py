@@ -123,6 +123,22 @@ def test_amax_kernels(capi):
             assert capi.amax(_cuda(x)).item() == x.float().abs().max().item()  # workspace re-armed
     x = _make(257, 4104, torch.bfloat16, seed=5)
     assert torch.equal(capi.row_amax(_cuda(x)).cpu(), o.row_amax(x))
+    # many 32-byte chunks per thread (the unrolled part of the kernel), then a 16-byte group and a
+    # scalar tail; the maximum is planted in each region in turn, with both signs, and the same
+    # again from a base pointer that is only 16-byte aligned (the narrow-load path)
+    n = 1184 * 256 * 16 * 9 + 8 + 5
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        base = torch.rand(n + 8, dtype=torch.float32).to(dtype).cuda()
+        for off in (0, 8 if dtype != torch.float32 else 4):
+            x = base[off:off + n]
+            assert x.data_ptr() % 32 == (0 if off == 0 else 16)
+            for pos in (0, 12345, 1184 * 256 * 16 * 8 + 77, n - 14, n - 13, n - 1):
+                for val in (3.0, -5.0):
+                    keep = x[pos].item()
+                    x[pos] = val
+                    assert capi.amax(x).item() == abs(val), (dtype, off, pos)
+                    x[pos] = keep
+            assert capi.amax(x).item() == x.float().abs().max().item()
 
 
 def test_special_values(capi):

@@ -100,6 +100,31 @@ def test_fused_add_norm_quantize(b200, cols):
     assert (codes2 != c3).float().mean().item() < 2e-2
 
 
+@pytest.mark.parametrize("cols", [64, 1040, 4096, 8192, 12288])
+@pytest.mark.parametrize("rows", [1184, 2501])
+def test_fused_add_norm_quantize_many_tokens(b200, rows, cols):
+    """From 8 rows per SM on, the kernel is the persistent one fed through a shared-memory ring of rows
+    (where a row fits the ring): bit-identical with the one-CTA-per-row form run on slices of the same
+    input, with and without delta, repeatedly (the ring's barriers start from scratch every launch)."""
+    capi = b200.capi
+    g = torch.Generator().manual_seed(rows + cols)
+    h = torch.randn(rows, cols, generator=g).bfloat16().cuda()
+    d = (torch.randn(rows, cols, generator=g) * 0.3).bfloat16().cuda()
+    w = (1 + 0.1 * torch.randn(cols, generator=g)).bfloat16().cuda()
+    # slices of 300 to 900 rows: one CTA per row there (fewer rows would split a row over a cluster,
+    # which sums the squares in another order)
+    edges = list(range(0, rows - 300, 400)) + [rows]
+    for delta in (d, None):
+        parts = [capi.add_rms_norm_fp8_quantize(h[a:b].clone(), None if delta is None else delta[a:b], w, 1e-5)
+                 for a, b in zip(edges[:-1], edges[1:])]
+        for _ in range(2):
+            h_new, codes, scales = capi.add_rms_norm_fp8_quantize(h.clone(), delta, w, 1e-5)
+            assert torch.equal(h_new, torch.cat([p[0] for p in parts]))
+            assert torch.equal(codes, torch.cat([p[1] for p in parts]))
+            assert torch.equal(scales, torch.cat([p[2] for p in parts]))
+    assert capi.device_status() == 0
+
+
 @pytest.mark.parametrize("mode", ["fp8", "nvfp4"])
 def test_stack_matches_oracle_single_gpu(b200, mode):
     from tensorrt_b200.stack import DecoderStack, StackConfig
