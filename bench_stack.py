@@ -195,6 +195,52 @@ def _layer_gemm_ms(capi, cfg, world, tokens):
     return total
 
 
+def collective_stage_times(capi, stack, cfg, world, rows, iters=20):
+    """CUDA-event time of one token-sharded row-parallel linear at this rank's shapes and `rows` tokens
+    (one micro-batch), `iters` of them back to back so that the ranks pace each other through the flag
+    exchange as in a forward: the GEMM whose epilogue pushes its partial tiles to the owners + the
+    owners' reduce, residual add, RMSNorm, FP8 quantize and all-gather of codes, against the same GEMM
+    with a local output alone.  Max over ranks, with the algorithmic NVLink bytes each rank sends."""
+    rp, layer = stack._fused, stack.layers[0]
+    h_shard = torch.zeros(rows // world, cfg.hidden, device="cuda", dtype=torch.bfloat16)
+    rp.prepare(rows)
+
+    def loop(fn):
+        for _ in range(3):
+            fn()
+        bc.barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return bc.max_over_ranks(e0.elapsed_time(e1) / iters, world)
+
+    out = {"tokens": rows}
+    push_bytes = 2.0 * rows * cfg.hidden * (world - 1) / world
+    gather_bytes = (1.0 * rows * cfg.hidden + 4.0 * rows) * (world - 1) / world
+    # HBM bytes of the owners' kernel: `world` partials and the residual in, residual and the local copy of the codes out
+    reduce_hbm = (rows / world) * cfg.hidden * (2.0 * world + 2.0 + 2.0) + rows * cfg.hidden * 1.0
+    for name, k, w in (("o_proj", cfg.q_width // world, layer.wo), ("down_proj", cfg.ffn // world, layer.wdown)):
+        x = capi.fp8_quantize(torch.randn(rows, k, device="cuda", dtype=torch.bfloat16), None)
+
+        def fused():
+            rp.partials_to_owners(x, w)
+            rp.reduce_norm_quantize(h_shard, layer.norm2, cfg.eps)
+
+        both = loop(fused)
+        local = loop(lambda: capi.fp8_gemm(x[0], x[1], w[0], w[1], None))
+        out[name] = {
+            "k_per_rank": k, "gemm_reduce_scatter_plus_reduce_gather_ms": both, "gemm_local_output_ms": local,
+            "exchange_and_reduce_ms": both - local,
+            "nvlink_bytes_out_per_rank": push_bytes + gather_bytes, "nvlink_ms_at_770GBps": (push_bytes + gather_bytes) / 770e9 * 1e3,
+            "reduce_kernel_hbm_bytes": reduce_hbm, "reduce_kernel_hbm_ms_at_measured_peak": reduce_hbm / (bc.measured_peaks()["hbm_gbs"] * 1e9) * 1e3,
+        }
+        del x
+    return out
+
+
 def run(args):
     from tensorrt_b200 import capi
     from tensorrt_b200.stack import DecoderStack, random_layer_weights
@@ -303,6 +349,8 @@ def run(args):
                      "nvlink_bytes_out_per_layer_per_rank": nvlink_out,
                      "nvlink_ms_per_layer_at_770GBps": nvlink_out / 770e9 * 1e3,
                      "limiter": "gemm" if gemm_ms >= 0.8 * per_layer_ms else "exchange + glue not hidden under the GEMMs"}
+        if sharded and fused:
+            breakdown["collective_stages"] = collective_stage_times(capi, stack, cfg, world, tokens // mb)
     kernels_per_layer = 10 if (world > 1 and sharded and fused) else 8
     launches = steps * (cfg.layers * kernels_per_layer * (mb if world > 1 else 1) + 2)
     line = {

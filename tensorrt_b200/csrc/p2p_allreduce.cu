@@ -14,6 +14,8 @@
 // word s of rank r = "rank s finished phase A", word world + s = "... phase C", last word =
 // block ticket.  Every wait is bounded (b200q_cfg::peer_wait_ms, default 2 s); a wait that gives up
 // records it in the device status word and the kernel returns without touching the output again.
+#include <type_traits>
+
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -278,6 +280,178 @@ reduce_norm_quant_gather_kernel(const GatherPeers pr, const __nv_bfloat16* __res
 }
 
 
+// The same kernel for whole micro-batches of a prefill: persistent CTAs, and every row it reads (the
+// `world` partials of a token, then the token's residual) arrives through a ring of shared-memory
+// stages filled by bulk asynchronous copies that one thread keeps issuing `stages` rows ahead, across
+// tokens.  The one-CTA-per-token form above issues its loads partial by partial and stops loading
+// while it reduces and stores; with 2 to 8 partials per token that leaves most of the HBM bandwidth
+// unused.  Thread-to-element mapping, summation order and rounding points are unchanged: same bits.
+constexpr int kGatherStagesMax = 12;
+constexpr int kGatherRingBytes = 96 * 1024;
+
+template <int ITEMS>
+__global__ void __launch_bounds__(kThreads, 2)
+reduce_norm_quant_gather_stream_kernel(const GatherPeers pr, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ h,
+                                       const __nv_bfloat16* __restrict__ w, int rows_per, int N, float eps, uint32_t epoch,
+                                       uint64_t limit_ns, int stages, int* status) {
+  extern __shared__ __align__(128) unsigned char ring[];
+  __shared__ uint64_t full[kGatherStagesMax];
+  __shared__ int s_last;
+  __shared__ float red[kThreads / 32];
+  const int W = pr.world;
+  uint32_t* my_flags = pr.flags[pr.rank];
+  const bool ok = *reinterpret_cast<volatile int*>(status) == 0;
+
+  if (ok) {
+    const int groups = N >> 3;
+    const uint32_t row_bytes = static_cast<uint32_t>(N) * 2u;
+    const int64_t slot = static_cast<int64_t>(rows_per) * N;
+    const int step = static_cast<int>(gridDim.x);
+    const int my_rows = (rows_per - static_cast<int>(blockIdx.x) + step - 1) / step;   // rows this CTA walks
+    const int per_row = W + 1;                                                         // W partials, then the residual
+    const int total = my_rows * per_row;
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < stages; ++s) ptx::mbar_init(&full[s], 1);
+      ptx::fence_barrier_init();
+    }
+    __syncthreads();
+    // copy number q of this CTA: source q % per_row of its row number q / per_row
+    auto issue = [&](int q) {
+      const int64_t row = static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(q / per_row) * step;
+      const int src = q % per_row;
+      const __nv_bfloat16* from = src < W ? pr.recv + src * slot + row * N : h + row * N;
+      const int s = q % stages;
+      ptx::mbar_arrive_expect_tx(&full[s], row_bytes);
+      ptx::bulk_load(ring + static_cast<size_t>(s) * row_bytes, from, row_bytes, &full[s]);
+    };
+    if (threadIdx.x == 0)
+      for (int q = 0; q < stages && q < total; ++q) issue(q);
+    // norm weights and bias of this thread's groups: the same for every token
+    uint4 wp[ITEMS], bp[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const int g = threadIdx.x + i * kThreads;
+      wp[i] = g < groups ? ld_nc_128(w + static_cast<int64_t>(g) * 8) : make_uint4(0u, 0u, 0u, 0u);
+      bp[i] = (g < groups && bias != nullptr) ? ld_nc_128(bias + static_cast<int64_t>(g) * 8) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    bool arrived = true;   // after one wait gave up the rest are not waited for: the status word says the result is void
+    int q = 0;
+    // one stage consumed: wait for it, hand the 16 bytes of every group of this thread to `use`, and once
+    // the whole CTA has read it let thread 0 refill it with the copy `stages` places ahead
+    auto consume = [&](auto&& use) {
+      const int s = q % stages;
+      if (arrived && !ptx::mbar_wait(&full[s], static_cast<uint32_t>(q / stages) & 1u)) {
+        arrived = false;
+        atomicCAS(status, 0, 25);
+      }
+      const unsigned char* st = ring + static_cast<size_t>(s) * row_bytes;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int g = threadIdx.x + i * kThreads;
+        if (g < groups) use(i, *reinterpret_cast<const uint4*>(st + static_cast<size_t>(g) * 16));
+      }
+      __syncthreads();
+      if (threadIdx.x == 0 && q + stages < total) issue(q + stages);
+      ++q;
+    };
+    for (int64_t row = blockIdx.x; row < rows_per; row += step) {
+      float v[ITEMS][8];
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+      for (int src = 0; src < W; ++src) {
+        consume([&](int i, const uint4& raw) {
+          float pv[8];
+          Elem<__nv_bfloat16>::unpack(raw, pv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] += pv[j];
+        });
+      }
+      float ss = 0.0f;
+      consume([&](int i, const uint4& raw) {
+        float hv[8];
+        Elem<__nv_bfloat16>::unpack(raw, hv);
+        if (bias != nullptr) {
+          float b[8];
+          Elem<__nv_bfloat16>::unpack(bp[i], b);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] += b[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[i][j] = __bfloat162float(__float2bfloat16_rn(hv[j] + __bfloat162float(__float2bfloat16_rn(v[i][j]))));
+          ss = fmaf(v[i][j], v[i][j], ss);
+        }
+        Elem<__nv_bfloat16>::store8(h + row * N + static_cast<int64_t>(threadIdx.x + i * kThreads) * 8, v[i]);
+      });
+      const float inv = rsqrtf(block_sum<kThreads>(ss, red) / static_cast<float>(N) + eps);
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const int g = threadIdx.x + i * kThreads;
+        if (g < groups) {
+          float wv[8];
+          Elem<__nv_bfloat16>::unpack(wp[i], wv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j] * inv * wv[j]));
+            amax = fmaxf(amax, fabsf(v[i][j]));
+          }
+        }
+      }
+      amax = warp_max(amax);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+      __syncthreads();
+      amax = (threadIdx.x & 31) < kThreads / 32 ? red[threadIdx.x & 31] : 0.0f;
+      amax = warp_max(amax);
+      __syncthreads();  // scratch free for the next token
+      const float scale = fp8_scale_from_amax(amax);
+      const int64_t grow = static_cast<int64_t>(pr.rank) * rows_per + row;
+      if (threadIdx.x < W) pr.scales[threadIdx.x][grow] = scale;
+      const float y = b200q_rcp_rn(scale);
+      auto emit = [&](auto fast_tag) {
+        constexpr bool kFast = decltype(fast_tag)::value;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          const int g = threadIdx.x + i * kThreads;
+          if (g < groups) {
+            float qv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) qv[j] = kFast ? b200q_div_by_shared(v[i][j], scale, y) : __fdiv_rn(v[i][j], scale);
+            const uint32_t lo = f32x2_to_e4m3x2(qv[0], qv[1]) | (f32x2_to_e4m3x2(qv[2], qv[3]) << 16);
+            const uint32_t hi = f32x2_to_e4m3x2(qv[4], qv[5]) | (f32x2_to_e4m3x2(qv[6], qv[7]) << 16);
+            const uint2 packed = make_uint2(lo, hi);
+            for (int r = 0; r < W; ++r) *reinterpret_cast<uint2*>(pr.codes[r] + grow * N + static_cast<int64_t>(g) * 8) = packed;
+          }
+        }
+      };
+      if (b200q_div_fast_ok(scale)) emit(std::true_type{});   // one branch per token, not one select per element
+      else emit(std::false_type{});
+    }
+  }
+
+  // ---- gathered activations exchanged; the last block to finish signals and waits (as above)
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int t = atomicAdd(my_flags + 2 * W, 1u);
+    s_last = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) my_flags[2 * W] = 0u;  // re-arm the ticket
+    if (ok && *reinterpret_cast<volatile int*>(status) == 0) {
+      if (threadIdx.x < W) {
+        __threadfence_system();
+        st_release_sys(pr.flags[threadIdx.x] + W + pr.rank, epoch);
+        if (!wait_epoch(my_flags + W + threadIdx.x, epoch, limit_ns)) atomicCAS(status, 0, 24);
+      }
+    }
+  }
+}
+
+
 // ---------------------------------------------------------------------------------------------
 // Decode-sized all-reduce by pulling (a few tokens, M <= 128): the row-parallel GEMM leaves this
 // rank's partial [M, N] in its own symmetric buffer, a one-warp kernel tells every peer "my partial
@@ -512,6 +686,26 @@ int b200q_reduce_add_rms_norm_fp8_quantize_gather(const b200q_gather_peers* peer
   fp.world = W;
   for (int r = 0; r < W; ++r) fp.flags[r] = pr.flags[r];
   exchange_flags_kernel<<<1, 32, 0, st>>>(fp, epoch, limit_ns, status);
+  // whole micro-batches: persistent CTAs fed through a shared-memory ring, an equal number of tokens each
+  if (items <= 4 && rows_per >= 64 && kGatherRingBytes / (N * 2) >= 3) {
+    int stages = static_cast<int>(kGatherRingBytes / (N * 2));
+    if (stages > kGatherStagesMax) stages = kGatherStagesMax;
+    const int64_t slots = static_cast<int64_t>(sm_count()) * 2;
+    const int64_t rows_per_cta = (rows_per + slots - 1) / slots;
+    const unsigned sgrid = static_cast<unsigned>((rows_per + rows_per_cta - 1) / rows_per_cta);
+    const size_t smem = static_cast<size_t>(stages) * static_cast<size_t>(N) * 2;
+    const int r32 = static_cast<int>(rows_per), n32 = static_cast<int>(N);
+#define B200Q_RNQG(I)                                                                                                          \
+  do {                                                                                                                          \
+    cudaFuncSetAttribute(reduce_norm_quant_gather_stream_kernel<I>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGatherRingBytes); \
+    reduce_norm_quant_gather_stream_kernel<I><<<sgrid, kThreads, smem, st>>>(pr, bp, hp, wp, r32, n32, eps, epoch, limit_ns, stages, status); \
+  } while (0)
+    if (items <= 1) B200Q_RNQG(1);
+    else if (items <= 2) B200Q_RNQG(2);
+    else B200Q_RNQG(4);
+#undef B200Q_RNQG
+    return check_launch();
+  }
   if (items <= 1) reduce_norm_quant_gather_kernel<1><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, limit_ns, status);
   else if (items <= 2) reduce_norm_quant_gather_kernel<2><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, limit_ns, status);
   else if (items <= 4) reduce_norm_quant_gather_kernel<4><<<grid, kThreads, 0, st>>>(pr, bp, hp, wp, rows_per, N, eps, epoch, limit_ns, status);

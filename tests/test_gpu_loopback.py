@@ -165,7 +165,10 @@ def test_known_answer_through_the_fused_reduction(b200, world):
         assert torch.allclose(rk.out[r].float().cpu(), torch.full((M, N), world * (world + 1) / 2), atol=1e-3, rtol=1e-3)
 
 
-@pytest.mark.parametrize("world,M,N,K", [(2, 512, 512, 1024), (4, 1024, 1024, 2048), (8, 2048, 2048, 4096), (2, 256, 8192, 512)])
+# the last three: persistent CTAs that walk 4 and 7 tokens each (ring stages reused across tokens), and
+# a row too long for the ring (one CTA per token)
+@pytest.mark.parametrize("world,M,N,K", [(2, 512, 512, 1024), (4, 1024, 1024, 2048), (8, 2048, 2048, 4096), (2, 256, 8192, 512),
+                                         (2, 2048, 4096, 512), (8, 16384, 1024, 1024), (2, 256, 16384, 512)])
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_reduce_norm_quantize_gather_loopback(b200, world, M, N, K, with_bias):
     """Token-sharded form: GEMM (reduce-scatter epilogue) -> reduce + bias + residual add + RMSNorm +
