@@ -20,7 +20,7 @@
 // rescaling scheme whose quantization points would differ from the definition above.
 //
 // One CTA per (batch, head, 128 queries): warp 0 = TMA producer, warp 1 = MMA issue + tensor-memory
-// allocation, warps 2-5 = softmax (one query row per thread, lane quarter = warp & 3).  K and Q tiles are
+// allocation, warps 2-9 = softmax (two threads per query row, each half of the columns; lane quarter = warp & 3).  K and Q tiles are
 // [rows, D] with D bytes per row (K-major), V is supplied TRANSPOSED per head ([D, keys], produced by
 // b200q_fp8_quantize_transpose) so that the second contraction is K-major too.  D <= 128 (a multiple of
 // 16); rows are zero-filled to 128 bytes by the TMA loads.  No TMA multicast; every wait is bounded.
@@ -40,11 +40,18 @@ EncodeTiledFn encode_tiled();
 
 namespace {
 
-constexpr int kAttThreads = 192;
+constexpr int kAttThreads = 320;          // producer warp, MMA warp, 8 softmax warps
 constexpr int kTile = 128;                 // queries per CTA, keys per step, padded head dimension
 constexpr int kTileBytes = kTile * 128;    // one operand tile: 128 rows x 128 bytes
-constexpr int kKStages = 3, kVStages = 2;
-constexpr int kAttSmem = 1024 + kTileBytes * (1 + kKStages + kVStages + 2) + 1024;
+// Two CTAs per SM: while one waits for its tensor-core results the other's softmax warps have the issue
+// slots.  Per CTA that leaves 6 operand tiles of shared memory (Q, 2 K stages, 1 V stage, 2 P tiles) and
+// 256 columns of tensor memory: one output accumulator and one score tile.  The score tile is computed
+// and consumed as two halves of 64 keys (two buffers of 64 columns), so that the tensor core fills one
+// half while the softmax warps work on the other.
+constexpr int kKStages = 2, kVStages = 1, kSBufs = 2;
+constexpr int kHalf = kTile / 2;           // keys per score buffer
+constexpr int kTmemCols = 256;
+constexpr int kAttSmem = 1024 + kTileBytes * (1 + kKStages + kVStages + 2) + 4096;   // tail: barriers, row statistics
 
 struct AttParams {
   const float* q_scale;     // per-tensor scales (device scalars)
@@ -60,7 +67,14 @@ struct AttParams {
 
 __device__ __forceinline__ void att_timeout(int* status, int where) { atomicCAS(status, 0, where); }
 
-__global__ void __launch_bounds__(kAttThreads, 1)
+// 2^x on the special-function unit (about 2 ulp; -inf -> 0, subnormal results flushed)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kAttThreads, 2)
 fp8_sdpa_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_vt, const AttParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -75,12 +89,13 @@ fp8_sdpa_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint64_t* k_empty = k_full + kKStages;
   uint64_t* v_full = k_empty + kKStages;
   uint64_t* v_empty = v_full + kVStages;
-  uint64_t* s_full = v_empty + kVStages;     // 2 score buffers in tensor memory
-  uint64_t* s_empty = s_full + 2;
-  uint64_t* p_full = s_empty + 2;            // 2 probability tiles in shared memory
+  uint64_t* s_full = v_empty + kVStages;     // score buffers in tensor memory
+  uint64_t* s_empty = s_full + kSBufs;
+  uint64_t* p_full = s_empty + kSBufs;       // 2 probability tiles in shared memory
   uint64_t* p_empty = p_full + 2;
   uint64_t* o_full = p_empty + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_full + 1);
+  float2* row_stat = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(bars) + 1024);   // [2][kTile] (max, sum) of each column half
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * kTile;
@@ -96,10 +111,12 @@ fp8_sdpa_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     ptx::mbar_init(q_full, 1);
     for (int s = 0; s < kKStages; ++s) ptx::mbar_init(k_full + s, 1), ptx::mbar_init(k_empty + s, 1);
     for (int s = 0; s < kVStages; ++s) ptx::mbar_init(v_full + s, 1), ptx::mbar_init(v_empty + s, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kSBufs; ++s) {
       ptx::mbar_init(s_full + s, 1);
-      ptx::mbar_init(s_empty + s, 4);   // one arrival per softmax warp
-      ptx::mbar_init(p_full + s, 4);
+      ptx::mbar_init(s_empty + s, 8);   // one arrival per softmax warp
+    }
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(p_full + s, 8);
       ptx::mbar_init(p_empty + s, 1);
     }
     ptx::mbar_init(o_full, 1);
@@ -109,14 +126,14 @@ fp8_sdpa_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     ptx::prefetch_tmap(&tmap_vt);
   }
   if (warp == 1) {
-    ptx::tmem_alloc<1>(tmem_holder, 512);
+    ptx::tmem_alloc<1>(tmem_holder, kTmemCols);
     ptx::tmem_relinquish<1>();
   }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmem_o = tmem_base + 256;
+  const uint32_t tmem_o = tmem_base + kSBufs * kHalf;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -172,22 +189,30 @@ fp8_sdpa_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t kph = 0, vph = 0, sph = 0, pph = 0;
       bool ok = ptx::mbar_wait(q_full, 0);
       if (!ok) att_timeout(p.status, 65);
-      // S[sb] = Q K_j^T for the next key tile in ring order
+      // S[sb] = Q K^T for the two halves (64 keys each) of the next key tile in ring order
+      constexpr uint32_t idesc_half = ptx::idesc_f8(kTile, kHalf);
       auto issue_scores = [&]() -> bool {
-        if (!ptx::mbar_wait(k_full + ks, kph) || !ptx::mbar_wait(s_empty + sb, sph ^ 1u)) {
+        if (!ptx::mbar_wait(k_full + ks, kph)) {
           att_timeout(p.status, 66);
           return false;
         }
-        ptx::tc_fence_after();
-        const uint32_t k_lo = k_lo0 + ks * (kTileBytes >> 4);
+        for (int hh = 0; hh < 2; ++hh) {
+          if (!ptx::mbar_wait(s_empty + sb, sph ^ 1u)) {
+            att_timeout(p.status, 66);
+            return false;
+          }
+          ptx::tc_fence_after();
+          // keys 64 hh .. 64 hh + 63 of the stage: 64 rows of 128 bytes further on (whole swizzle atoms)
+          const uint32_t k_lo = k_lo0 + ks * (kTileBytes >> 4) + hh * ((kHalf * 128) >> 4);
 #pragma unroll
-        for (int kb = 0; kb < 4; ++kb)
-          ptx::mma_f8<1>(tmem_base + sb * kTile, ptx::desc_join(q_lo + kb * 2, ptx::kDescHiSw128),
-                         ptx::desc_join(k_lo + kb * 2, ptx::kDescHiSw128), idesc, kb > 0 ? 1u : 0u);
-        ptx::tc_commit<1>(s_full + sb);
+          for (int kb = 0; kb < 4; ++kb)
+            ptx::mma_f8<1>(tmem_base + sb * kHalf, ptx::desc_join(q_lo + kb * 2, ptx::kDescHiSw128),
+                           ptx::desc_join(k_lo + kb * 2, ptx::kDescHiSw128), idesc_half, kb > 0 ? 1u : 0u);
+          ptx::tc_commit<1>(s_full + sb);
+          if (++sb == kSBufs) sb = 0, sph ^= 1u;
+        }
         ptx::tc_commit<1>(k_empty + ks);
         if (++ks == kKStages) ks = 0, kph ^= 1u;
-        if (++sb == 2) sb = 0, sph ^= 1u;
         return true;
       };
       for (int j = 0; j < n_tiles && ok; ++j) ok = issue_scores();         // pass 1: scores only
@@ -215,94 +240,124 @@ fp8_sdpa_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (ok) ptx::tc_commit<1>(o_full);
     }
   } else {
-    // ------------------------------------------------------------ softmax (warps 2..5): one query row per thread
+    // ------------------------------------------------------------ softmax (warps 2..9): two threads per query row.
+    // A warp reaches the 32 tensor-memory lanes of its quarter (warp & 3); the two warps of a quarter split
+    // the columns: of every 64-key score buffer (and of the output) warp set `ch` takes the 32-column chunk ch.
     const int q = warp & 3;
+    const int ch = (warp - 2) >> 2;
     const int r = q * 32 + lane;                  // row inside the tile
     const int qi = q0 + r;                        // query index inside the head
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    // scores in the base-2 exponent domain: s2 = acc * (q_scale * k_scale * softmax_scale * log2(e))
+    // scores in the base-2 exponent domain: s2 = acc * c2, c2 = q_scale * k_scale * softmax_scale * log2(e) > 0,
+    // so the running maximum is kept on the raw accumulators and the scaling rides in the FMA in front of ex2
     const float c2 = __ldg(p.q_scale) * __ldg(p.k_scale) * p.softmax_scale * 1.4426950408889634f;
     const int last_key = p.causal ? min(k_end - 1, qi + shift) : k_end - 1;   // keys beyond it are masked for this row
+    // key tiles below this index are visible to every row of the CTA in full: no per-element mask there
+    const int full_tiles = (p.causal ? max(0, min(k_end, q0 + shift + 1)) : k_end) / kTile;
     int sb = 0, pb = 0;
     uint32_t sph = 0, pph = 0;
-    float m = -INFINITY, l = 0.0f;
+    float m = -INFINITY, l = 0.0f;                // raw-accumulator maximum, sum of 2^(s2 - m * c2)
     bool ok = true;
-    // ---- pass 1: running maximum and sum
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    // ---- pass 1: running maximum and sum, one half tile (64 keys) per step
+    for (int t = 0; t < 2 * n_tiles && ok; ++t) {
       if (!ptx::mbar_wait(s_full + sb, sph)) {
         att_timeout(p.status, 68);
         ok = false;
         break;
       }
       ptx::tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      const bool masked = (t >> 1) >= full_tiles;
+      {
+        const int c = ch;
         uint32_t v[32];
-        ptx::tmem_ld_32x32(tmem_base + lane_addr + sb * kTile + c * 32, v);
+        ptx::tmem_ld_32x32(tmem_base + lane_addr + sb * kHalf + c * 32, v);
         ptx::tmem_ld_wait();
-        const int key0 = j * kTile + c * 32;
-        float cm = -INFINITY;
+        if (masked) {
+          const int key0 = t * kHalf + c * 32;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s2 = (key0 + i <= last_key) ? __uint_as_float(v[i]) * c2 : -INFINITY;
-          v[i] = __float_as_uint(s2);
-          cm = fmaxf(cm, s2);
+          for (int i = 0; i < 32; ++i)
+            if (key0 + i > last_key) v[i] = 0xff800000u;   // -inf
         }
+        float cm = __uint_as_float(v[0]);
+#pragma unroll
+        for (int i = 1; i < 32; ++i) cm = fmaxf(cm, __uint_as_float(v[i]));
         if (cm > m) {
-          l *= exp2f(m - cm);                     // m = -inf: l is 0 and stays 0
+          l *= ex2_approx((m - cm) * c2);         // m = -inf: l is 0 and stays 0
           m = cm;
         }
         if (m > -INFINITY) {
+          const float off = -m * c2;
+          float l0 = 0.0f, l1 = 0.0f;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) l += exp2f(__uint_as_float(v[i]) - m);
+          for (int i = 0; i < 32; i += 2) {
+            l0 += ex2_approx(fmaf(__uint_as_float(v[i]), c2, off));
+            l1 += ex2_approx(fmaf(__uint_as_float(v[i + 1]), c2, off));
+          }
+          l += l0 + l1;
         }
       }
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(s_empty + sb);
-      if (++sb == 2) sb = 0, sph ^= 1u;
+      if (++sb == kSBufs) sb = 0, sph ^= 1u;
     }
-    const float inv_l = l > 0.0f ? 1.0f / l : 0.0f;
-    // ---- pass 2: final probabilities, quantized with scale 1/448, written as the A operand of P V
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!ptx::mbar_wait(s_full + sb, sph) || !ptx::mbar_wait(p_empty + pb, pph ^ 1u)) {
+    // the two threads of a row each hold the statistics of their columns: merge (every softmax thread gets here)
+    row_stat[ch * kTile + r] = make_float2(m, l);
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    {
+      const float2 o = row_stat[(ch ^ 1) * kTile + r];
+      const float mm = fmaxf(m, o.x);
+      const float mine = m > -INFINITY ? l * ex2_approx((m - mm) * c2) : 0.0f;
+      const float theirs = o.x > -INFINITY ? o.y * ex2_approx((o.x - mm) * c2) : 0.0f;
+      l = mine + theirs;
+      m = mm;
+    }
+    // ---- pass 2: final probabilities, quantized with scale 1/448, written as the A operand of P V:
+    // 448 * 2^(s2 - m2) / l = 2^(acc * c2 + off2) with the normaliser folded into the exponent
+    const float off2 = l > 0.0f ? -m * c2 + __log2f(kE4M3Max / l) : -INFINITY;
+    for (int t = 0; t < 2 * n_tiles && ok; ++t) {
+      const int hh = t & 1;
+      if (!ptx::mbar_wait(s_full + sb, sph) || (hh == 0 && !ptx::mbar_wait(p_empty + pb, pph ^ 1u))) {
         att_timeout(p.status, 69);
         ok = false;
         break;
       }
       ptx::tc_fence_after();
+      const bool masked = (t >> 1) >= full_tiles;
       uint8_t* prow = sp + pb * kTileBytes + r * 128;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      {
+        const int c = ch;
         uint32_t v[32];
-        ptx::tmem_ld_32x32(tmem_base + lane_addr + sb * kTile + c * 32, v);
+        ptx::tmem_ld_32x32(tmem_base + lane_addr + sb * kHalf + c * 32, v);
         ptx::tmem_ld_wait();
-        const int key0 = j * kTile + c * 32;
+        if (masked) {
+          const int key0 = t * kHalf + c * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (key0 + i > last_key) v[i] = 0xff800000u;   // -inf -> probability 0
+        }
         uint32_t w[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           float pr[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int idx = 4 * i + e;
-            const float s2 = __uint_as_float(v[idx]) * c2;
-            pr[e] = (key0 + idx <= last_key) ? exp2f(s2 - m) * inv_l * kE4M3Max : 0.0f;
-          }
+          for (int e = 0; e < 4; ++e) pr[e] = ex2_approx(fmaf(__uint_as_float(v[4 * i + e]), c2, off2));
           w[i] = f32x2_to_e4m3x2(pr[0], pr[1]) | (f32x2_to_e4m3x2(pr[2], pr[3]) << 16);
         }
         // 128-byte swizzle of the operand layout: the 16-byte piece i of row r lives at piece i ^ (r & 7)
-        *reinterpret_cast<uint4*>(prow + (((2 * c) ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(prow + (((2 * c + 1) ^ (r & 7)) * 16)) = make_uint4(w[4], w[5], w[6], w[7]);
+        const int piece = 2 * (hh * 2 + c);
+        *reinterpret_cast<uint4*>(prow + ((piece ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(prow + (((piece + 1) ^ (r & 7)) * 16)) = make_uint4(w[4], w[5], w[6], w[7]);
       }
-      ptx::fence_proxy_async();                   // the tensor core reads this tile through the async proxy
+      if (hh == 1) ptx::fence_proxy_async();      // the tensor core reads this tile through the async proxy
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        ptx::mbar_arrive(p_full + pb);
+        if (hh == 1) ptx::mbar_arrive(p_full + pb);
         ptx::mbar_arrive(s_empty + sb);
       }
-      if (++sb == 2) sb = 0, sph ^= 1u;
-      if (++pb == 2) pb = 0, pph ^= 1u;
+      if (++sb == kSBufs) sb = 0, sph ^= 1u;
+      if (hh == 1 && ++pb == 2) pb = 0, pph ^= 1u;
     }
     // ---- output: O * (v_scale / 448) -> out dtype
     if (ok && n_tiles > 0 && !ptx::mbar_wait(o_full, 0)) {
@@ -316,7 +371,7 @@ fp8_sdpa_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const float oscale = n_tiles > 0 ? __ldg(p.v_scale) / kE4M3Max : 0.0f;
       const int64_t row_off = (static_cast<int64_t>(bh) * p.Sq + qi) * p.D;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * ch; c < 2 * ch + 2; ++c) {
         if (c * 32 >= p.D) break;
         uint32_t v[32];
         if (n_tiles > 0) {
@@ -345,7 +400,7 @@ fp8_sdpa_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc<1>(tmem_base, 512);
+    ptx::tmem_dealloc<1>(tmem_base, kTmemCols);
   }
 }
 
