@@ -411,6 +411,119 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict_
   else emit(std::false_type{});
 }
 
+// Many-token form of silu_mul_quant_kernel: persistent CTAs (two per SM), one row per iteration, the
+// gate and up halves of the row arriving in chunks of 2 * kThreads groups (8 KB each) through a ring of
+// shared-memory stages that one thread keeps filled with bulk asynchronous copies, across rows.  The
+// row's results wait in registers, packed as bf16, for the row maximum.  Same expression, rounding
+// points and thread-to-element mapping per chunk as the per-row kernels: same codes and scales.
+constexpr int kSiluChunkGroups = 2 * kThreads;                // groups of 8 elements per chunk and half
+constexpr int kSiluChunkBytes = kSiluChunkGroups * 16;        // per half
+constexpr int kSiluStages = 6;                                // 6 x 16 KB
+
+template <int CHUNKS>
+__global__ void __launch_bounds__(kThreads, 2)
+silu_mul_quant_stream_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict__ codes, float* __restrict__ scales, int rows,
+                             int f, int* __restrict__ status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(128) unsigned char ring[];
+  __shared__ uint64_t full[kSiluStages];
+  __shared__ float red[kThreads / 32];
+  const int groups = f >> 3;
+  const int nch = (groups + kSiluChunkGroups - 1) / kSiluChunkGroups;    // chunks per row (<= CHUNKS)
+  const int step = static_cast<int>(gridDim.x);
+  const int my_rows = (rows - static_cast<int>(blockIdx.x) + step - 1) / step;
+  const int total = my_rows * nch;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kSiluStages; ++s) ptx::mbar_init(&full[s], 1);
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  // copy number q of this CTA: chunk q % nch of its row number q / nch; gate half first, up half behind it
+  auto issue = [&](int q) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(q / nch) * step;
+    const int c = q % nch;
+    const int g0 = c * kSiluChunkGroups;
+    const uint32_t bytes = static_cast<uint32_t>(min(kSiluChunkGroups, groups - g0)) * 16u;
+    const __nv_bfloat16* gate = gu + row * 2 * f + static_cast<int64_t>(g0) * 8;
+    const int s = q % kSiluStages;
+    unsigned char* dst = ring + static_cast<size_t>(s) * (2 * kSiluChunkBytes);
+    ptx::mbar_arrive_expect_tx(&full[s], 2 * bytes);
+    ptx::bulk_load(dst, gate, bytes, &full[s]);
+    ptx::bulk_load(dst + kSiluChunkBytes, gate + f, bytes, &full[s]);
+  };
+  if (threadIdx.x == 0)
+    for (int q = 0; q < kSiluStages && q < total; ++q) issue(q);
+  bool arrived = true;   // after one wait gave up the rest are not waited for: the status word says the result is void
+  int q = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += step) {
+    uint4 y[CHUNKS][2];
+    __nv_bfloat162 m2 = __floats2bfloat162_rn(0.0f, 0.0f);
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      if (c < nch) {
+        const int s = q % kSiluStages;
+        if (arrived && !ptx::mbar_wait(&full[s], static_cast<uint32_t>(q / kSiluStages) & 1u)) {
+          arrived = false;
+          atomicCAS(status, 0, 82);
+        }
+        const unsigned char* st = ring + static_cast<size_t>(s) * (2 * kSiluChunkBytes);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int gl = threadIdx.x + i * kThreads;              // group inside the chunk
+          y[c][i] = make_uint4(0u, 0u, 0u, 0u);
+          if (c * kSiluChunkGroups + gl < groups) {
+            float a[8], b[8];
+            Elem<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(st + static_cast<size_t>(gl) * 16), a);
+            Elem<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(st + kSiluChunkBytes + static_cast<size_t>(gl) * 16), b);
+            uint32_t* u = &y[c][i].x;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __nv_bfloat162 hh = __floats2bfloat162_rn(silu_mul_f32(a[2 * j], b[2 * j]), silu_mul_f32(a[2 * j + 1], b[2 * j + 1]));
+              u[j] = *reinterpret_cast<const uint32_t*>(&hh);
+              m2 = __hmax2(m2, __habs2(hh));
+            }
+          }
+        }
+        __syncthreads();                                           // the whole CTA has taken its part of the stage
+        if (threadIdx.x == 0 && q + kSiluStages < total) issue(q + kSiluStages);
+        ++q;
+      }
+    }
+    float amax = fmaxf(__low2float(m2), __high2float(m2));
+    amax = warp_max(amax);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = (threadIdx.x & 31) < kThreads / 32 ? red[threadIdx.x & 31] : 0.0f;
+    amax = warp_max(amax);
+    const float scale = fp8_scale_from_amax(amax);
+    if (threadIdx.x == 0) scales[row] = scale;
+    const float rcp = b200q_rcp_rn(scale);
+    auto emit = [&](auto fast_tag) {
+      constexpr bool kFast = decltype(fast_tag)::value;
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int g = c * kSiluChunkGroups + threadIdx.x + i * kThreads;
+          if (c < nch && g < groups) {
+            float v[8], qv[8];
+            Elem<__nv_bfloat16>::unpack(y[c][i], v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) qv[j] = kFast ? b200q_div_by_shared(v[j], scale, rcp) : __fdiv_rn(v[j], scale);
+            const uint32_t lo = f32x2_to_e4m3x2(qv[0], qv[1]) | (f32x2_to_e4m3x2(qv[2], qv[3]) << 16);
+            const uint32_t hi = f32x2_to_e4m3x2(qv[4], qv[5]) | (f32x2_to_e4m3x2(qv[6], qv[7]) << 16);
+            *reinterpret_cast<uint2*>(codes + row * f + static_cast<int64_t>(g) * 8) = make_uint2(lo, hi);
+          }
+        }
+      }
+    };
+    if (b200q_div_fast_ok(scale)) emit(std::true_type{});
+    else emit(std::false_type{});
+    // `red` is written again only after the next row's chunk barriers
+  }
+}
+
 // out = a + b (bf16, fp32 add)
 __global__ void __launch_bounds__(kThreads)
 add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ out, int64_t n) {
@@ -576,6 +689,25 @@ int b200q_silu_mul_fp8_quantize(const void* gate_up, uint8_t* codes_out, float* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const auto* gp = static_cast<const __nv_bfloat16*>(gate_up);
   const int64_t groups = f >> 3;
+  // many tokens, rows of at least one chunk: persistent CTAs fed through a shared-memory ring
+  if (rows >= 8 * sm_count() && groups >= kSiluChunkGroups) {
+    int* status = gemm::device_status_word();
+    if (status == nullptr) return B200Q_ERR_CUDA;
+    const int nch = static_cast<int>((groups + kSiluChunkGroups - 1) / kSiluChunkGroups);
+    const size_t smem = static_cast<size_t>(kSiluStages) * 2 * kSiluChunkBytes;
+    const dim3 grid(static_cast<unsigned>(2 * sm_count()));
+    const int r32 = static_cast<int>(rows), f32 = static_cast<int>(f);
+#define B200Q_SILUS(C)                                                                                              \
+  do {                                                                                                               \
+    cudaFuncSetAttribute(silu_mul_quant_stream_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    launch_pdl(silu_mul_quant_stream_kernel<C>, grid, dim3(kThreads), smem, st, gp, codes_out, scales_out, r32, f32, status);   \
+  } while (0)
+    if (nch <= 2) B200Q_SILUS(2);
+    else if (nch <= 4) B200Q_SILUS(4);
+    else B200Q_SILUS(8);
+#undef B200Q_SILUS
+    return check_launch();
+  }
   // few tokens: split every row over a cluster so that the launch covers the SMs
   int parts = 1;
   while (parts < 8 && rows * parts < 2 * sm_count() && groups / (parts * 2) >= kThreads / 2) parts *= 2;

@@ -54,7 +54,10 @@ def test_glue_kernels(b200):
     assert torch.equal(out, v)
 
 
-@pytest.mark.parametrize("rows,f", [(1, 16), (33, 528), (64, 3584), (17, 14336), (5, 28672), (3, 32768)])
+# from 8 rows per SM and 4096 columns on: persistent CTAs fed by a ring of 4096-column chunks (1, 2 with a ragged
+# second, 4 ragged, 7 and 8 chunks per row; CTAs that walk 4 and 5 rows)
+@pytest.mark.parametrize("rows,f", [(1, 16), (33, 528), (64, 3584), (17, 14336), (5, 28672), (3, 32768),
+                                    (1184, 4096), (1400, 4112), (1190, 14336), (1200, 28672), (1185, 32768)])
 def test_fused_silu_mul_quantize_is_bit_identical(b200, rows, f):
     """silu(gate) * up + per-token FP8 quantize in one kernel: codes and scales equal those of the
     two separate kernels bit for bit (same bf16 rounding point, same division), and dequantize to
