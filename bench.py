@@ -52,6 +52,9 @@ def main():
     ap.add_argument("--sharded", type=int, default=1,
                     help="tp_stack prefill: 1 = token-sharded residual stream (reduce-scatter + all-gather of FP8 codes), "
                          "0 = all-reduce")
+    ap.add_argument("--attention", choices=["identity", "fp8_sdpa"], default="identity",
+                    help="tp_stack: attention core between the QKV and O linears: the V-slice stand-in of the linear stack "
+                         "(default, the configuration the metric is quoted on) or causal FP8 attention over the 1024-token sequences")
     ap.add_argument("--slabs", type=int, default=1, help="row slabs per row-parallel linear (all-reduce overlap) in tp_stack")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -32,7 +32,8 @@ PARITY_TOL = 2e-2   # rel-L2 of the bf16 stack output against the oracle (bf16 i
 def workload_string(cfg, batch, seq):
     return (f"{cfg.mode} decoder linear stack hidden {cfg.hidden}, {cfg.n_q}q/{cfg.n_kv}kv x {cfg.head_dim}, ffn {cfg.ffn}, "
             f"{cfg.layers} layers; prefill {batch} x {seq} tokens; random-init weights N(0, 0.02); "
-            "attention core = identity on the V slice (kv heads repeated to the query width)")
+            + ("attention core = identity on the V slice (kv heads repeated to the query width)" if cfg.attention == "identity"
+               else "attention core = causal FP8 SDPA per sequence (Q, K, V quantized per tensor)"))
 
 
 def _config(args):
@@ -42,7 +43,10 @@ def _config(args):
     cfg = LLAMA3_70B if tp else LLAMA3_8B
     if getattr(args, "layers", 0):
         cfg = dataclasses.replace(cfg, layers=args.layers)   # shortened stack: profiling runs only
-    return tp, cfg, ((32, 1024) if tp else (8, 2048)), (4 if tp else 3)
+    batch, seq = (32, 1024) if tp else (8, 2048)
+    if getattr(args, "attention", "identity") != "identity":
+        cfg = dataclasses.replace(cfg, attention=args.attention, seq_len=seq)
+    return tp, cfg, (batch, seq), (4 if tp else 3)
 
 
 # ----------------------------------------------------------------------------- parity gate
@@ -148,6 +152,8 @@ def run_reference(args):
     if int(os.environ.get("RANK", "0")) != 0:
         return
     tp, cfg, (batch, seq), seed = _config(args)
+    if cfg.attention != "identity":
+        raise SystemExit("--impl reference times the default attention core (the linear stack the metric is quoted on)")
     tokens = batch * seq
     for _ in range(min(args.warmup, 1)):
         cpu_extrapolated(cfg, seed, tokens)

@@ -56,7 +56,7 @@ __all__ = [
     "pack_e2m1", "unpack_e2m1", "swizzle_scales", "unswizzle_scales", "swizzled_scale_bytes",
     "quantize_op", "dynamic_block_quantize_op",
     "linear_ref", "fp8_linear_ref", "nvfp4_linear_ref", "rel_l2",
-    "all_reduce_ref", "rms_norm_ref", "decoder_layer_ref", "shard_decoder_layer", "fp8_sdpa_ref",
+    "all_reduce_ref", "rms_norm_ref", "decoder_layer_ref", "shard_decoder_layer", "fp8_sdpa_ref", "causal_attention_ref",
 ]
 
 E4M3_MAX = 448.0
@@ -348,14 +348,30 @@ def shard_decoder_layer(layer: dict, rank: int, world: int, n_q: int, n_kv: int,
     }
 
 
+def causal_attention_ref(qkv, n_q: int, n_kv: int, head_dim: int, seq_len: int) -> torch.Tensor:
+    """Attention core of one rank's heads on its QKV output [tokens, (n_q + 2 n_kv) * head_dim] (q heads,
+    then k heads, then v heads; tokens = batch * seq_len, sequence-major): causal FP8 SDPA (`fp8_sdpa_ref`)
+    with each of Q, K, V quantized per tensor at its own abs-max -> [tokens, n_q * head_dim]."""
+    t = qkv.shape[0]
+    if seq_len <= 0 or t % seq_len:
+        raise ValueError(f"{t} tokens are not whole sequences of {seq_len}")
+    b, qw, kvw = t // seq_len, n_q * head_dim, n_kv * head_dim
+    heads = lambda x, n: x.reshape(b, seq_len, n, head_dim).permute(0, 2, 1, 3).contiguous()  # noqa: E731
+    q, k, v = heads(qkv[:, :qw], n_q), heads(qkv[:, qw:qw + kvw], n_kv), heads(qkv[:, qw + kvw:], n_kv)
+    out = fp8_sdpa_ref(q, k, v, q.float().abs().max(), k.float().abs().max(), v.float().abs().max(), is_causal=True)
+    return out.permute(0, 2, 1, 3).reshape(t, qw).contiguous()
+
+
 def decoder_layer_ref(h, layer: dict, n_q: int, n_kv: int, head_dim: int, mode: str,
-                      world: int = 1) -> torch.Tensor:
+                      world: int = 1, attention: str = "identity", seq_len: int = 0) -> torch.Tensor:
     """One decoder layer of the linear stack, evaluated as `world` tensor-parallel ranks
     whose row-parallel partial outputs are summed (world=1: the plain layer).
 
-    h -> RMSNorm -> QKV linear -> "attention" = identity on the V slice, each kv head
-    repeated n_q/n_kv times to the q width -> O linear (+ all-reduce) -> residual ->
+    h -> RMSNorm -> QKV linear -> attention core -> O linear (+ all-reduce) -> residual ->
     RMSNorm -> gate/up linear -> silu(gate)*up -> down linear (+ all-reduce) -> residual.
+    Attention core: "identity" = the V slice, each kv head repeated n_q/n_kv times to the q width
+    (the linear-stack stand-in); "fp8_sdpa" = causal FP8 attention over sequences of `seq_len`
+    tokens (h is then [tokens, hidden], sequence-major), every rank on its own heads.
     Each rank quantizes its own activation slice (per-token amax over the local slice for
     FP8; a per-rank tensor amax for NVFP4)."""
     rep = n_q // n_kv
@@ -366,9 +382,12 @@ def decoder_layer_ref(h, layer: dict, n_q: int, n_kv: int, head_dim: int, mode: 
         sh = shard_decoder_layer(layer, r, world, n_q, n_kv, head_dim)
         qkv = _qlinear(x, sh["wqkv"], mode).to(dt)
         kvw = (n_kv // world) * head_dim
-        v = qkv[..., -kvw:]
-        attn = v.reshape(*v.shape[:-1], n_kv // world, 1, head_dim).expand(
-            *v.shape[:-1], n_kv // world, rep, head_dim).reshape(*v.shape[:-1], -1)
+        if attention == "fp8_sdpa":
+            attn = causal_attention_ref(qkv, n_q // world, n_kv // world, head_dim, seq_len)
+        else:
+            v = qkv[..., -kvw:]
+            attn = v.reshape(*v.shape[:-1], n_kv // world, 1, head_dim).expand(
+                *v.shape[:-1], n_kv // world, rep, head_dim).reshape(*v.shape[:-1], -1)
         parts.append(_qlinear(attn.contiguous(), sh["wo"], mode).to(dt))
     h = h + all_reduce_ref(parts, dt)
     x = rms_norm_ref(h, layer["norm2"])

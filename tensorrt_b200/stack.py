@@ -42,6 +42,11 @@ class StackConfig:
     layers: int
     mode: str = "fp8"          # "fp8" (per-token activations x per-channel weights) or "nvfp4" (W4A4)
     eps: float = 1e-5
+    # attention core between the QKV and O linears: "identity" = the V slice with every kv head repeated to the
+    # query width (the linear-stack stand-in); "fp8_sdpa" = causal FP8 attention (Q, K, V quantized per tensor,
+    # softmax output quantized at scale 1/448) over sequences of `seq_len` tokens, tokens sequence-major
+    attention: str = "identity"
+    seq_len: int = 0
 
     @property
     def q_width(self):
@@ -56,6 +61,10 @@ class StackConfig:
             raise ValueError(f"mode must be 'fp8' or 'nvfp4', got {self.mode!r}")
         if self.n_q % self.n_kv:
             raise ValueError("n_q must be a multiple of n_kv")
+        if self.attention not in ("identity", "fp8_sdpa"):
+            raise ValueError(f"attention must be 'identity' or 'fp8_sdpa', got {self.attention!r}")
+        if self.attention == "fp8_sdpa" and (self.seq_len <= 0 or self.head_dim % 16 or self.head_dim > 128):
+            raise ValueError("attention='fp8_sdpa' needs seq_len > 0 and a head dimension that is a multiple of 16 up to 128")
         if self.n_q % world or self.n_kv % world or self.ffn % world:
             raise ValueError(f"heads ({self.n_q}/{self.n_kv}) and ffn ({self.ffn}) must divide by the TP size {world}")
 
@@ -131,6 +140,18 @@ class CudaBackend:
         h_new = h if delta is None else capi.add(h, delta)
         x = capi.rms_norm(h_new, weight, eps)
         return h_new, self.quantize(x, amax)
+
+    def causal_attention(self, qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, seq_len: int) -> torch.Tensor:
+        """qkv [tokens, (n_q + 2 n_kv) * head_dim] of whole sequences -> causal FP8 attention output
+        [tokens, n_q * head_dim]; Q, K, V quantized per tensor at their measured abs-max."""
+        t = qkv.shape[0]
+        if seq_len <= 0 or t % seq_len:
+            raise ValueError(f"{t} tokens are not whole sequences of {seq_len}")
+        b, qw, kvw = t // seq_len, n_q * head_dim, n_kv * head_dim
+        heads = lambda x, n: x.reshape(b, seq_len, n, head_dim).permute(0, 2, 1, 3).contiguous()  # noqa: E731
+        q, k, v = heads(qkv[:, :qw], n_q), heads(qkv[:, qw:qw + kvw], n_kv), heads(qkv[:, qw + kvw:], n_kv)
+        out = capi.fp8_sdpa(q, k, v, capi.amax(q), capi.amax(k), capi.amax(v), True)
+        return out.permute(0, 2, 1, 3).reshape(t, qw)
 
     def measure_norm_amax(self, h, delta, weight, eps):
         if self.mode != "nvfp4":
@@ -269,6 +290,16 @@ class DecoderLayer:
                 self.amax[name] = m if name not in self.amax else torch.maximum(self.amax[name], m)
         return self.amax.get(name)
 
+    def _attention(self, qkv: torch.Tensor) -> torch.Tensor:
+        """Attention core on this rank's heads: qkv [T, (q + 2 kv) / W] -> [T, q / W]."""
+        cfg, be, w = self.cfg, self.backend, self.world
+        if cfg.attention == "fp8_sdpa" and qkv.shape[0] % cfg.seq_len == 0:
+            return be.causal_attention(qkv, cfg.n_q // w, cfg.n_kv // w, cfg.head_dim, cfg.seq_len)
+        if cfg.attention == "fp8_sdpa" and qkv.shape[0] >= cfg.seq_len:
+            raise ValueError(f"{qkv.shape[0]} tokens are not whole sequences of {cfg.seq_len}")
+        # fewer tokens than a sequence (a decode step has no key cache here) and the linear-stack form
+        return be.expand_heads(qkv, (cfg.q_width + cfg.kv_width) // w, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
+
     def _ffn_act(self, xq):
         """gate/up linear + silu(gate) * up -> input of the down projection (quantized when the
         backend fuses the quantize, else bf16)."""
@@ -284,8 +315,7 @@ class DecoderLayer:
         cfg, be, w = self.cfg, self.backend, self.world
         h, xq = be.add_norm_quantize(h, delta, self.norm1, cfg.eps, self._norm_amax("qkv", h, delta, self.norm1))
         qkv = be.matmul(xq, self.wqkv)                                   # [T, (q + 2 kv) / W]
-        q_local, kv_local = cfg.q_width // w, cfg.kv_width // w
-        attn = be.expand_heads(qkv, q_local + kv_local, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
+        attn = self._attention(qkv)
         delta = self.row_parallel(attn, self.wo, self._amax("o", attn))
         h, xq = be.add_norm_quantize(h, delta, self.norm2, cfg.eps, self._norm_amax("gate_up", h, delta, self.norm2))
         act = self._ffn_act(xq)
@@ -301,8 +331,7 @@ class DecoderLayer:
             raise ValueError("the token-sharded residual stream is implemented for FP8 stacks")
         h, xq = be.add_norm_quantize(h, delta, self.norm1, cfg.eps)
         qkv = be.matmul(comm.all_gather_quantized(xq), self.wqkv)
-        q_local, kv_local = cfg.q_width // w, cfg.kv_width // w
-        attn = be.expand_heads(qkv, q_local + kv_local, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
+        attn = self._attention(qkv)
         delta = comm.reduce_scatter(be.linear(attn, self.wo))
         h, xq = be.add_norm_quantize(h, delta, self.norm2, cfg.eps)
         act = self._ffn_act(comm.all_gather_quantized(xq))
@@ -317,8 +346,7 @@ class DecoderLayer:
         the gathered quantized input of the next layer, or (next_norm None) the full bf16 output."""
         cfg, be, w = self.cfg, self.backend, self.world
         qkv = be.matmul(xq, self.wqkv)
-        q_local, kv_local = cfg.q_width // w, cfg.kv_width // w
-        attn = be.expand_heads(qkv, q_local + kv_local, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
+        attn = self._attention(qkv)
         rp.partials_to_owners(attn, self.wo)
         xq = rp.reduce_norm_quantize(h, self.norm2, cfg.eps)
         rp.partials_to_owners(self._ffn_act(xq), self.wdown)

@@ -148,6 +148,32 @@ def test_stack_matches_oracle_single_gpu(b200, mode):
     assert o.rel_l2(y.float().cpu(), ref.float()) < (2e-2 if mode == "fp8" else 6e-2)
 
 
+def test_stack_with_fp8_attention_matches_oracle(b200):
+    """Attention core = causal FP8 SDPA (b200q_fp8_sdpa on Q, K, V quantized per tensor) instead of the
+    identity stand-in: 3 sequences of 128 tokens through 2 layers against the oracle's layer with the
+    same attention core; a 5-token forward (a decode step: no key cache here) takes the stand-in."""
+    from tensorrt_b200.stack import DecoderStack, StackConfig
+
+    cfg = StackConfig(hidden=512, n_q=8, n_kv=2, head_dim=64, ffn=1024, layers=2, mode="fp8", attention="fp8_sdpa", seq_len=128)
+    ws = _weights(cfg, 9)
+    g = torch.Generator().manual_seed(71)
+    h = torch.randn(3 * 128, cfg.hidden, generator=g).bfloat16()
+    stack = DecoderStack(cfg, _to(ws, "cuda"))
+    y = stack(h.cuda())
+    torch.cuda.synchronize()
+    assert b200.capi.device_status() == 0
+    ref, ref_id = h, h
+    for w in ws:
+        ref = o.decoder_layer_ref(ref, w, cfg.n_q, cfg.n_kv, cfg.head_dim, "fp8", attention="fp8_sdpa", seq_len=128)
+        ref_id = o.decoder_layer_ref(ref_id, w, cfg.n_q, cfg.n_kv, cfg.head_dim, "fp8")
+    err = o.rel_l2(y.float().cpu(), ref.float())
+    assert err < 2e-2, err
+    assert o.rel_l2(ref_id.float(), ref.float()) > 10 * err          # the two attention cores are far apart
+    assert stack(h[:5].cuda()).shape == (5, cfg.hidden)
+    with pytest.raises(ValueError):
+        stack(h[:200].cuda())                                        # 200 tokens are not whole sequences of 128
+
+
 def _tp_worker(rank, world, store_path, out_path, slabs, fused, micro, sharded):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist

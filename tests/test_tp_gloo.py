@@ -41,6 +41,9 @@ class OracleBackend:
     def rms_norm(self, x, w, eps):
         return self.o.rms_norm_ref(x, w, eps)
 
+    def causal_attention(self, qkv, n_q, n_kv, head_dim, seq_len):
+        return self.o.causal_attention_ref(qkv, n_q, n_kv, head_dim, seq_len)
+
     def silu_mul(self, gu):
         f = gu.shape[-1] // 2
         return (torch.nn.functional.silu(gu[..., :f].float()) * gu[..., f:].float()).to(gu.dtype)
@@ -131,6 +134,24 @@ def _worker_stack(rank, world, store_path, mode, out_path):
             raise AssertionError("ragged token count not rejected")
         # sharded=True asks for the fused peer-memory kernels; without them (CPU) it is the all-reduce form
         assert torch.equal(stack.forward(h, sharded=True), ref_tp)
+        # causal FP8 attention as the attention core (2 sequences of 8 tokens), every rank on its own heads
+        from dataclasses import replace
+
+        cfg_a = replace(cfg, attention="fp8_sdpa", seq_len=8)
+        stack_a = DecoderStack(cfg_a, weights, backend=OracleBackend(mode), rank=rank, world=world)
+        ref_a = h.reshape(-1, cfg.hidden)
+        for w in weights:
+            ref_a = o.decoder_layer_ref(ref_a, w, cfg.n_q, cfg.n_kv, cfg.head_dim, mode, world=world, attention="fp8_sdpa", seq_len=8)
+        for form in (False, "collectives"):
+            assert torch.equal(stack_a.forward(h, sharded=form).reshape(-1, cfg.hidden), ref_a)
+        assert not torch.equal(ref_a, ref_tp.reshape(-1, cfg.hidden))
+        try:
+            DecoderStack(replace(cfg, attention="fp8_sdpa", seq_len=5), weights, backend=OracleBackend(mode), rank=rank,
+                         world=world).forward(h)
+        except ValueError as e:
+            assert "whole sequences" in str(e)
+        else:
+            raise AssertionError("16 tokens are not whole sequences of 5")
     if rank == 0:
         torch.save(y, out_path)
     dist.barrier()
