@@ -50,7 +50,7 @@ const char* b200q_status_string(int status);
  * it on the device for dynamic quantization.
  *
  * b200q_amax: max(|x|) over n elements -> amax_out[0].  Needs a workspace of
- * b200q_amax_workspace_bytes() bytes (per-block partial maxima and a ticket counter);
+ * b200q_amax_workspace_bytes() bytes (a ticket counter and the running maximum of the CTAs);
  * the workspace must be zero the first time it is used and is left zero again on return,
  * so one memset at allocation is enough.  Calls sharing a workspace must not overlap.
  * b200q_row_amax: max(|x|) per row -> amax_out[rows].
@@ -66,7 +66,7 @@ int b200q_row_amax(const void* x, int dtype, int64_t rows, int64_t cols, float* 
  * must not allocate device memory at the point where they call it: a TensorRT plugin's
  * enqueue() only gets the workspace TensorRT sized at build time, a stream being captured
  * into a CUDA graph rejects cudaMalloc, and a serving process may have handed all device
- * memory to its own pool.  The per-CTA partial maxima and the ticket counter live in a
+ * memory to its own pool.  The ticket counter and the running maximum of the CTAs live in a
  * 4352-byte array compiled into the library (every GPU that loads the library holds it
  * until the process exits), so nothing is allocated or freed here, by this library or by
  * any library it calls.
@@ -77,7 +77,7 @@ int b200q_row_amax(const void* x, int dtype, int64_t rows, int64_t cols, float* 
  *   - All calls on a device share the one array: calls that can overlap on the GPU (two
  *     streams, two host threads) race with each other and give wrong results; serialise
  *     them or use b200q_amax with separate workspaces.
- *   - The ticket counter in the array is re-armed by the last CTA of every launch.  A launch that
+ *   - The ticket counter and the running maximum in the array are re-armed by the last CTA of every launch.  A launch that
  *     dies part-way (a fault elsewhere in the context) can leave it non-zero, and since the caller
  *     cannot reach the array to clear it, later calls on that device then return wrong maxima:
  *     after a failed launch treat the context as lost, as for any other sticky CUDA error.

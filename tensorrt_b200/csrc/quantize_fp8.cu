@@ -202,8 +202,8 @@ fp8_dequant_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ 
 constexpr int kAmaxBlocks = 148 * 8;
 constexpr int kAmaxThreads = 256;
 
-// Single-pass tensor abs-max.  Every CTA writes its partial maximum to `partials`, takes a
-// ticket; the last CTA to arrive reduces the partials, writes the result and re-arms the
+// Single-pass tensor abs-max.  Every CTA folds its maximum into one running word (atomicMax on the
+// bit pattern) and takes a ticket; the CTA that draws the last ticket writes the result and re-arms the
 // ticket counter (so the workspace is zero again when the kernel ends).
 // Running abs-max over 32-byte chunks as they come from memory.  16-bit types stay packed: the
 // maximum of absolute values is exact in the input format, so two elements cost one instruction.
@@ -246,7 +246,8 @@ __global__ void __launch_bounds__(kAmaxThreads)
 amax_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ out, float* __restrict__ partials,
             unsigned int* __restrict__ ticket, bool wide) {
   __shared__ float red[kAmaxThreads / 32];
-  __shared__ bool last;
+  pdl_launch_dependents();   // no-ops unless launched with the programmatic-serialization attribute
+  pdl_wait();
   float local = 0.0f;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -281,20 +282,16 @@ amax_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ out, float* 
     for (int64_t i = (groups << 3) + threadIdx.x; i < n; i += blockDim.x) local = fmaxf(local, fabsf(static_cast<float>(x[i])));
   }
   const float m = block_max<kAmaxThreads>(local, red);
+  // CTA maxima meet in one word next to the ticket: values are >= 0 and never NaN here, so their bit patterns
+  // order like unsigned integers.  The CTA that draws the last ticket hands the result out and re-arms both words.
   if (threadIdx.x == 0) {
-    partials[blockIdx.x] = m;
+    unsigned int* running = ticket + 1;
+    atomicMax(running, __float_as_uint(m));
     __threadfence();
     const unsigned int t = atomicAdd(ticket, 1u);
-    last = (t == gridDim.x - 1);
-  }
-  __syncthreads();
-  if (last) {
-    __threadfence();
-    float r = 0.0f;
-    for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) r = fmaxf(r, __ldcg(partials + i));
-    r = block_max<kAmaxThreads>(r, red);
-    if (threadIdx.x == 0) {
-      out[0] = r;
+    if (t == gridDim.x - 1) {
+      __threadfence();
+      out[0] = __uint_as_float(atomicExch(running, 0u));
       *ticket = 0u;
     }
   }
@@ -327,15 +324,18 @@ int launch_amax(const void* x, int dtype, int64_t n, float* out, float* partials
   // one CTA per kAmaxThreads x 4 chunks of 32 bytes (16 bytes without the alignment), up to 8 CTAs per SM
   int blocks = static_cast<int>((n >> 3) / (kAmaxThreads * (wide ? 8 : 1)));
   blocks = blocks < 1 ? 1 : (blocks > kAmaxBlocks ? kAmaxBlocks : blocks);
+  // launched with the programmatic-serialization attribute: back-to-back launches overlap the next one's
+  // start-up with this one's tail (the kernel waits for its predecessor before its first load)
+  const dim3 grid(static_cast<unsigned>(blocks)), block(kAmaxThreads);
   switch (dtype) {
     case B200Q_BF16:
-      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), n, out, partials, ticket, wide);
+      launch_pdl(amax_kernel<__nv_bfloat16>, grid, block, 0, st, static_cast<const __nv_bfloat16*>(x), n, out, partials, ticket, wide);
       break;
     case B200Q_F16:
-      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const __half*>(x), n, out, partials, ticket, wide);
+      launch_pdl(amax_kernel<__half>, grid, block, 0, st, static_cast<const __half*>(x), n, out, partials, ticket, wide);
       break;
     case B200Q_F32:
-      amax_kernel<<<blocks, kAmaxThreads, 0, st>>>(static_cast<const float*>(x), n, out, partials, ticket, wide);
+      launch_pdl(amax_kernel<float>, grid, block, 0, st, static_cast<const float*>(x), n, out, partials, ticket, wide);
       break;
     default:
       return B200Q_ERR_INVALID;
@@ -344,9 +344,8 @@ int launch_amax(const void* x, int dtype, int64_t n, float* out, float* partials
 }
 
 // ---------------------------------------------------------------- abs-max without a caller workspace
-// Scratch of b200q_amax_static: the ticket counter lives in the first 256 bytes, one partial
-// maximum per CTA follows.  Zero at module load; the kernel re-arms the ticket when it ends
-// and every partial that is read was written by the same launch.
+// Scratch of b200q_amax_static: the ticket counter and the running maximum live in the first 256
+// bytes (the rest is spare).  Zero at module load; the kernel re-arms both words when it ends.
 constexpr int kStaticAmaxMaxBlocks = 1024;
 constexpr int64_t kStaticAmaxElemsPerBlock = 1 << 18;
 static __device__ __align__(256) unsigned char g_amax_static_scratch[256 + kStaticAmaxMaxBlocks * sizeof(float)];
