@@ -114,6 +114,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   uint64_t* acc_full = empty_bar + kSmallMaxStages;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tail + 256);
   volatile int* failed = reinterpret_cast<volatile int*>(tail + 260);
+  uint64_t* sft_full = reinterpret_cast<uint64_t*>(tail + 384);   // NVFP4: a stage's scales are in tensor memory (4 warps)
   float* wscale = reinterpret_cast<float*>(tail + 512);   // [128] dequantization scale of each weight row
   float* wbias = wscale + 128;                            // [128]
   float* xscale = wbias + 128;                            // [128] dequantization scale of each token
@@ -131,6 +132,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(full_bar + s, 1);
       ptx::mbar_init(empty_bar + s, 1);
+      ptx::mbar_init(sft_full + s, 4);
     }
     ptx::mbar_init(acc_full, 1);
     *failed = 0;
@@ -215,11 +217,15 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       int kblocks = 4;
       if constexpr (NVF4) {
         kblocks = min(4, p.sf_col_tiles - kt * 4);
-        const uint32_t sfw_lo = ptx::desc_lo_sf(sw + C::kWBytes + x_bytes), sfx_lo = sfw_lo + (2048 >> 4);
-        for (int kb = 0; kb < kblocks; ++kb) {
-          ptx::tmem_cp_sf<1>(tmem_sfw + kb * 4, ptx::desc_join(sfw_lo + kb * 32, ptx::kDescHiSf));
-          ptx::tmem_cp_sf<1>(tmem_sfx + kb * 4, ptx::desc_join(sfx_lo + kb * 32, ptx::kDescHiSf));
+        // the stage's block scales are put into tensor memory by warps 2-5 (tcgen05.st from registers): a
+        // tcgen05.cp costs about 50 tensor-pipe clocks and does not overlap MMAs, and a stage would need 8
+        if (!ptx::mbar_wait(sft_full + stage, phase)) {
+          raise_timeout(p.status, 34);
+          *failed = 1;
+          ok = false;
+          break;
         }
+        ptx::tc_fence_after();
       }
       for (int kb = 0; kb < kblocks; ++kb) {
         const uint32_t accum = (kt > kt0 || kb > 0) ? 1u : 0u;
@@ -254,6 +260,39 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       wscale[wrow] = ws;
       wbias[wrow] = wb;
       xscale[wrow] = xs;
+    }
+    if constexpr (NVF4) {
+      // main loop: shared memory -> tensor memory for the scale tiles of every stage.  Lane l of each
+      // lane quarter holds, per 512-byte scale tile, the 16 bytes at offset 16 l (4 columns): the layout
+      // the block-scaled MMA reads, replicated in the four quarters.
+      const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kt = kt0; kt < kt1; ++kt) {
+        if (!ptx::mbar_wait(full_bar + stage, phase)) {
+          raise_timeout(p.status, 33);
+          *failed = 1;
+          break;
+        }
+        const uint8_t* sfw = smem + stage * stage_bytes + C::kWBytes + x_bytes + lane * 16;
+        const uint8_t* sfx = sfw + 2048;
+        uint32_t rw[16], rx[16];
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+          const uint4 a = *reinterpret_cast<const uint4*>(sfw + kb * 512);
+          const uint4 b = *reinterpret_cast<const uint4*>(sfx + kb * 512);
+          rw[kb * 4 + 0] = a.x, rw[kb * 4 + 1] = a.y, rw[kb * 4 + 2] = a.z, rw[kb * 4 + 3] = a.w;
+          rx[kb * 4 + 0] = b.x, rx[kb * 4 + 1] = b.y, rx[kb * 4 + 2] = b.z, rx[kb * 4 + 3] = b.w;
+        }
+        const uint32_t dst = tmem_base + 128 + stage * C::kSfCols + lane_base;
+        ptx::tmem_st_32x32_x16(dst, rw);
+        ptx::tmem_st_32x32_x16(dst + 16, rx);
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(sft_full + stage);
+        if (++stage == stages) stage = 0, phase ^= 1u;
+      }
     }
     float* partial = reinterpret_cast<float*>(smem);     // [token][128 weight rows]: lanes hit consecutive banks
     const bool have = kt1 > kt0;
