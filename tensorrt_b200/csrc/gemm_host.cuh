@@ -248,9 +248,11 @@ int launch_smallm(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st,
 // Cluster size of the small-M kernel.  Measured: one SM pulls about 60 bytes per nanosecond
 // through TMA whatever the ring depth, so about 110 streaming SMs are needed to saturate HBM;
 // the smallest power of two that reaches that many CTAs wins, larger clusters only add
-// reduction cost.
-inline int smallm_splits(int n_tiles, int k_tiles, int sms) {
-  const int want = (sms * 3) / 4;
+// reduction cost.  With at most 32 tokens the partial tiles are small enough that two CTAs per SM
+// pay (one's prologue and cluster reduction under the other's weight stream: 10-25 % faster at
+// 16 tokens, neutral at 64, slower at 128), so the target there is one and a half CTAs per SM.
+inline int smallm_splits(int n_tiles, int k_tiles, int sms, int tokens) {
+  const int want = tokens <= 32 ? (sms * 3) / 2 : (sms * 3) / 4;
   int s = 1;
   while (s < 8 && n_tiles * s < want && s * 2 <= k_tiles) s <<= 1;
   return s;
@@ -277,7 +279,7 @@ int launch(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, const 
     // (1001 / 1002 / 1004 / 1008 force 1 / 2 / 4 / 8 CTAs per tile)
     int splits = 0;
     if (bn == 1001 || bn == 1002 || bn == 1004 || bn == 1008) splits = bn - 1000;
-    else if (bn == 0) splits = smallm_splits((p.N + kSmallWRows - 1) / kSmallWRows, k_tiles, sm_count());
+    else if (bn == 0) splits = smallm_splits((p.N + kSmallWRows - 1) / kSmallWRows, k_tiles, sm_count(), p.M);
     if (splits >= 1 && splits <= k_tiles) return launch_smallm<NVF4>(a, b, p, st, splits, forced_smallm_stages());
   }
   if (bn >= 1000) bn = 0;
