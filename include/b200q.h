@@ -184,6 +184,17 @@ int b200q_fp8_gemm(const uint8_t* a_codes, const float* a_scales, int64_t a_scal
                    const uint8_t* b_codes, const float* b_scales, int64_t b_scales_numel,
                    const void* bias, void* out, int64_t M, int64_t N, int64_t K,
                    b200q_stream_t stream, const b200q_cfg* cfg);
+
+/* b200q_fp8_gemm with the gate/up activation fused into its epilogue (producer fusion):
+ * b holds F gate rows followed by F up rows (N = 2 F, F a multiple of 128; scales and bias indexed the
+ * same way), out is [M, F] bf16 = silu(g) * u with g, u the two linear outputs rounded to bf16 first,
+ * i.e. the same bits as b200q_fp8_gemm followed by b200q_silu_mul, without the [M, 2 F] round trip
+ * through memory.  Replaces linear + silu + mul of a gated MLP (the graph the reference lowers
+ * tools/llm models to; aten_ops_converters.py linear / silu / mul converters).  cfg: tile_n must be 0. */
+int b200q_fp8_gemm_silu_mul(const uint8_t* a_codes, const float* a_scales, int64_t a_scales_numel,
+                            const uint8_t* b_codes, const float* b_scales, int64_t b_scales_numel,
+                            const void* bias, void* out, int64_t M, int64_t N, int64_t K,
+                            b200q_stream_t stream, const b200q_cfg* cfg);
 int b200q_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_scales, const float* a_global,
                      const uint8_t* b_codes, const uint8_t* b_scales, const float* b_global,
                      const void* bias, void* out, int64_t M, int64_t N, int64_t K,

@@ -217,6 +217,27 @@ def fp8_gemm(a_codes, a_scales, b_codes, b_scales, bias=None, tile_n=None, stati
     return out
 
 
+def fp8_gemm_silu_mul(a_codes, a_scales, b_codes, b_scales, bias=None, out=None) -> torch.Tensor:
+    """Gate/up linear with the activation in the GEMM epilogue: b [2F, K] = F gate rows then F up rows
+    (F a multiple of 128) -> bf16 [.., F] = silu(g) * u, the same bits as `silu_mul(fp8_gemm(..))`."""
+    _need_cuda(a_codes, a_scales, b_codes, b_scales, bias)
+    a_codes, b_codes = a_codes.contiguous(), b_codes.contiguous()
+    k = a_codes.shape[-1]
+    m = a_codes.numel() // max(k, 1)
+    n = b_codes.shape[0]
+    if b_codes.dim() != 2 or b_codes.shape[1] != k or n % 256:
+        raise ValueError(f"b must be [2F, {k}] with F a multiple of 128, got {tuple(b_codes.shape)}")
+    a_scales, b_scales = a_scales.float().contiguous(), b_scales.float().contiguous()
+    if bias is not None:
+        bias = bias.to(torch.bfloat16).contiguous()
+    out = _gemm_out(out, tuple(a_codes.shape[:-1]) + (n // 2,), a_codes.device)
+    with torch.cuda.device(a_codes.device):
+        check(load().b200q_fp8_gemm_silu_mul(a_codes.data_ptr(), a_scales.data_ptr(), a_scales.numel(), b_codes.data_ptr(),
+                                             b_scales.data_ptr(), b_scales.numel(), _ptr(bias), out.data_ptr(), m, n, k,
+                                             _stream(a_codes), None), "b200q_fp8_gemm_silu_mul")
+    return out
+
+
 def nvfp4_gemm(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias=None, tile_n=None, static_weights=None,
                out=None) -> torch.Tensor:
     _need_cuda(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias)

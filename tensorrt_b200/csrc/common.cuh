@@ -228,6 +228,11 @@ __device__ __forceinline__ float block_sum(float v, float* smem) {
   return r;
 }
 
+// silu(a) * b = a / (1 + exp(-a)) * b with the hardware exponential and reciprocal (a few ulp in fp32,
+// below the bf16 rounding that follows).  Every kernel that applies the activation uses exactly this
+// expression, so the fused and the separate forms give the same bits.
+__device__ __forceinline__ float silu_mul_f32(float a, float b) { return __fdividef(a, 1.0f + __expf(-a)) * b; }
+
 // fp8 scale from amax: amax / 448, zero -> 1 (true division, as the CPU restatement).
 __device__ __forceinline__ float fp8_scale_from_amax(float amax) {
   float s = __fdiv_rn(amax, kE4M3Max);

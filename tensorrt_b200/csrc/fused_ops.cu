@@ -313,10 +313,6 @@ add_norm_quant_stream_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfl
   }
 }
 
-// silu(a) * b = a / (1 + exp(-a)) * b with the hardware exponential and reciprocal (a few ulp in fp32,
-// below the bf16 rounding that follows); both kernels below use exactly this expression.
-__device__ __forceinline__ float silu_mul_f32(float a, float b) { return __fdividef(a, 1.0f + __expf(-a)) * b; }
-
 // act[t, j] = silu(gu[t, j]) * gu[t, F + j], gu is [T, 2F] (gate columns first)
 __global__ void __launch_bounds__(kThreads)
 silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int64_t rows, int64_t f) {

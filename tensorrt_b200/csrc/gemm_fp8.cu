@@ -101,6 +101,34 @@ int b200q_fp8_gemm(const uint8_t* a_codes, const float* a_scales, int64_t a_scal
   return gemm::launch<false>(a_codes, b_codes, p, static_cast<cudaStream_t>(stream), cfg);
 }
 
+int b200q_fp8_gemm_silu_mul(const uint8_t* a_codes, const float* a_scales, int64_t a_scales_numel, const uint8_t* b_codes,
+                            const float* b_scales, int64_t b_scales_numel, const void* bias, void* out, int64_t M, int64_t N,
+                            int64_t K, b200q_stream_t stream, const b200q_cfg* cfg) {
+  if (a_codes == nullptr || b_codes == nullptr || a_scales == nullptr || b_scales == nullptr || out == nullptr)
+    return B200Q_ERR_INVALID;
+  if (cfg != nullptr && (cfg->tile_n != 0 || cfg->reserved != 0)) return B200Q_ERR_INVALID;   // one kernel serves this entry
+  if (M < 0 || N < 0 || K <= 0 || M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200Q_ERR_INVALID;
+  if (K % 16 != 0 || N % 256 != 0) return B200Q_ERR_INVALID;                                   // F = N / 2 in whole 128-column tiles
+  if ((a_scales_numel != 1 && a_scales_numel != M) || (b_scales_numel != 1 && b_scales_numel != N)) return B200Q_ERR_INVALID;
+  if (!aligned(a_codes, 16) || !aligned(b_codes, 16) || !aligned(out, 16)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  if (M == 0 || N == 0) return B200Q_OK;
+  gemm::Params p{};
+  p.a_scales = a_scales;
+  p.b_scales = b_scales;
+  p.a_scale_stride = a_scales_numel == 1 ? 0 : 1;
+  p.b_scale_stride = b_scales_numel == 1 ? 0 : 1;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.k_bytes = static_cast<int>(K);
+  p.silu_f = static_cast<int>(N / 2);
+  p.status = gemm::device_status_word();
+  if (p.status == nullptr) return B200Q_ERR_CUDA;
+  return gemm::launch_pair<false, true>(a_codes, b_codes, p, static_cast<cudaStream_t>(stream));
+}
+
 static int fill_rs(gemm::Params& p, gemm::RsTargets& rs, const b200q_peers* peers, int64_t M) {
   if (peers == nullptr || peers->world < 2 || peers->world > 8 || peers->rank < 0 || peers->rank >= peers->world) return B200Q_ERR_INVALID;
   if (M % (static_cast<int64_t>(peers->world) * 128) != 0) return B200Q_ERR_INVALID;

@@ -108,14 +108,14 @@ inline int make_scale_map(CUtensorMap* map, const void* base, int64_t row_tiles,
 }
 
 // CTA-pair kernel: clusters of two CTAs, one cluster per 256 x 256 output tile.
-template <bool NVF4>
+template <bool NVF4, bool SILU = false>
 int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, const RsTargets* rs = nullptr) {
   using C = Cfg2<NVF4>;
   static bool configured[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200Q_ERR_CUDA;
   if (!configured[dev]) {
-    if (cudaFuncSetAttribute(gemm_pair_kernel<NVF4>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_pair_kernel<NVF4, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
       return B200Q_ERR_CUDA;
     configured[dev] = true;
   }
@@ -123,7 +123,14 @@ int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, c
   OutMaps tout = {};
   if (int rc = make_operand_map(&ta, a, p.M, p.k_bytes, 128)) return rc;
   if (int rc = make_operand_map(&tb, b, p.N, p.k_bytes, kPairN / 2)) return rc;
-  if (int rc = build_out_maps(&tout, p, rs)) return rc;
+  if constexpr (SILU) {
+    // out is [M, F]: TMA stores only (F is a multiple of 128)
+    p.tma_store = 1;
+    if (rs != nullptr || p.rs_world > 1) return B200Q_ERR_INVALID;
+    if (int rc = make_output_map(&tout.m[0], p.out, p.M, p.silu_f)) return rc;
+  } else {
+    if (int rc = build_out_maps(&tout, p, rs)) return rc;
+  }
   if constexpr (NVF4) {
     if (int rc = make_scale_map(&tsfa, p.sfa, (p.M + 127) / 128, p.sf_col_tiles, 1)) return rc;
     if (int rc = make_scale_map(&tsfb, p.sfb, (p.N + 127) / 128, p.sf_col_tiles, 2)) return rc;
@@ -131,7 +138,7 @@ int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, c
     tsfa = ta;
     tsfb = ta;
   }
-  const int tiles = ((p.M + kPairM - 1) / kPairM) * ((p.N + kPairN - 1) / kPairN);
+  const int tiles = ((p.M + kPairM - 1) / kPairM) * (SILU ? (p.silu_f + kPairN / 2 - 1) / (kPairN / 2) : (p.N + kPairN - 1) / kPairN);
   const int max_pairs = sm_count() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   cudaLaunchConfig_t cfg = {};
@@ -146,7 +153,7 @@ int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, c
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemm_pair_kernel<NVF4>, ta, tb, tout, tsfa, tsfb, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, gemm_pair_kernel<NVF4, SILU>, ta, tb, tout, tsfa, tsfb, p) != cudaSuccess) {
     cudaGetLastError();
     return B200Q_ERR_CUDA;
   }

@@ -90,6 +90,8 @@ struct Params {
   int static_weights;      // small-M kernel under programmatic dependent launch: 1 = B (weights, their scales, bias) was
                            // written before the preceding kernel on the stream started, so it may be read before
                            // waiting for that kernel; 0 = wait first
+  int silu_f;              // FP8 CTA-pair kernel, > 0: B holds F gate rows then F up rows (N = 2 F); the epilogue
+                           // writes out[M, F] = silu(gate) * up, each linear output rounded to bf16 first
   int sf_copier;           // NVFP4, 1-CTA kernel: 1 = a dedicated warp (warp 6 of 224 threads) issues the tcgen05.cp scale copies
   int* status;             // device status word (0 = ok)
 };
@@ -183,6 +185,56 @@ __device__ __forceinline__ void epilogue_tile(uint32_t taddr, float rscale, cons
       if (++sbuf == EPI_BUFS) sbuf = 0;
     } else if (row < M) {
       epilogue_store_direct(orow + (c + 1) * 32, w, n0 + (c + 1) * 32, N, vec_ok);
+    }
+  }
+}
+
+// Epilogue of one 128 x 256 accumulator slice whose columns 0..127 are gate outputs and 128..255 the
+// matching up outputs: both are scaled, biased and rounded to bf16 exactly as the plain epilogue does,
+// then silu(gate) * up leaves as 64-column panels of the [M, F] activation (TMA stores only).
+template <int EPI_BUFS, int PANEL_BYTES, typename Release>
+__device__ __forceinline__ void epilogue_tile_silu(uint32_t taddr, float rscale, const float* colscale, const float* colbias,
+                                                   uint8_t* warp_panels, int& sbuf, const CUtensorMap* tmap_out, int store_y, int row0,
+                                                   int col0, int M, int F, int lane, Release release) {
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t rg[32], ru[32];
+    ptx::tmem_ld_32x32(taddr + c * 32, rg);
+    ptx::tmem_ld_32x32(taddr + 128 + c * 32, ru);
+    ptx::tmem_ld_wait();
+    if (c == 3) {   // the whole accumulator has been read: hand the tensor-memory buffer back
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) release();
+    }
+    uint32_t wg[16], wu[16], w[16];
+    epilogue_convert(rg, rscale, colscale + c * 32, colbias + c * 32, wg);
+    epilogue_convert(ru, rscale, colscale + 128 + c * 32, colbias + 128 + c * 32, wu);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float g0 = __uint_as_float(wg[j] << 16), g1 = __uint_as_float(wg[j] & 0xffff0000u);
+      const float u0 = __uint_as_float(wu[j] << 16), u1 = __uint_as_float(wu[j] & 0xffff0000u);
+      const __nv_bfloat162 h = __floats2bfloat162_rn(silu_mul_f32(g0, u0), silu_mul_f32(g1, u1));
+      w[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    uint8_t* panel = warp_panels + sbuf * PANEL_BYTES;
+    const int half = c & 1;
+    if (half == 0) {
+      if (lane == 0) ptx::bulk_wait_group_read<EPI_BUFS - 1>();
+      __syncwarp();
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+      *reinterpret_cast<uint4*>(panel + lane * 128 + (((half * 4 + v) ^ (lane & 7)) * 16)) = make_uint4(w[4 * v], w[4 * v + 1], w[4 * v + 2], w[4 * v + 3]);
+    if (half == 1) {
+      ptx::fence_proxy_async();
+      __syncwarp();
+      const int col = col0 + (c >> 1) * 64;
+      if (lane == 0 && row0 < M && col < F) {
+        ptx::tma_store_2d(tmap_out, panel, col, store_y);
+        ptx::bulk_commit_group();
+      }
+      if (++sbuf == EPI_BUFS) sbuf = 0;
     }
   }
 }

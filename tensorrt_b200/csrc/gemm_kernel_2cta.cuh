@@ -56,7 +56,10 @@ struct Cfg2 {
   static_assert(kColsNeeded <= 512, "tensor memory overflow");
 };
 
-template <bool NVF4>
+// SILU (FP8 only): the tile's B rows are 128 gate rows (loaded by the leader) and the matching 128 up rows
+// (loaded by the peer, F rows further on), so accumulator columns 0..127 / 128..255 are a gate / up pair
+// and the epilogue writes silu(gate) * up into out[M, F] (Params::silu_f = F).
+template <bool NVF4, bool SILU = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ OutMaps tmap_out, const __grid_constant__ CUtensorMap tmap_sfa,
@@ -77,7 +80,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta_rank = ptx::cluster_ctarank();
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int m_blocks = (p.M + kPairM - 1) / kPairM, n_blocks = (p.N + kPairN - 1) / kPairN;
+  const int m_blocks = (p.M + kPairM - 1) / kPairM;
+  const int n_blocks = SILU ? (p.silu_f + kPairN / 2 - 1) / (kPairN / 2) : (p.N + kPairN - 1) / kPairN;
   const int num_tiles = m_blocks * n_blocks;
   const int k_tiles = (p.k_bytes + kBKBytes - 1) / kBKBytes;
   constexpr int kGroupM = 8;
@@ -124,7 +128,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int mb, nb;
         tile_coord(t, mb, nb);
         const int32_t m0 = mb * kPairM + static_cast<int>(cta_rank) * 128;
-        const int32_t n0 = nb * kPairN + static_cast<int>(cta_rank) * (kPairN / 2);
+        const int32_t n0 = SILU ? nb * (kPairN / 2) + static_cast<int>(cta_rank) * p.silu_f
+                                : nb * kPairN + static_cast<int>(cta_rank) * (kPairN / 2);
         for (int kt = 0; kt < k_tiles; ++kt) {
           if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1u)) {
             raise_timeout(p.status, 11);
@@ -231,13 +236,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     for (int t = pair; t < num_tiles; t += num_pairs) {
       int mb, nb;
       tile_coord(t, mb, nb);
-      const int n0 = nb * BN;
+      const int n0 = SILU ? nb * (BN / 2) : nb * BN;     // first output column of the tile
       float* colscale = epi + buf * 2 * BN;
       float* colbias = colscale + BN;
       for (int i = et; i < BN; i += 128) {
-        const int n = n0 + i;
+        int n = n0 + i;
+        bool valid = n < p.N;
+        if constexpr (SILU) {                                // columns 0..127: gate rows n0 + i; 128..255: up rows F + n0 + i - 128
+          n = i < BN / 2 ? n0 + i : p.silu_f + n0 + (i - BN / 2);
+          valid = n0 + (i & (BN / 2 - 1)) < p.silu_f;
+        }
         float s = 1.0f, b = 0.0f;
-        if (n < p.N) {
+        if (valid) {
           if constexpr (!NVF4) s = __ldg(p.b_scales + static_cast<int64_t>(n) * p.b_scale_stride);
           if (p.bias != nullptr) b = __bfloat162float(p.bias[n]);
         }
@@ -269,9 +279,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         store_y = p.rs_rank * p.rs_rows + (row0 - owner * p.rs_rows);
       }
       uint64_t* release_bar = acc_empty + acc;
-      epilogue_tile<BN, C::kEpiBufs, C::kPanelBytes>(taddr, rscale, colscale, colbias, store_stage + q * C::kEpiBufs * C::kPanelBytes,
-                                                     sbuf, omap, store_y, p.tma_store != 0, orow, row, row0, n0, p.M, p.N, vec_ok, lane,
-                                                     [release_bar]() { ptx::mbar_arrive_cluster(release_bar, 0); });
+      if constexpr (SILU)
+        epilogue_tile_silu<C::kEpiBufs, C::kPanelBytes>(taddr, rscale, colscale, colbias, store_stage + q * C::kEpiBufs * C::kPanelBytes,
+                                                        sbuf, omap, store_y, row0, n0, p.M, p.silu_f, lane,
+                                                        [release_bar]() { ptx::mbar_arrive_cluster(release_bar, 0); });
+      else
+        epilogue_tile<BN, C::kEpiBufs, C::kPanelBytes>(taddr, rscale, colscale, colbias, store_stage + q * C::kEpiBufs * C::kPanelBytes,
+                                                       sbuf, omap, store_y, p.tma_store != 0, orow, row, row0, n0, p.M, p.N, vec_ok, lane,
+                                                       [release_bar]() { ptx::mbar_arrive_cluster(release_bar, 0); });
       if (++acc == C::kAccStages) acc = 0, acc_phase ^= 1u;
     }
     if (lane == 0) {

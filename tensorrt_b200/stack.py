@@ -124,6 +124,14 @@ class CudaBackend:
         """`x`: bf16 activation, or an already quantized operand (tuple, as `quantize` returns)."""
         return self.matmul(x if isinstance(x, tuple) else self.quantize(x, amax), qw)
 
+    def gate_up_activation(self, xq, qw):
+        """Quantized input of the down projection straight from the gate/up GEMM: silu(gate) * up is applied
+        in the GEMM's epilogue (the [T, 2F] bf16 tensor is never written), then quantized per token.  FP8 with
+        at least 256 tokens and F a multiple of 128; None otherwise (the caller takes the unfused kernels)."""
+        if self.mode != "fp8" or xq[0].shape[0] < 256 or qw[0].shape[0] % 256:
+            return None
+        return capi.fp8_quantize(capi.fp8_gemm_silu_mul(xq[0], xq[1], qw[0], qw[1], None), None)
+
     def silu_mul_quantize(self, gate_up: torch.Tensor):
         """silu(gate) * up as the quantized operand of the down projection (one kernel), or None
         when the mode has no fused form (NVFP4 block quantize needs the tensor amax first)."""
@@ -304,6 +312,10 @@ class DecoderLayer:
         """gate/up linear + silu(gate) * up -> input of the down projection (quantized when the
         backend fuses the quantize, else bf16)."""
         be = self.backend
+        if hasattr(be, "gate_up_activation") and not self.calibrating:
+            act = be.gate_up_activation(xq, self.wgu)     # activation fused into the GEMM epilogue, where the backend has it
+            if act is not None:
+                return act
         gu = be.matmul(xq, self.wgu)
         act = be.silu_mul_quantize(gu) if hasattr(be, "silu_mul_quantize") and not self.calibrating else None
         return be.silu_mul(gu) if act is None else act

@@ -309,3 +309,30 @@ def test_torch_library_gemm_ops(b200):
     assert torch.equal(one, out)
     half = torch.ops.tensorrt.b200_nvfp4_linear(x.half().cuda(), x.float().abs().max().cuda(), wc4, ws4, wg4)
     assert half.dtype == torch.float16 and o.rel_l2(half.float(), ref - b.float().cuda()) <= TOL
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,F,K,with_bias", [(256, 128, 128, False), (300, 256, 512, True), (2048, 1024, 1024, False),
+                                             (4096, 3584, 2048, True), (8192, 1792, 4096, False)])
+def test_gate_up_gemm_with_fused_activation_is_bit_identical(b200, M, F, K, with_bias):
+    """b200q_fp8_gemm_silu_mul (gate rows then up rows in one weight, activation in the GEMM epilogue)
+    against b200q_fp8_gemm + b200q_silu_mul on the same operands: the same bits, with a ragged last
+    row tile, several tile rounds per SM pair, per-channel weight scales and a bias; and against the
+    oracle's linear + silu * up."""
+    capi = b200.capi
+    g = torch.Generator().manual_seed(M + F + K)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(2 * F, K, generator=g) * 0.05).bfloat16()
+    bias = (torch.randn(2 * F, generator=g) * 0.1).bfloat16() if with_bias else None
+    xq = capi.fp8_quantize(x.cuda(), None)
+    wq = capi.fp8_quantize(w.cuda(), capi.row_amax(w.cuda()))
+    bd = None if bias is None else bias.cuda()
+    fused = capi.fp8_gemm_silu_mul(xq[0], xq[1], wq[0], wq[1], bd)
+    ref = capi.silu_mul(capi.fp8_gemm(xq[0], xq[1], wq[0], wq[1], bd))
+    assert fused.shape == (M, F) and torch.equal(fused, ref)
+    assert capi.device_status() == 0
+    y = o.fp8_linear_ref(x, w, bias).float()
+    want = torch.nn.functional.silu(y[:, :F].bfloat16().float()) * y[:, F:].bfloat16().float()
+    assert o.rel_l2(fused.float().cpu(), want) < 1e-2
+    with pytest.raises(ValueError):
+        capi.fp8_gemm_silu_mul(xq[0], xq[1], wq[0][:2 * F - 128], wq[1][:2 * F - 128])     # F not a multiple of 128
