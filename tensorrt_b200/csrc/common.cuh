@@ -50,6 +50,12 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+// fused_ops.cu: dynamic per-token FP8 quantize of many long bf16 rows by persistent CTAs fed through a
+// shared-memory ring; 1 = shape does not qualify, else a B200Q status.
+#ifdef __CUDACC__
+int launch_fp8_rows_stream(const __nv_bfloat16* x, uint8_t* codes, float* scales, int64_t rows, int64_t cols, cudaStream_t st);
+#endif
+
 // Device must be compute capability 10.x; cached per device.
 int check_arch();
 int sm_count();

@@ -416,10 +416,13 @@ constexpr int kSiluChunkGroups = 2 * kThreads;                // groups of 8 ele
 constexpr int kSiluChunkBytes = kSiluChunkGroups * 16;        // per half
 constexpr int kSiluStages = 6;                                // 6 x 16 KB
 
-template <int CHUNKS>
+// GATED = false: the same machine as a plain per-token FP8 quantize of bf16 rows [rows, f] (one source, chunks of
+// 8 KB): rows too long to stay in registers with one CTA per row would otherwise be read twice.
+template <int CHUNKS, bool GATED>
 __global__ void __launch_bounds__(kThreads, 2)
 silu_mul_quant_stream_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __restrict__ codes, float* __restrict__ scales, int rows,
                              int f, int* __restrict__ status) {
+  constexpr int kStageBytes = (GATED ? 2 : 1) * kSiluChunkBytes;
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(128) unsigned char ring[];
@@ -441,12 +444,12 @@ silu_mul_quant_stream_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __re
     const int c = q % nch;
     const int g0 = c * kSiluChunkGroups;
     const uint32_t bytes = static_cast<uint32_t>(min(kSiluChunkGroups, groups - g0)) * 16u;
-    const __nv_bfloat16* gate = gu + row * 2 * f + static_cast<int64_t>(g0) * 8;
+    const __nv_bfloat16* gate = gu + row * (GATED ? 2 : 1) * f + static_cast<int64_t>(g0) * 8;
     const int s = q % kSiluStages;
-    unsigned char* dst = ring + static_cast<size_t>(s) * (2 * kSiluChunkBytes);
-    ptx::mbar_arrive_expect_tx(&full[s], 2 * bytes);
+    unsigned char* dst = ring + static_cast<size_t>(s) * kStageBytes;
+    ptx::mbar_arrive_expect_tx(&full[s], (GATED ? 2u : 1u) * bytes);
     ptx::bulk_load(dst, gate, bytes, &full[s]);
-    ptx::bulk_load(dst + kSiluChunkBytes, gate + f, bytes, &full[s]);
+    if constexpr (GATED) ptx::bulk_load(dst + kSiluChunkBytes, gate + f, bytes, &full[s]);
   };
   if (threadIdx.x == 0)
     for (int q = 0; q < kSiluStages && q < total; ++q) issue(q);
@@ -463,12 +466,19 @@ silu_mul_quant_stream_kernel(const __nv_bfloat16* __restrict__ gu, uint8_t* __re
           arrived = false;
           atomicCAS(status, 0, 82);
         }
-        const unsigned char* st = ring + static_cast<size_t>(s) * (2 * kSiluChunkBytes);
+        const unsigned char* st = ring + static_cast<size_t>(s) * kStageBytes;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           const int gl = threadIdx.x + i * kThreads;              // group inside the chunk
           y[c][i] = make_uint4(0u, 0u, 0u, 0u);
           if (c * kSiluChunkGroups + gl < groups) {
+            if constexpr (!GATED) {
+              y[c][i] = *reinterpret_cast<const uint4*>(st + static_cast<size_t>(gl) * 16);
+              const uint32_t* u = &y[c][i].x;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&u[j])));
+              continue;
+            }
             float a[8], b[8];
             Elem<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(st + static_cast<size_t>(gl) * 16), a);
             Elem<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(st + kSiluChunkBytes + static_cast<size_t>(gl) * 16), b);
@@ -560,6 +570,32 @@ int grid_for(int64_t work_items) {
 }
 
 }  // namespace
+
+// Dynamic per-token FP8 quantize of many long bf16 rows through the ring-fed persistent kernel
+// (silu_mul_quant_stream_kernel<.., false>).  Returns 1 when the shape does not qualify (the caller
+// then takes its one-CTA-per-row kernels), else the launch status.
+int launch_fp8_rows_stream(const __nv_bfloat16* x, uint8_t* codes, float* scales, int64_t rows, int64_t cols, cudaStream_t st) {
+  const int64_t groups = cols >> 3;
+  if (cols % 8 != 0 || rows < 8 * sm_count() || rows > 0x7fffffffLL || groups < kSiluChunkGroups || groups > 8 * kSiluChunkGroups)
+    return 1;
+  if (!aligned(x, 16) || !aligned(codes, 8)) return 1;
+  int* status = gemm::device_status_word();
+  if (status == nullptr) return B200Q_ERR_CUDA;
+  const int nch = static_cast<int>((groups + kSiluChunkGroups - 1) / kSiluChunkGroups);
+  const size_t smem = static_cast<size_t>(kSiluStages) * kSiluChunkBytes;
+  const dim3 grid(static_cast<unsigned>(2 * sm_count()));
+  const int r32 = static_cast<int>(rows), f32 = static_cast<int>(cols);
+#define B200Q_ROWS_STREAM(C)                                                                                                 \
+  do {                                                                                                                        \
+    cudaFuncSetAttribute(silu_mul_quant_stream_kernel<C, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    launch_pdl(silu_mul_quant_stream_kernel<C, false>, grid, dim3(kThreads), smem, st, x, codes, scales, r32, f32, status);           \
+  } while (0)
+  if (nch <= 2) B200Q_ROWS_STREAM(2);
+  else if (nch <= 4) B200Q_ROWS_STREAM(4);
+  else B200Q_ROWS_STREAM(8);
+#undef B200Q_ROWS_STREAM
+  return check_launch();
+}
 }  // namespace b200q
 
 using namespace b200q;
@@ -695,8 +731,8 @@ int b200q_silu_mul_fp8_quantize(const void* gate_up, uint8_t* codes_out, float* 
     const int r32 = static_cast<int>(rows), f32 = static_cast<int>(f);
 #define B200Q_SILUS(C)                                                                                              \
   do {                                                                                                               \
-    cudaFuncSetAttribute(silu_mul_quant_stream_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
-    launch_pdl(silu_mul_quant_stream_kernel<C>, grid, dim3(kThreads), smem, st, gp, codes_out, scales_out, r32, f32, status);   \
+    cudaFuncSetAttribute(silu_mul_quant_stream_kernel<C, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    launch_pdl(silu_mul_quant_stream_kernel<C, true>, grid, dim3(kThreads), smem, st, gp, codes_out, scales_out, r32, f32, status);   \
   } while (0)
     if (nch <= 2) B200Q_SILUS(2);
     else if (nch <= 4) B200Q_SILUS(4);

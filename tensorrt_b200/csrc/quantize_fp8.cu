@@ -158,7 +158,14 @@ int launch_rows(const void* x, const float* amax, int64_t amax_numel, uint8_t* c
                 int64_t rows, int64_t cols, cudaStream_t st) {
   const T* xt = static_cast<const T*>(x);
   T* ft = static_cast<T*>(fake);
-  if (amax_numel == 0) return launch_rows_items<T, 0, OUT>(xt, amax, codes, ft, scales, rows, cols, st);
+  if (amax_numel == 0) {
+    if constexpr (std::is_same<T, __nv_bfloat16>::value && OUT == Out::Codes) {
+      // many long rows: persistent CTAs fed through a shared-memory ring (fused_ops.cu)
+      const int rc = launch_fp8_rows_stream(xt, codes, scales, rows, cols, st);
+      if (rc != 1) return rc;
+    }
+    return launch_rows_items<T, 0, OUT>(xt, amax, codes, ft, scales, rows, cols, st);
+  }
   if (amax_numel == 1) return launch_rows_items<T, 1, OUT>(xt, amax, codes, ft, scales, rows, cols, st);
   return launch_rows_items<T, 2, OUT>(xt, amax, codes, ft, scales, rows, cols, st);
 }

@@ -209,3 +209,20 @@ def test_ops_through_torch_library(b200):
         torch.ops.tensorrt.quantize_op(xd, _cuda(amax), 8, 0, False, False)
     with pytest.raises(ValueError, match="multiple of the block size"):
         torch.ops.tensorrt.dynamic_block_quantize_op(xd[..., :24], 16, _cuda(amax), 4, 2, 8, 4)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols", [(1184, 4096), (1300, 4112), (1200, 8192), (1190, 14336), (1185, 28672), (1186, 32768)])
+def test_per_token_quantize_of_many_long_rows(capi, rows, cols):
+    """From 8 rows per SM and 4096 columns on, the dynamic per-token bf16 quantize runs as persistent CTAs
+    fed through a shared-memory ring: codes and scales are the oracle's bit for bit, and equal to what the
+    one-CTA-per-row kernels give on slices of the same tensor (an all-zero row included)."""
+    x = _make(rows, cols, torch.bfloat16, seed=rows + cols)
+    x[5] = 0
+    xd = _cuda(x)
+    codes, scales = capi.fp8_quantize(xd, None)
+    ref_c, ref_s = o.fp8_quantize(x, o.row_amax(x))
+    assert torch.equal(codes.cpu(), ref_c) and torch.equal(scales.cpu().reshape(-1), ref_s.reshape(-1))
+    parts = [capi.fp8_quantize(xd[i:i + 500].contiguous(), None) for i in range(0, rows, 500)]
+    assert torch.equal(codes, torch.cat([p[0] for p in parts])) and torch.equal(scales, torch.cat([p[1] for p in parts]))
+    assert capi.device_status() == 0
