@@ -1,6 +1,7 @@
 // Elementwise / row-wise kernels either side of the quantized linears in the decoder
 // linear stack: RMSNorm, silu(gate) * up, residual add, and the "attention = identity on V"
 // head expansion.  All are HBM-bound streaming kernels over bf16 with 128-bit accesses.
+#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -575,9 +576,15 @@ int grid_for(int64_t work_items) {
 // (silu_mul_quant_stream_kernel<.., false>).  Returns 1 when the shape does not qualify (the caller
 // then takes its one-CTA-per-row kernels), else the launch status.
 int launch_fp8_rows_stream(const __nv_bfloat16* x, uint8_t* codes, float* scales, int64_t rows, int64_t cols, cudaStream_t st) {
+  static const bool enabled = [] {
+    const char* e = std::getenv("B200Q_ROWS_STREAM");   // 0 = always one CTA per row (A/B measurements)
+    return e == nullptr || e[0] != '0';
+  }();
+  if (!enabled) return 1;
   const int64_t groups = cols >> 3;
-  if (cols % 8 != 0 || rows < 8 * sm_count() || rows > 0x7fffffffLL || groups < kSiluChunkGroups || groups > 8 * kSiluChunkGroups)
-    return 1;
+  // rows of up to 16384 elements stay in registers with one CTA per row, which is faster (0.82-0.91 of HBM against
+  // 0.54-0.72 here); beyond that the one-CTA form reads the row twice and this one wins (0.81)
+  if (cols % 8 != 0 || rows < 8 * sm_count() || rows > 0x7fffffffLL || cols <= 16384 || groups > 8 * kSiluChunkGroups) return 1;
   if (!aligned(x, 16) || !aligned(codes, 8)) return 1;
   int* status = gemm::device_status_word();
   if (status == nullptr) return B200Q_ERR_CUDA;

@@ -212,11 +212,11 @@ def test_ops_through_torch_library(b200):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("rows,cols", [(1184, 4096), (1300, 4112), (1200, 8192), (1190, 14336), (1185, 28672), (1186, 32768)])
+@pytest.mark.parametrize("rows,cols", [(1184, 4096), (1200, 16384), (1300, 16400), (1190, 20480), (1185, 28672), (1186, 32768)])
 def test_per_token_quantize_of_many_long_rows(capi, rows, cols):
-    """From 8 rows per SM and 4096 columns on, the dynamic per-token bf16 quantize runs as persistent CTAs
-    fed through a shared-memory ring: codes and scales are the oracle's bit for bit, and equal to what the
-    one-CTA-per-row kernels give on slices of the same tensor (an all-zero row included)."""
+    """Rows longer than 16384 elements, 8 or more per SM: the dynamic per-token bf16 quantize runs as persistent
+    CTAs fed through a shared-memory ring; shorter rows keep one CTA per row.  Either way codes and scales are the
+    oracle's bit for bit and equal to what slices of the same tensor give (an all-zero row included)."""
     x = _make(rows, cols, torch.bfloat16, seed=rows + cols)
     x[5] = 0
     xd = _cuda(x)
