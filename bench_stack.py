@@ -296,10 +296,23 @@ def run(args):
             ms = bc.timed(lambda i: stack.forward(h, mb, sharded), steps, warmup, world)
     status = capi.device_status()
 
+    x_dev = torch.empty_like(h) if world > 1 else None
+
     def e2e(i):
-        x = h_host.to(dev, non_blocking=True)
+        # the request lives in ONE host process: rank 0 copies it in and the other ranks get it over NVLink
+        # (a broadcast on the process group); every rank ends up with the complete result, rank 0 copies it out
+        if world == 1:
+            x = h_host.to(dev, non_blocking=True)
+        else:
+            import torch.distributed as dist
+
+            if rank == 0:
+                x_dev.copy_(h_host, non_blocking=True)
+            dist.broadcast(x_dev, src=0)
+            x = x_dev
         y = stack.forward(x, mb, sharded)
-        y_host.copy_(y, non_blocking=True)               # the whole [tokens, hidden] bf16 result back to pinned host memory
+        if rank == 0:
+            y_host.copy_(y, non_blocking=True)           # the whole [tokens, hidden] bf16 result back to pinned host memory
         torch.cuda.current_stream().synchronize()
 
     if phase != "decode":
@@ -378,7 +391,9 @@ def run(args):
         "gpu_launches": launches,
         "e2e": {"value": tokens * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h_host.numel() * 2,
                 "d2h_bytes_per_step": y_host.numel() * 2, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
-                "path": "pinned host bf16 activations -> device, DecoderStack.forward, bf16 result -> pinned host"},
+                "path": "pinned host bf16 activations -> device"
+                        + (" of rank 0 -> broadcast to the ranks over NVLink" if world > 1 else "")
+                        + ", DecoderStack.forward, bf16 result -> pinned host" + (" of rank 0" if world > 1 else "")},
         "model_tflops": tflops,
         "roofline": {"bound": "tensor", "achieved": tflops / world, "peak": peaks["bf16_tflops_sustained"] * scale, "unit": "TFLOP/s",
                      "frac": tflops / world / (peaks["bf16_tflops_sustained"] * scale),
