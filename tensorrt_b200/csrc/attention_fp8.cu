@@ -278,22 +278,32 @@ fp8_sdpa_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           for (int i = 0; i < 32; ++i)
             if (key0 + i > last_key) v[i] = 0xff800000u;   // -inf
         }
-        float cm = __uint_as_float(v[0]);
+        // four independent chains each for the maximum and the sum: a warp has few neighbours on its scheduler
+        // here, so the length of a dependent chain is what it waits for
+        float c0 = __uint_as_float(v[0]), c1 = __uint_as_float(v[1]), c2m = __uint_as_float(v[2]), c3 = __uint_as_float(v[3]);
 #pragma unroll
-        for (int i = 1; i < 32; ++i) cm = fmaxf(cm, __uint_as_float(v[i]));
+        for (int i = 4; i < 32; i += 4) {
+          c0 = fmaxf(c0, __uint_as_float(v[i]));
+          c1 = fmaxf(c1, __uint_as_float(v[i + 1]));
+          c2m = fmaxf(c2m, __uint_as_float(v[i + 2]));
+          c3 = fmaxf(c3, __uint_as_float(v[i + 3]));
+        }
+        const float cm = fmaxf(fmaxf(c0, c1), fmaxf(c2m, c3));
         if (cm > m) {
           l *= ex2_approx((m - cm) * c2);         // m = -inf: l is 0 and stays 0
           m = cm;
         }
         if (m > -INFINITY) {
           const float off = -m * c2;
-          float l0 = 0.0f, l1 = 0.0f;
+          float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
+          for (int i = 0; i < 32; i += 4) {
             l0 += ex2_approx(fmaf(__uint_as_float(v[i]), c2, off));
             l1 += ex2_approx(fmaf(__uint_as_float(v[i + 1]), c2, off));
+            l2 += ex2_approx(fmaf(__uint_as_float(v[i + 2]), c2, off));
+            l3 += ex2_approx(fmaf(__uint_as_float(v[i + 3]), c2, off));
           }
-          l += l0 + l1;
+          l += (l0 + l1) + (l2 + l3);
         }
       }
       ptx::tc_fence_before();
