@@ -266,6 +266,42 @@ Tensor fp8_gemm_nobias_meta(const Tensor& a, const Tensor& sa, const Tensor& b, 
 Tensor fp8_gemm_bias_meta(const Tensor& a, const Tensor& sa, const Tensor& b, const Tensor& sb, const Tensor&) {
   return fp8_gemm_meta(a, sa, b, sb, std::nullopt);
 }
+// Gate/up linear of a gated MLP with the activation in the GEMM epilogue: b = [F gate rows; F up rows],
+// out [.., F] = silu(g) * u.  Fewer than 256 tokens (a decode step) take the GEMM and the activation
+// kernel one after the other: the same bits.
+Tensor fp8_gemm_silu_mul_cuda(const Tensor& a_codes, const Tensor& a_scales, const Tensor& b_codes, const Tensor& b_scales) {
+  TORCH_CHECK(a_codes.scalar_type() == at::kByte && b_codes.scalar_type() == at::kByte, "b200_fp8_gemm_silu_mul: codes must be uint8");
+  TORCH_CHECK(b_codes.dim() == 2 && a_codes.dim() >= 1 && a_codes.size(-1) == b_codes.size(1) && b_codes.size(0) % 256 == 0,
+              "b200_fp8_gemm_silu_mul: a [.., K] and b [2F, K] with F a multiple of 128, got ", a_codes.sizes(), " and ", b_codes.sizes());
+  c10::cuda::CUDAGuard guard(a_codes.device());
+  Tensor a = a_codes.contiguous(), b = b_codes.contiguous();
+  Tensor sa = a_scales.contiguous(), sb = b_scales.contiguous();
+  TORCH_CHECK(sa.scalar_type() == at::kFloat && sb.scalar_type() == at::kFloat, "b200_fp8_gemm_silu_mul: scales must be float32");
+  const int64_t K = b.size(1), N = b.size(0), M = a.numel() / std::max<int64_t>(K, 1);
+  TORCH_CHECK((sa.numel() == 1 || sa.numel() == M) && (sb.numel() == 1 || sb.numel() == N),
+              "b200_fp8_gemm_silu_mul: scales must be per-tensor or per-row");
+  auto shape = a.sizes().vec();
+  shape.back() = N / 2;
+  Tensor out = at::empty(shape, a.options().dtype(at::kBFloat16));
+  if (out.numel() == 0) return out;
+  if (M >= 256) {
+    check_status(b200q_fp8_gemm_silu_mul(a.data_ptr<uint8_t>(), sa.data_ptr<float>(), sa.numel(), b.data_ptr<uint8_t>(), sb.data_ptr<float>(),
+                                         sb.numel(), nullptr, out.data_ptr(), M, N, K, current_stream(), nullptr),
+                 "b200q_fp8_gemm_silu_mul");
+  } else {
+    Tensor gu = at::empty({M, N}, a.options().dtype(at::kBFloat16));
+    check_status(b200q_fp8_gemm(a.data_ptr<uint8_t>(), sa.data_ptr<float>(), sa.numel(), b.data_ptr<uint8_t>(), sb.data_ptr<float>(), sb.numel(),
+                                nullptr, gu.data_ptr(), M, N, K, current_stream(), nullptr),
+                 "b200q_fp8_gemm");
+    check_status(b200q_silu_mul(gu.data_ptr(), out.data_ptr(), M, N / 2, current_stream()), "b200q_silu_mul");
+  }
+  return out;
+}
+Tensor fp8_gemm_silu_mul_meta(const Tensor& a_codes, const Tensor&, const Tensor& b_codes, const Tensor&) {
+  auto shape = a_codes.sizes().vec();
+  shape.back() = b_codes.size(0) / 2;
+  return at::empty(shape, a_codes.options().dtype(at::kBFloat16));
+}
 Tensor nvfp4_gemm_nobias_cuda(const Tensor& a, const Tensor& sa, const Tensor& ga, const Tensor& b, const Tensor& sb, const Tensor& gb) {
   return nvfp4_gemm_cuda(a, sa, ga, b, sb, gb, std::nullopt);
 }
@@ -441,6 +477,9 @@ TORCH_LIBRARY_FRAGMENT(tensorrt, m) {
   m.def("b200_fp8_gemm_bias(Tensor a_codes, Tensor a_scales, Tensor b_codes, Tensor b_scales, Tensor bias) -> Tensor");
   m.impl("b200_fp8_gemm_bias", c10::DispatchKey::CUDA, TORCH_FN(fp8_gemm_bias_cuda));
   m.impl("b200_fp8_gemm_bias", c10::DispatchKey::Meta, TORCH_FN(fp8_gemm_bias_meta));
+  m.def("b200_fp8_gemm_silu_mul(Tensor a_codes, Tensor a_scales, Tensor b_codes, Tensor b_scales) -> Tensor");
+  m.impl("b200_fp8_gemm_silu_mul", c10::DispatchKey::CUDA, TORCH_FN(fp8_gemm_silu_mul_cuda));
+  m.impl("b200_fp8_gemm_silu_mul", c10::DispatchKey::Meta, TORCH_FN(fp8_gemm_silu_mul_meta));
   m.def("b200_nvfp4_gemm(Tensor a_codes, Tensor a_scales, Tensor a_global, Tensor b_codes, Tensor b_scales, Tensor b_global) -> Tensor");
   m.impl("b200_nvfp4_gemm", c10::DispatchKey::CUDA, TORCH_FN(nvfp4_gemm_nobias_cuda));
   m.impl("b200_nvfp4_gemm", c10::DispatchKey::Meta, TORCH_FN(nvfp4_gemm_nobias_meta));

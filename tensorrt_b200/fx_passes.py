@@ -323,6 +323,71 @@ def fuse_fp8_sdpa(gm: fx.GraphModule) -> int:
     return count
 
 
+def fuse_gated_mlp(gm: fx.GraphModule) -> int:
+    """`silu(gate(x)) * up(x)` whose two linears were rewritten by `fuse_quantized_linear` into
+    `b200_fp8_gemm` nodes on the SAME quantized activation, with folded (constant) weights and no bias,
+    becomes one `tensorrt::b200_fp8_gemm_silu_mul` node on the stacked weight [gate rows; up rows]: the
+    activation rides in the GEMM epilogue and the [tokens, 2F] tensor is never written (the bits of the GEMM
+    followed by this library's silu * up kernel: one bf16 rounding where eager silu and mul round twice).  This
+    is the MLP of the models the reference lowers (`down_proj(act_fn(gate_proj(x)) * up_proj(x))`).  Left
+    alone: F not a multiple of 128, weights that are not constants, a bias, an output cast between the GEMM
+    and the activation.  Returns the number of MLPs rewritten; run it after `fuse_quantized_linear`."""
+    from . import ops
+
+    ops.load_ops()
+    t, a = torch.ops.tensorrt, torch.ops.aten
+    gemm = t.b200_fp8_gemm.default
+    silus = (torch.nn.functional.silu, a.silu, a.silu.default)
+    muls = (operator.mul, torch.mul, a.mul, a.mul.Tensor)
+    graph, count = gm.graph, 0
+    for node in list(graph.nodes):
+        if node.op != "call_function" or node.target not in muls or len(node.args) != 2:
+            continue
+        lhs, rhs = node.args
+        if not (isinstance(lhs, fx.Node) and isinstance(rhs, fx.Node)):
+            continue
+        act, up = (lhs, rhs) if (lhs.op == "call_function" and lhs.target in silus) else (rhs, lhs)
+        if not (act.op == "call_function" and act.target in silus and len(act.args) >= 1 and len(act.users) == 1):
+            continue
+        gate = act.args[0]
+        if not all(isinstance(n, fx.Node) and n.op == "call_function" and n.target is gemm and len(n.users) == 1 for n in (gate, up)):
+            continue
+        if gate.args[0] is not up.args[0] or gate.args[1] is not up.args[1]:
+            continue                                            # not the same quantized activation
+        consts = [_const_tensor(gm, n) for n in (gate.args[2], gate.args[3], up.args[2], up.args[3])]
+        if any(c is None for c in consts):
+            continue
+        gc, gs, uc, us = consts
+        f = gc.shape[0]
+        if gc.shape != uc.shape or f % 128 or gs.numel() not in (1, f) or us.numel() not in (1, f):
+            continue
+        gs, us = (s_.reshape(-1).expand(f) for s_ in (gs, us))          # a per-tensor scale becomes one per row: same products
+        names = []
+        for i, stacked in enumerate((torch.cat([gc, uc], dim=0).contiguous(), torch.cat([gs.reshape(-1), us.reshape(-1)]).contiguous())):
+            name = f"_b200q_gu{count}_{i}"
+            while hasattr(gm, name):
+                name += "_"
+            gm.register_buffer(name, stacked)
+            names.append(name)
+        with graph.inserting_before(node):
+            w_parts = [graph.get_attr(n) for n in names]
+            out = graph.call_function(t.b200_fp8_gemm_silu_mul.default, (gate.args[0], gate.args[1], *w_parts))
+        out.meta.update({k: v for k, v in node.meta.items() if k in ("val", "tensor_meta")})
+        node.replace_all_uses_with(out)
+        old_consts = [gate.args[2], gate.args[3], up.args[2], up.args[3]]
+        for dead in (node, act, gate, up):
+            if not dead.users:
+                graph.erase_node(dead)
+        for c in old_consts:
+            _drop_unused_constant(gm, c)
+        count += 1
+    if count:
+        graph.eliminate_dead_code()
+        graph.lint()
+        gm.recompile()
+    return count
+
+
 def fuse_all_reduce_wait(gm: fx.GraphModule) -> int:
     """`_c10d_functional.all_reduce(x, op, group)` whose only user is `wait_tensor` becomes one
     `tensorrt::fused_nccl_all_reduce(x, op, group)` node, the form the reference's converters (and

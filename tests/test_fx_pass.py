@@ -386,3 +386,58 @@ def test_all_reduce_plus_wait_becomes_the_fused_op(b200):
     gm2 = _all_reduce_graph(extra_user=True)
     before = _targets(gm2)
     assert fuse_all_reduce_wait(gm2) == 0 and _targets(gm2) == before
+
+
+class GatedMlp(torch.nn.Module):
+    """down(silu(gate(x)) * up(x)) with Q/DQ on every linear input and weight, gate and up sharing the
+    input quantizer (per-tensor amax, as after calibration)."""
+
+    def __init__(self, hidden=256, ffn=384, bias=False):
+        super().__init__()
+        self.gate, self.up = QdqLinear(ffn, hidden, bias=bias, seed=11), QdqLinear(ffn, hidden, bias=bias, seed=12)
+        self.down = QdqLinear(hidden, ffn, bias=False, seed=13)
+
+    def forward(self, x):
+        xq = self.gate.q(x, self.gate.x_amax)
+        g = torch.nn.functional.linear(xq, self.gate.q(self.gate.weight, self.gate.w_amax), self.gate.bias)
+        u = torch.nn.functional.linear(xq, self.up.q(self.up.weight, self.up.w_amax), self.up.bias)
+        return self.down(torch.nn.functional.silu(g) * u)
+
+
+def test_gated_mlp_pass_leaves_unfolded_or_biased_linears_alone(b200):
+    """On CPU the weights are not folded into constants, so there is nothing the pass may stack."""
+    from tensorrt_b200.fx_passes import fuse_gated_mlp, fuse_quantized_linear
+
+    gm = torch.fx.symbolic_trace(GatedMlp())
+    assert fuse_quantized_linear(gm) == 3
+    assert fuse_gated_mlp(gm) == 0
+    assert sum("b200_fp8_gemm" in t for t in _targets(gm)) == 3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tokens", [8, 300])
+def test_gated_mlp_becomes_one_gemm_with_the_activation_in_its_epilogue(b200, tokens):
+    """gate and up linears + silu * up -> one b200_fp8_gemm_silu_mul node on the stacked weight (fewer than 256
+    tokens run GEMM + activation kernel inside the op, more run the fused epilogue).  Against the graph before
+    the pass, where torch's own silu and mul round to bf16 twice, the result differs by that rounding only; a
+    bias or an F that is not a multiple of 128 is left alone."""
+    from tensorrt_b200.fx_passes import fuse_gated_mlp, fuse_quantized_linear
+
+    x = (torch.randn(tokens, 256, generator=torch.Generator().manual_seed(3)) * 1.5).bfloat16().cuda()
+    gm = torch.fx.symbolic_trace(GatedMlp().cuda())
+    assert fuse_quantized_linear(gm) == 3
+    before = gm(x)
+    assert fuse_gated_mlp(gm) == 1
+    names = _targets(gm)
+    assert sum("b200_fp8_gemm_silu_mul" in t for t in names) == 1 and not any("silu." in t or t.endswith("silu") for t in names if "gemm" not in t)
+    assert sum("b200_fp8_gemm" in t for t in names) == 2               # the fused node and the down projection
+    assert sum("b200_fp8_quantize" in t for t in names) == 2           # x and the activation: all weights folded
+    after = gm(x)
+    assert o.rel_l2(after.float().cpu(), before.float().cpu()) < 5e-3
+    assert fuse_gated_mlp(gm) == 0                                      # idempotent
+    leftovers = [n for n, _ in gm.named_buffers() if n.startswith("_b200q_w")]
+    assert len(leftovers) == 2, leftovers                               # codes and scales of the down projection only
+    for model in (GatedMlp(bias=True), GatedMlp(ffn=320)):
+        gm2 = torch.fx.symbolic_trace(model.cuda())
+        assert fuse_quantized_linear(gm2) == 3
+        assert fuse_gated_mlp(gm2) == 0
