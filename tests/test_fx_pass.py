@@ -433,7 +433,7 @@ def test_gated_mlp_becomes_one_gemm_with_the_activation_in_its_epilogue(b200, to
     assert sum("b200_fp8_gemm" in t for t in names) == 2               # the fused node and the down projection
     assert sum("b200_fp8_quantize" in t for t in names) == 2           # x and the activation: all weights folded
     after = gm(x)
-    assert o.rel_l2(after.float().cpu(), before.float().cpu()) < 5e-3
+    assert o.rel_l2(after.float().cpu(), before.float().cpu()) < 2e-2   # through the FP8 re-quantization in front of the down projection
     assert fuse_gated_mlp(gm) == 0                                      # idempotent
     leftovers = [n for n, _ in gm.named_buffers() if n.startswith("_b200q_w")]
     assert len(leftovers) == 2, leftovers                               # codes and scales of the down projection only
