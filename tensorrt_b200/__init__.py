@@ -6,6 +6,7 @@
     tensorrt_b200.Fp8Linear.from_float(linear)(x)                           # real-quant FP8 GEMM path
     tensorrt_b200.Nvfp4Linear.from_float(linear)(x)                         # real-quant NVFP4 GEMM path
     tensorrt_b200.fuse_quantized_linear(graph_module)                       # Q/DQ-wrapped linears -> GEMM nodes
+    tensorrt_b200.fuse_gated_mlp(graph_module)                              # silu(gate(x)) * up(x) -> one GEMM
 
 Only CUDA (compute capability 10.x) is implemented; there is no CPU or other-GPU fallback.
 """
