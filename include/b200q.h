@@ -195,6 +195,17 @@ int b200q_fp8_gemm_silu_mul(const uint8_t* a_codes, const float* a_scales, int64
                             const uint8_t* b_codes, const float* b_scales, int64_t b_scales_numel,
                             const void* bias, void* out, int64_t M, int64_t N, int64_t K,
                             b200q_stream_t stream, const b200q_cfg* cfg);
+
+/* The same with the activation's FP8 quantizer folded in as well, for a STATIC per-tensor amax (what the
+ * input quantizer of the down projection holds after calibration): codes_out [M, F] uint8 =
+ * e4m3(clamp(bf16(silu(g) * u) / scale)), scale = act_amax[0] / 448 (0 -> 1) also written to scale_out[0]
+ * when that is not NULL.  The same bits as b200q_fp8_gemm_silu_mul followed by b200q_fp8_quantize with
+ * amax_numel = 1; no bf16 activation is written at all. */
+int b200q_fp8_gemm_silu_mul_quantize(const uint8_t* a_codes, const float* a_scales, int64_t a_scales_numel,
+                                     const uint8_t* b_codes, const float* b_scales, int64_t b_scales_numel,
+                                     const void* bias, const float* act_amax, uint8_t* codes_out,
+                                     float* scale_out, int64_t M, int64_t N, int64_t K,
+                                     b200q_stream_t stream, const b200q_cfg* cfg);
 int b200q_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_scales, const float* a_global,
                      const uint8_t* b_codes, const uint8_t* b_scales, const float* b_global,
                      const void* bias, void* out, int64_t M, int64_t N, int64_t K,

@@ -34,6 +34,7 @@ SIGNATURES = {
     "b200q_nvfp4_dequantize": (_c.c_int, [_p, _p, _p, _i64, _i64, _p, _c.c_int, _p]),
     "b200q_fp8_gemm": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _p, _p]),
     "b200q_fp8_gemm_silu_mul": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _p, _p]),
+    "b200q_fp8_gemm_silu_mul_quantize": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _p, _p, _p, _i64, _i64, _i64, _p, _p]),
     "b200q_nvfp4_gemm": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _p]),
     "b200q_fp8_gemm_reduce_scatter": (_c.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _p, _p]),
     "b200q_nvfp4_gemm_reduce_scatter": (_c.c_int, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _p]),

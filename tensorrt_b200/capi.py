@@ -238,6 +238,33 @@ def fp8_gemm_silu_mul(a_codes, a_scales, b_codes, b_scales, bias=None, out=None)
     return out
 
 
+def fp8_gemm_silu_mul_quantize(a_codes, a_scales, b_codes, b_scales, act_amax, bias=None):
+    """`fp8_gemm_silu_mul` with the activation's static per-tensor FP8 quantizer in the epilogue as well:
+    -> (E4M3 codes [.., F] uint8, scale [1] = act_amax / 448), the same bits as quantizing its bf16 result
+    with `fp8_quantize(.., act_amax)`."""
+    _need_cuda(a_codes, a_scales, b_codes, b_scales, bias, act_amax)
+    a_codes, b_codes = a_codes.contiguous(), b_codes.contiguous()
+    k = a_codes.shape[-1]
+    m = a_codes.numel() // max(k, 1)
+    n = b_codes.shape[0]
+    if b_codes.dim() != 2 or b_codes.shape[1] != k or n % 256:
+        raise ValueError(f"b must be [2F, {k}] with F a multiple of 128, got {tuple(b_codes.shape)}")
+    if act_amax.numel() != 1:
+        raise ValueError("act_amax must hold one value (a static per-tensor amax)")
+    a_scales, b_scales = a_scales.float().contiguous(), b_scales.float().contiguous()
+    act_amax = act_amax.float().reshape(1).contiguous()
+    if bias is not None:
+        bias = bias.to(torch.bfloat16).contiguous()
+    codes = torch.empty(tuple(a_codes.shape[:-1]) + (n // 2,), dtype=torch.uint8, device=a_codes.device)
+    scale = torch.empty(1, dtype=torch.float32, device=a_codes.device)
+    with torch.cuda.device(a_codes.device):
+        check(load().b200q_fp8_gemm_silu_mul_quantize(a_codes.data_ptr(), a_scales.data_ptr(), a_scales.numel(), b_codes.data_ptr(),
+                                                      b_scales.data_ptr(), b_scales.numel(), _ptr(bias), act_amax.data_ptr(),
+                                                      codes.data_ptr(), scale.data_ptr(), m, n, k, _stream(a_codes), None),
+              "b200q_fp8_gemm_silu_mul_quantize")
+    return codes, scale
+
+
 def nvfp4_gemm(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias=None, tile_n=None, static_weights=None,
                out=None) -> torch.Tensor:
     _need_cuda(a_codes, a_scales, a_global, b_codes, b_scales, b_global, bias)

@@ -126,7 +126,38 @@ int b200q_fp8_gemm_silu_mul(const uint8_t* a_codes, const float* a_scales, int64
   p.silu_f = static_cast<int>(N / 2);
   p.status = gemm::device_status_word();
   if (p.status == nullptr) return B200Q_ERR_CUDA;
-  return gemm::launch_pair<false, true>(a_codes, b_codes, p, static_cast<cudaStream_t>(stream));
+  return gemm::launch_pair<false, 1>(a_codes, b_codes, p, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_fp8_gemm_silu_mul_quantize(const uint8_t* a_codes, const float* a_scales, int64_t a_scales_numel, const uint8_t* b_codes,
+                                     const float* b_scales, int64_t b_scales_numel, const void* bias, const float* act_amax,
+                                     uint8_t* codes_out, float* scale_out, int64_t M, int64_t N, int64_t K, b200q_stream_t stream,
+                                     const b200q_cfg* cfg) {
+  if (a_codes == nullptr || b_codes == nullptr || a_scales == nullptr || b_scales == nullptr || codes_out == nullptr || act_amax == nullptr)
+    return B200Q_ERR_INVALID;
+  if (cfg != nullptr && (cfg->tile_n != 0 || cfg->reserved != 0)) return B200Q_ERR_INVALID;
+  if (M < 0 || N < 0 || K <= 0 || M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200Q_ERR_INVALID;
+  if (K % 16 != 0 || N % 256 != 0) return B200Q_ERR_INVALID;
+  if ((a_scales_numel != 1 && a_scales_numel != M) || (b_scales_numel != 1 && b_scales_numel != N)) return B200Q_ERR_INVALID;
+  if (!aligned(a_codes, 16) || !aligned(b_codes, 16) || !aligned(codes_out, 16)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  if (M == 0 || N == 0) return B200Q_OK;
+  gemm::Params p{};
+  p.a_scales = a_scales;
+  p.b_scales = b_scales;
+  p.a_scale_stride = a_scales_numel == 1 ? 0 : 1;
+  p.b_scale_stride = b_scales_numel == 1 ? 0 : 1;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.out = reinterpret_cast<__nv_bfloat16*>(codes_out);
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.k_bytes = static_cast<int>(K);
+  p.silu_f = static_cast<int>(N / 2);
+  p.act_amax = act_amax;
+  p.act_scale_out = scale_out;
+  p.status = gemm::device_status_word();
+  if (p.status == nullptr) return B200Q_ERR_CUDA;
+  return gemm::launch_pair<false, 2>(a_codes, b_codes, p, static_cast<cudaStream_t>(stream));
 }
 
 static int fill_rs(gemm::Params& p, gemm::RsTargets& rs, const b200q_peers* peers, int64_t M) {

@@ -108,7 +108,7 @@ inline int make_scale_map(CUtensorMap* map, const void* base, int64_t row_tiles,
 }
 
 // CTA-pair kernel: clusters of two CTAs, one cluster per 256 x 256 output tile.
-template <bool NVF4, bool SILU = false>
+template <bool NVF4, int SILU = 0>
 int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, const RsTargets* rs = nullptr) {
   using C = Cfg2<NVF4>;
   static bool configured[64] = {};
@@ -123,7 +123,11 @@ int launch_pair(const uint8_t* a, const uint8_t* b, Params p, cudaStream_t st, c
   OutMaps tout = {};
   if (int rc = make_operand_map(&ta, a, p.M, p.k_bytes, 128)) return rc;
   if (int rc = make_operand_map(&tb, b, p.N, p.k_bytes, kPairN / 2)) return rc;
-  if constexpr (SILU) {
+  if constexpr (SILU == 2) {
+    // E4M3 codes [M, F] leave through plain stores: no output map
+    p.tma_store = 0;
+    if (rs != nullptr || p.rs_world > 1) return B200Q_ERR_INVALID;
+  } else if constexpr (SILU == 1) {
     // out is [M, F]: TMA stores only (F is a multiple of 128)
     p.tma_store = 1;
     if (rs != nullptr || p.rs_world > 1) return B200Q_ERR_INVALID;

@@ -92,6 +92,8 @@ struct Params {
                            // waiting for that kernel; 0 = wait first
   int silu_f;              // FP8 CTA-pair kernel, > 0: B holds F gate rows then F up rows (N = 2 F); the epilogue
                            // writes out[M, F] = silu(gate) * up, each linear output rounded to bf16 first
+  const float* act_amax;   // quantizing form of the above: static per-tensor abs-max of the activation; `out` then
+  float* act_scale_out;    // receives E4M3 codes [M, F] (one byte each) and act_scale_out[0] the scale amax / 448
   int sf_copier;           // NVFP4, 1-CTA kernel: 1 = a dedicated warp (warp 6 of 224 threads) issues the tcgen05.cp scale copies
   int* status;             // device status word (0 = ok)
 };
@@ -235,6 +237,50 @@ __device__ __forceinline__ void epilogue_tile_silu(uint32_t taddr, float rscale,
         ptx::bulk_commit_group();
       }
       if (++sbuf == EPI_BUFS) sbuf = 0;
+    }
+  }
+}
+
+// The same with the activation quantized on the way out: silu(gate) * up is rounded to bf16 (the value the
+// unfused graph would hand to its quantizer), divided by the static per-tensor scale with the exact-division
+// sequence of the quantize kernels, and stored as E4M3 codes, 32 bytes per row and chunk (plain stores).
+template <typename Release>
+__device__ __forceinline__ void epilogue_tile_silu_quant(uint32_t taddr, float rscale, const float* colscale, const float* colbias,
+                                                         uint8_t* crow, bool row_ok, int col0, int F, float scale, float y, float lim,
+                                                         bool fast, int lane, Release release) {
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t rg[32], ru[32];
+    ptx::tmem_ld_32x32(taddr + c * 32, rg);
+    ptx::tmem_ld_32x32(taddr + 128 + c * 32, ru);
+    ptx::tmem_ld_wait();
+    if (c == 3) {
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) release();
+    }
+    uint32_t wg[16], wu[16];
+    epilogue_convert(rg, rscale, colscale + c * 32, colbias + c * 32, wg);
+    epilogue_convert(ru, rscale, colscale + 128 + c * 32, colbias + 128 + c * 32, wu);
+    uint32_t codes[8];
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) {
+      float q[4];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float g0 = __uint_as_float(wg[j + e] << 16), g1 = __uint_as_float(wg[j + e] & 0xffff0000u);
+        const float u0 = __uint_as_float(wu[j + e] << 16), u1 = __uint_as_float(wu[j + e] & 0xffff0000u);
+        const __nv_bfloat162 h = __floats2bfloat162_rn(silu_mul_f32(g0, u0), silu_mul_f32(g1, u1));
+        const float a0 = __low2float(h), a1 = __high2float(h);
+        q[2 * e] = fast ? div_path<kDivClamped>(a0, scale, y, lim) : div_path<kDivTrue>(a0, scale, y, lim);
+        q[2 * e + 1] = fast ? div_path<kDivClamped>(a1, scale, y, lim) : div_path<kDivTrue>(a1, scale, y, lim);
+      }
+      codes[j >> 1] = f32x2_to_e4m3x2(q[0], q[1]) | (f32x2_to_e4m3x2(q[2], q[3]) << 16);
+    }
+    if (row_ok && col0 + c * 32 < F) {
+      uint4* dst = reinterpret_cast<uint4*>(crow + c * 32);
+      dst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+      dst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
     }
   }
 }

@@ -58,8 +58,9 @@ struct Cfg2 {
 
 // SILU (FP8 only): the tile's B rows are 128 gate rows (loaded by the leader) and the matching 128 up rows
 // (loaded by the peer, F rows further on), so accumulator columns 0..127 / 128..255 are a gate / up pair
-// and the epilogue writes silu(gate) * up into out[M, F] (Params::silu_f = F).
-template <bool NVF4, bool SILU = false>
+// and the epilogue writes silu(gate) * up into out[M, F] (Params::silu_f = F): SILU = 1 as bf16, SILU = 2 as E4M3
+// codes at the static per-tensor scale Params::act_amax / 448.
+template <bool NVF4, int SILU = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ OutMaps tmap_out, const __grid_constant__ CUtensorMap tmap_sfa,
@@ -279,7 +280,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         store_y = p.rs_rank * p.rs_rows + (row0 - owner * p.rs_rows);
       }
       uint64_t* release_bar = acc_empty + acc;
-      if constexpr (SILU)
+      if constexpr (SILU == 2) {
+        const float qscale = fp8_scale_from_amax(__ldg(p.act_amax));
+        if (t == 0 && cta_rank == 0 && et == 0 && p.act_scale_out != nullptr) p.act_scale_out[0] = qscale;
+        uint8_t* crow = reinterpret_cast<uint8_t*>(p.out) + static_cast<int64_t>(row) * p.silu_f + n0;
+        epilogue_tile_silu_quant(taddr, rscale, colscale, colbias, crow, row < p.M, n0, p.silu_f, qscale, b200q_rcp_rn(qscale),
+                                 __fmul_rn(qscale, 512.0f), b200q_div_fast_ok(qscale), lane,
+                                 [release_bar]() { ptx::mbar_arrive_cluster(release_bar, 0); });
+      } else if constexpr (SILU == 1)
         epilogue_tile_silu<C::kEpiBufs, C::kPanelBytes>(taddr, rscale, colscale, colbias, store_stage + q * C::kEpiBufs * C::kPanelBytes,
                                                         sbuf, omap, store_y, row0, n0, p.M, p.silu_f, lane,
                                                         [release_bar]() { ptx::mbar_arrive_cluster(release_bar, 0); });

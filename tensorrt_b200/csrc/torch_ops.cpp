@@ -302,6 +302,48 @@ Tensor fp8_gemm_silu_mul_meta(const Tensor& a_codes, const Tensor&, const Tensor
   shape.back() = b_codes.size(0) / 2;
   return at::empty(shape, a_codes.options().dtype(at::kBFloat16));
 }
+// ... and with the static per-tensor FP8 quantizer of the activation in the epilogue too: (codes, scale)
+std::tuple<Tensor, Tensor> fp8_gemm_silu_mul_quant_cuda(const Tensor& a_codes, const Tensor& a_scales, const Tensor& b_codes,
+                                                        const Tensor& b_scales, const Tensor& amax) {
+  TORCH_CHECK(amax.numel() == 1, "b200_fp8_gemm_silu_mul_quant: amax must hold one value");
+  c10::cuda::CUDAGuard guard(a_codes.device());
+  const int64_t K = b_codes.size(1), N = b_codes.size(0), M = a_codes.numel() / std::max<int64_t>(K, 1);
+  Tensor am = amax.to(a_codes.device(), at::kFloat).reshape({1}).contiguous();
+  if (M < 256) {   // a decode step: the kernels one after the other give the same bits
+    Tensor act = fp8_gemm_silu_mul_cuda(a_codes, a_scales, b_codes, b_scales);
+    auto shape = act.sizes().vec();
+    Tensor codes = at::empty(shape, act.options().dtype(at::kByte));
+    Tensor scale = at::empty({1}, act.options().dtype(at::kFloat));
+    if (act.numel() > 0)
+      check_status(b200q_fp8_quantize(act.data_ptr(), B200Q_BF16, M, N / 2, am.data_ptr<float>(), 1, codes.data_ptr<uint8_t>(),
+                                      scale.data_ptr<float>(), current_stream()),
+                   "b200q_fp8_quantize");
+    return {codes, scale};
+  }
+  TORCH_CHECK(a_codes.scalar_type() == at::kByte && b_codes.scalar_type() == at::kByte && b_codes.dim() == 2 &&
+                  a_codes.size(-1) == K && N % 256 == 0,
+              "b200_fp8_gemm_silu_mul_quant: a [.., K] and b [2F, K] uint8 with F a multiple of 128");
+  Tensor a = a_codes.contiguous(), b = b_codes.contiguous();
+  Tensor sa = a_scales.contiguous(), sb = b_scales.contiguous();
+  TORCH_CHECK(sa.scalar_type() == at::kFloat && sb.scalar_type() == at::kFloat && (sa.numel() == 1 || sa.numel() == M) &&
+                  (sb.numel() == 1 || sb.numel() == N),
+              "b200_fp8_gemm_silu_mul_quant: float32 scales, per-tensor or per-row");
+  auto shape = a.sizes().vec();
+  shape.back() = N / 2;
+  Tensor codes = at::empty(shape, a.options().dtype(at::kByte));
+  Tensor scale = at::empty({1}, a.options().dtype(at::kFloat));
+  check_status(b200q_fp8_gemm_silu_mul_quantize(a.data_ptr<uint8_t>(), sa.data_ptr<float>(), sa.numel(), b.data_ptr<uint8_t>(),
+                                                sb.data_ptr<float>(), sb.numel(), nullptr, am.data_ptr<float>(), codes.data_ptr<uint8_t>(),
+                                                scale.data_ptr<float>(), M, N, K, current_stream(), nullptr),
+               "b200q_fp8_gemm_silu_mul_quantize");
+  return {codes, scale};
+}
+std::tuple<Tensor, Tensor> fp8_gemm_silu_mul_quant_meta(const Tensor& a_codes, const Tensor&, const Tensor& b_codes, const Tensor&,
+                                                        const Tensor&) {
+  auto shape = a_codes.sizes().vec();
+  shape.back() = b_codes.size(0) / 2;
+  return {at::empty(shape, a_codes.options().dtype(at::kByte)), at::empty({1}, a_codes.options().dtype(at::kFloat))};
+}
 Tensor nvfp4_gemm_nobias_cuda(const Tensor& a, const Tensor& sa, const Tensor& ga, const Tensor& b, const Tensor& sb, const Tensor& gb) {
   return nvfp4_gemm_cuda(a, sa, ga, b, sb, gb, std::nullopt);
 }
@@ -480,6 +522,9 @@ TORCH_LIBRARY_FRAGMENT(tensorrt, m) {
   m.def("b200_fp8_gemm_silu_mul(Tensor a_codes, Tensor a_scales, Tensor b_codes, Tensor b_scales) -> Tensor");
   m.impl("b200_fp8_gemm_silu_mul", c10::DispatchKey::CUDA, TORCH_FN(fp8_gemm_silu_mul_cuda));
   m.impl("b200_fp8_gemm_silu_mul", c10::DispatchKey::Meta, TORCH_FN(fp8_gemm_silu_mul_meta));
+  m.def("b200_fp8_gemm_silu_mul_quant(Tensor a_codes, Tensor a_scales, Tensor b_codes, Tensor b_scales, Tensor amax) -> (Tensor, Tensor)");
+  m.impl("b200_fp8_gemm_silu_mul_quant", c10::DispatchKey::CUDA, TORCH_FN(fp8_gemm_silu_mul_quant_cuda));
+  m.impl("b200_fp8_gemm_silu_mul_quant", c10::DispatchKey::Meta, TORCH_FN(fp8_gemm_silu_mul_quant_meta));
   m.def("b200_nvfp4_gemm(Tensor a_codes, Tensor a_scales, Tensor a_global, Tensor b_codes, Tensor b_scales, Tensor b_global) -> Tensor");
   m.impl("b200_nvfp4_gemm", c10::DispatchKey::CUDA, TORCH_FN(nvfp4_gemm_nobias_cuda));
   m.impl("b200_nvfp4_gemm", c10::DispatchKey::Meta, TORCH_FN(nvfp4_gemm_nobias_meta));

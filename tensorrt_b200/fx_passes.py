@@ -331,7 +331,8 @@ def fuse_gated_mlp(gm: fx.GraphModule) -> int:
     followed by this library's silu * up kernel: one bf16 rounding where eager silu and mul round twice).  This
     is the MLP of the models the reference lowers (`down_proj(act_fn(gate_proj(x)) * up_proj(x))`).  Left
     alone: F not a multiple of 128, weights that are not constants, a bias, an output cast between the GEMM
-    and the activation.  Returns the number of MLPs rewritten; run it after `fuse_quantized_linear`."""
+    and the activation.  When the product feeds nothing but an FP8 quantizer with a constant per-tensor amax,
+    that quantizer moves into the epilogue as well (`b200_fp8_gemm_silu_mul_quant` -> codes, scale).  Returns the number of MLPs rewritten; run it after `fuse_quantized_linear`."""
     from . import ops
 
     ops.load_ops()
@@ -369,11 +370,27 @@ def fuse_gated_mlp(gm: fx.GraphModule) -> int:
                 name += "_"
             gm.register_buffer(name, stacked)
             names.append(name)
-        with graph.inserting_before(node):
+        # the product's only reader is an FP8 quantizer with a static per-tensor amax (the calibrated input quantizer
+        # of the down projection): it goes into the epilogue too and the node returns (codes, scale) in its place
+        quantizer = None
+        if len(node.users) == 1:
+            user = next(iter(node.users))
+            if user.op == "call_function" and user.target is t.b200_fp8_quantize.default and len(user.args) == 2 and user.args[0] is node:
+                amax_const = _const_tensor(gm, user.args[1])
+                if amax_const is not None and amax_const.numel() == 1:
+                    quantizer = user
+        with graph.inserting_before(quantizer if quantizer is not None else node):
             w_parts = [graph.get_attr(n) for n in names]
-            out = graph.call_function(t.b200_fp8_gemm_silu_mul.default, (gate.args[0], gate.args[1], *w_parts))
-        out.meta.update({k: v for k, v in node.meta.items() if k in ("val", "tensor_meta")})
-        node.replace_all_uses_with(out)
+            if quantizer is not None:
+                out = graph.call_function(t.b200_fp8_gemm_silu_mul_quant.default, (gate.args[0], gate.args[1], *w_parts, quantizer.args[1]))
+            else:
+                out = graph.call_function(t.b200_fp8_gemm_silu_mul.default, (gate.args[0], gate.args[1], *w_parts))
+        if quantizer is not None:
+            quantizer.replace_all_uses_with(out)
+            graph.erase_node(quantizer)
+        else:
+            out.meta.update({k: v for k, v in node.meta.items() if k in ("val", "tensor_meta")})
+            node.replace_all_uses_with(out)
         old_consts = [gate.args[2], gate.args[3], up.args[2], up.args[3]]
         for dead in (node, act, gate, up):
             if not dead.users:

@@ -429,9 +429,10 @@ def test_gated_mlp_becomes_one_gemm_with_the_activation_in_its_epilogue(b200, to
     before = gm(x)
     assert fuse_gated_mlp(gm) == 1
     names = _targets(gm)
-    assert sum("b200_fp8_gemm_silu_mul" in t for t in names) == 1 and not any("silu." in t or t.endswith("silu") for t in names if "gemm" not in t)
+    # the activation's static quantizer went into the epilogue too: the node returns (codes, scale)
+    assert sum("b200_fp8_gemm_silu_mul_quant" in t for t in names) == 1 and not any("silu." in t or t.endswith("silu") for t in names if "gemm" not in t)
     assert sum("b200_fp8_gemm" in t for t in names) == 2               # the fused node and the down projection
-    assert sum("b200_fp8_quantize" in t for t in names) == 2           # x and the activation: all weights folded
+    assert sum("b200_fp8_quantize" in t for t in names) == 1           # x only: all weights folded, the activation quantized in the GEMM
     after = gm(x)
     assert o.rel_l2(after.float().cpu(), before.float().cpu()) < 2e-2   # through the FP8 re-quantization in front of the down projection
     assert fuse_gated_mlp(gm) == 0                                      # idempotent

@@ -336,3 +336,10 @@ def test_gate_up_gemm_with_fused_activation_is_bit_identical(b200, M, F, K, with
     assert o.rel_l2(fused.float().cpu(), want) < 1e-2
     with pytest.raises(ValueError):
         capi.fp8_gemm_silu_mul(xq[0], xq[1], wq[0][:2 * F - 128], wq[1][:2 * F - 128])     # F not a multiple of 128
+    # ... and with the static per-tensor quantizer of the activation in the epilogue as well: the codes and the scale
+    # of quantizing the bf16 result, for an amax above the data and one below it (the clamp)
+    for amax in (fused.float().abs().max() * 1.25, fused.float().abs().max() * 0.3, torch.zeros((), device="cuda")):
+        codes, scale = capi.fp8_gemm_silu_mul_quantize(xq[0], xq[1], wq[0], wq[1], amax.reshape(1), bd)
+        c_ref, s_ref = capi.fp8_quantize(fused, amax.reshape(1))
+        assert torch.equal(codes, c_ref) and torch.equal(scale.reshape(-1), s_ref.reshape(-1))
+    assert capi.device_status() == 0
