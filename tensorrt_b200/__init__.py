@@ -13,11 +13,11 @@ Only CUDA (compute capability 10.x) is implemented; there is no CPU or other-GPU
 from . import capi  # noqa: F401
 from ._lib import B200QError, load as load_library  # noqa: F401
 from .ops import load_ops, ops_loaded  # noqa: F401
-from .linear import Fp8Linear, Nvfp4Linear, QuantizedLinear, fp8_linear, nvfp4_linear  # noqa: F401
+from .linear import Fp8GatedMlp, Fp8Linear, Nvfp4Linear, QuantizedLinear, fp8_linear, nvfp4_linear  # noqa: F401
 from .plugin import register_with_torch_tensorrt  # noqa: F401
 from .fx_passes import fuse_all_reduce_wait, fuse_fp8_sdpa, fuse_gated_mlp, fuse_quantized_linear  # noqa: F401
 
-__all__ = ["capi", "B200QError", "load_library", "load_ops", "ops_loaded", "Fp8Linear", "Nvfp4Linear",
+__all__ = ["capi", "B200QError", "load_library", "load_ops", "ops_loaded", "Fp8GatedMlp", "Fp8Linear", "Nvfp4Linear",
            "QuantizedLinear", "fp8_linear", "nvfp4_linear", "register_with_torch_tensorrt", "fuse_quantized_linear", "fuse_all_reduce_wait", "fuse_fp8_sdpa", "fuse_gated_mlp"]
 
 load_ops()

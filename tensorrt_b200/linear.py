@@ -56,6 +56,48 @@ class Fp8Linear(nn.Module):
         return fp8_linear(x, self.w_codes, self.w_scales, self.bias, self.input_amax)
 
 
+class Fp8GatedMlp(nn.Module):
+    """down(silu(gate(x)) * up(x)) with FP8 linears, the MLP of the decoder models the reference lowers
+    (tools/llm: `down_proj(act_fn(gate_proj(x)) * up_proj(x))`, every linear input and weight behind a quantizer).
+    The gate and up weights are stacked once ([gate rows; up rows]) so that one GEMM computes both and applies
+    the activation in its epilogue; with a static `act_amax` (the calibrated input quantizer of the down
+    projection) the epilogue also emits the FP8 codes the down GEMM reads, and a forward is three launches.
+    `input_amax` / `act_amax` None = dynamic per-token scales measured by the quantize kernels.  No biases."""
+
+    def __init__(self, gu_codes, gu_scales, down_codes, down_scales, input_amax=None, act_amax=None):
+        super().__init__()
+        if gu_codes.shape[0] % 256:
+            raise ValueError("the intermediate size must be a multiple of 128")
+        for name, tensor in (("gu_codes", gu_codes), ("gu_scales", gu_scales), ("down_codes", down_codes), ("down_scales", down_scales),
+                             ("input_amax", input_amax), ("act_amax", act_amax)):
+            self.register_buffer(name, tensor)
+
+    @classmethod
+    def from_float(cls, gate, up, down, per_channel=True, input_amax=None, act_amax=None):
+        ws = [(m.weight if isinstance(m, nn.Module) else m).detach() for m in (gate, up, down)]
+        if any(isinstance(m, nn.Module) and getattr(m, "bias", None) is not None for m in (gate, up, down)):
+            raise ValueError("Fp8GatedMlp has no bias terms")
+        if ws[0].shape != ws[1].shape or ws[2].shape != (ws[0].shape[1], ws[0].shape[0]):
+            raise ValueError("expected gate, up [F, H] and down [H, F]")
+        parts = [capi.fp8_quantize(w, capi.row_amax(w) if per_channel else capi.amax(w)) for w in ws]
+        f = ws[0].shape[0]
+        # one scale per stacked row (a per-tensor scale is repeated: same products)
+        gu_scales = torch.cat([parts[0][1].reshape(-1).expand(f), parts[1][1].reshape(-1).expand(f)])
+        return cls(torch.cat([parts[0][0], parts[1][0]]).contiguous(), gu_scales.contiguous(), parts[2][0], parts[2][1], input_amax, act_amax)
+
+    def forward(self, x):
+        xq = capi.fp8_quantize(x, self.input_amax)
+        tokens = xq[0].numel() // xq[0].shape[-1]
+        if tokens >= 256 and self.act_amax is not None and self.act_amax.numel() == 1:
+            aq = capi.fp8_gemm_silu_mul_quantize(xq[0], xq[1], self.gu_codes, self.gu_scales, self.act_amax)
+        elif tokens >= 256:
+            aq = capi.fp8_quantize(capi.fp8_gemm_silu_mul(xq[0], xq[1], self.gu_codes, self.gu_scales), self.act_amax)
+        else:   # a decode step: the small-M GEMM and the activation kernels (the same bits)
+            gu = capi.fp8_gemm(xq[0], xq[1], self.gu_codes, self.gu_scales)
+            aq = capi.fp8_quantize(capi.silu_mul(gu), self.act_amax) if self.act_amax is not None else capi.silu_mul_fp8_quantize(gu)
+        return capi.fp8_gemm(aq[0], aq[1], self.down_codes, self.down_scales)
+
+
 class Nvfp4Linear(nn.Module):
     """y = nvfp4(x) @ nvfp4(W)^T + b (block 16, E4M3 block scales, fp32 global scales)."""
 

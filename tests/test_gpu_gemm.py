@@ -343,3 +343,34 @@ def test_gate_up_gemm_with_fused_activation_is_bit_identical(b200, M, F, K, with
         c_ref, s_ref = capi.fp8_quantize(fused, amax.reshape(1))
         assert torch.equal(codes, c_ref) and torch.equal(scale.reshape(-1), s_ref.reshape(-1))
     assert capi.device_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tokens", [8, 300])
+@pytest.mark.parametrize("static", [False, True])
+def test_gated_mlp_module(b200, tokens, static):
+    """Fp8GatedMlp (stacked gate/up weight, activation and, with a static amax, its quantizer in the GEMM
+    epilogue) against the same MLP built from three Fp8Linear modules and this library's silu * up kernel (the
+    same bits), and against the oracle's linears with an fp32 activation (close)."""
+    capi = b200.capi
+    g = torch.Generator().manual_seed(tokens)
+    hdim, f = 256, 384
+    x = torch.randn(2, tokens // 2, hdim, generator=g).bfloat16().cuda()
+    wg, wu = ((torch.randn(f, hdim, generator=g) * 0.06).bfloat16().cuda() for _ in range(2))
+    wd = (torch.randn(hdim, f, generator=g) * 0.05).bfloat16().cuda()
+    in_amax = x.float().abs().max().reshape(1) if static else None
+    gate, up, down = (b200.Fp8Linear.from_float(w, input_amax=in_amax) for w in (wg, wu, wd))
+    act = capi.silu_mul(torch.cat([gate(x), up(x)], dim=-1))
+    act_amax = (act.float().abs().max() * 0.9).reshape(1) if static else None
+    down.input_amax = act_amax
+    ref = down(act)
+    mlp = b200.Fp8GatedMlp.from_float(wg, wu, wd, input_amax=in_amax, act_amax=act_amax)
+    y = mlp(x)
+    assert y.shape == x.shape and torch.equal(y, ref)
+    assert capi.device_status() == 0
+    yo = o.fp8_linear_ref(x.cpu().reshape(-1, hdim), torch.cat([wg, wu]).cpu()).bfloat16().float()
+    want = o.fp8_linear_ref((torch.nn.functional.silu(yo[:, :f]) * yo[:, f:]).bfloat16(), wd.cpu())
+    if not static:
+        assert o.rel_l2(y.float().cpu().reshape(-1, hdim), want.float()) < 2e-2
+    with pytest.raises(ValueError):
+        b200.Fp8GatedMlp.from_float(wg[:192], wu[:192], wd[:, :192])        # 192 is not a multiple of 128
