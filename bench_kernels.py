@@ -304,6 +304,45 @@ def attention_case(capi, peaks, min_ms=300.0):
             "roofline": tensor_roofline(tf, peaks, "fp8", "fp8_sdpa_kernel", flops)}
 
 
+def gated_mlp_case(capi, peaks, min_ms=300.0, tokens=32768, hidden=8192, ffn=28672):
+    """The FP8 gated MLP of the stack's shape through `Fp8GatedMlp`: dynamic per-token activation scales (the
+    stack's configuration: quantize, gate/up GEMM with the activation in its epilogue, quantize, down GEMM) and
+    static per-tensor ones (three launches: the activation's quantizer rides in the epilogue too), against the
+    unfused chain (quantize, gate/up GEMM, silu * up + quantize kernel, down GEMM)."""
+    import tensorrt_b200 as b200
+
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16, generator=g)
+    wg, wu = (torch.randn(ffn, hidden, device="cuda", dtype=torch.bfloat16, generator=g) * 0.02 for _ in range(2))
+    wd = torch.randn(hidden, ffn, device="cuda", dtype=torch.bfloat16, generator=g) * 0.02
+    dyn = b200.Fp8GatedMlp.from_float(wg, wu, wd)
+    act = capi.fp8_gemm_silu_mul(*capi.fp8_quantize(x, None), dyn.gu_codes, dyn.gu_scales)
+    static = b200.Fp8GatedMlp(dyn.gu_codes, dyn.gu_scales, dyn.down_codes, dyn.down_scales, x.float().abs().max().reshape(1),
+                              act.float().abs().max().reshape(1))
+    del wg, wu, wd, act
+
+    def unfused():
+        xq = capi.fp8_quantize(x, None)
+        aq = capi.silu_mul_fp8_quantize(capi.fp8_gemm(xq[0], xq[1], dyn.gu_codes, dyn.gu_scales))
+        return capi.fp8_gemm(aq[0], aq[1], dyn.down_codes, dyn.down_scales)
+
+    flops = 2.0 * tokens * hidden * ffn * 3
+    out = {"shape": f"{tokens} tokens, hidden {hidden}, ffn {ffn}"}
+    variants = (("unfused_dynamic", unfused), ("fused_dynamic", lambda: dyn(x)), ("fused_static", lambda: static(x)))
+    # the variants take turns (three rounds each): under the power cap whatever runs later runs warmer and slower
+    acc = {name: [0.0, 0] for name, _ in variants}
+    for _ in range(3):
+        for name, fn in variants:
+            ms, k = time_device(fn, min_ms / 3, min_iters=4)
+            acc[name][0] += ms * k
+            acc[name][1] += k
+    for name, (total, k) in acc.items():
+        ms = total / k
+        out[name] = {"ms": ms, "launches": k, "tflops": flops / ms / 1e9,
+                     "roofline": tensor_roofline(flops / ms / 1e9, peaks, "fp8", "gemm_pair_kernel<fp8> (+ glue)", flops)}
+    return out
+
+
 def full_sweep_shapes():
     return [(m, n, k) for (n, k) in SWEEP_NK for m in SWEEP_M]
 
@@ -321,6 +360,10 @@ def extras(capi, peaks, min_ms=500.0):
             out["fp8_attention"] = attention_case(capi, peaks)
         except Exception as exc:
             out["fp8_attention"] = {"error": str(exc)[:200]}
+        try:
+            out["fp8_gated_mlp"] = gated_mlp_case(capi, peaks)
+        except Exception as exc:
+            out["fp8_gated_mlp"] = {"error": str(exc)[:200]}
         out["library"] = library_comparators(peaks)
     out["clocks"] = clocks.summary()
     return out
