@@ -75,7 +75,39 @@ def cases():
     np.savez_compressed(HERE / "cases.npz", **out)
 
 
+def layers():
+    """Attention, all-reduce and decoder-layer restatements on small seeded inputs (outputs are compared within
+    a bf16 unit in the last place: the fp32 sums inside may be ordered differently on another CPU)."""
+    out = {}
+    g = torch.Generator().manual_seed(4321)
+    q = torch.randn(1, 4, 40, 32, generator=g).half()
+    k = torch.randn(1, 2, 40, 32, generator=g).half()
+    v = torch.randn(1, 2, 40, 32, generator=g).half()
+    am = torch.tensor(3.5)
+    out["sdpa_q"], out["sdpa_k"], out["sdpa_v"] = q.float().numpy(), k.float().numpy(), v.float().numpy()
+    out["sdpa_full"] = o.fp8_sdpa_ref(q, k, v, am, am, am).float().numpy()
+    out["sdpa_causal"] = o.fp8_sdpa_ref(q, k, v, am, am, am, is_causal=True).float().numpy()
+    out["sdpa_causal_short_q"] = o.fp8_sdpa_ref(q[:, :, -8:], k, v, am, am, am, is_causal=True).float().numpy()   # lower-right mask
+    parts = [(torch.randn(6, 16, generator=g) * 3).bfloat16() for _ in range(4)]
+    out["ar_parts"] = torch.stack(parts).float().numpy()
+    out["ar_sum"] = o.all_reduce_ref(parts, torch.bfloat16).float().numpy()
+    hidden, n_q, n_kv, hd, ffn = 64, 4, 2, 16, 128
+    rnd = lambda r, c: (torch.randn(r, c, generator=g) * 0.05).bfloat16()  # noqa: E731
+    layer = {"norm1": (1 + 0.1 * torch.randn(hidden, generator=g)).bfloat16(), "norm2": (1 + 0.1 * torch.randn(hidden, generator=g)).bfloat16(),
+             "wqkv": rnd((n_q + 2 * n_kv) * hd, hidden), "wo": rnd(hidden, n_q * hd), "wgu": rnd(2 * ffn, hidden), "wdown": rnd(hidden, ffn)}
+    h = torch.randn(16, hidden, generator=g).bfloat16()
+    for key, t in layer.items():
+        out[f"layer_{key}"] = t.float().numpy()
+    out["layer_h"] = h.float().numpy()
+    for mode in ("fp8", "nvfp4"):
+        for world in (1, 2):
+            out[f"layer_{mode}_w{world}"] = o.decoder_layer_ref(h, layer, n_q, n_kv, hd, mode, world=world).float().numpy()
+    out["layer_fp8_sdpa_w2"] = o.decoder_layer_ref(h, layer, n_q, n_kv, hd, "fp8", world=2, attention="fp8_sdpa", seq_len=8).float().numpy()
+    np.savez_compressed(HERE / "layers.npz", **out)
+
+
 if __name__ == "__main__":
     formats()
     cases()
+    layers()
     print("wrote", [p.name for p in HERE.glob("*.npz")])

@@ -176,3 +176,32 @@ def test_tensor_parallel_layer_matches_single_rank(mode):
     y2 = o.decoder_layer_ref(h, layer, nq, nkv, hd, mode, world=2)
     assert y1.shape == h.shape
     assert o.rel_l2(y2.float(), y1.float()) < (2e-2 if mode == "fp8" else 8e-2)
+
+
+def _close_in_bf16(a: torch.Tensor, b: np.ndarray) -> bool:
+    """Equal up to one unit in the last place of bf16 (fp32 sums inside may be ordered differently on another CPU)."""
+    b = torch.from_numpy(b)
+    return bool(((a.float() - b).abs() <= 2.0 ** -7 * torch.maximum(a.float().abs(), b.abs()) + 1e-6).all())
+
+
+def test_golden_attention_all_reduce_and_decoder_layer():
+    """Fixtures of the layer-level restatements (tests/golden/layers.npz, generator beside it): FP8 attention with
+    GQA, the lower-right causal mask and a short query block; the fp32-sum all-reduce; a decoder layer in both
+    modes, as 1 and 2 tensor-parallel ranks, with the identity and the FP8-attention core."""
+    z = np.load(G / "layers.npz")
+    q, k, v = (torch.from_numpy(z[f"sdpa_{n}"]).half() for n in "qkv")
+    am = torch.tensor(3.5)
+    assert _close_in_bf16(o.fp8_sdpa_ref(q, k, v, am, am, am), z["sdpa_full"])
+    assert _close_in_bf16(o.fp8_sdpa_ref(q, k, v, am, am, am, is_causal=True), z["sdpa_causal"])
+    assert _close_in_bf16(o.fp8_sdpa_ref(q[:, :, -8:], k, v, am, am, am, is_causal=True), z["sdpa_causal_short_q"])
+    assert not np.array_equal(z["sdpa_full"], z["sdpa_causal"])
+    # the last 8 queries of the full causal problem see the same keys as the short query block aligned to the end
+    assert np.allclose(z["sdpa_causal"][:, :, -8:], z["sdpa_causal_short_q"], atol=1e-3)
+    parts = [t.bfloat16() for t in torch.from_numpy(z["ar_parts"])]
+    assert np.array_equal(o.all_reduce_ref(parts, torch.bfloat16).float().numpy(), z["ar_sum"])
+    layer = {key: torch.from_numpy(z[f"layer_{key}"]).bfloat16() for key in ("norm1", "norm2", "wqkv", "wo", "wgu", "wdown")}
+    h = torch.from_numpy(z["layer_h"]).bfloat16()
+    for mode in ("fp8", "nvfp4"):
+        for world in (1, 2):
+            assert _close_in_bf16(o.decoder_layer_ref(h, layer, 4, 2, 16, mode, world=world), z[f"layer_{mode}_w{world}"]), (mode, world)
+    assert _close_in_bf16(o.decoder_layer_ref(h, layer, 4, 2, 16, "fp8", world=2, attention="fp8_sdpa", seq_len=8), z["layer_fp8_sdpa_w2"])
