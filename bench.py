@@ -55,6 +55,11 @@ def main():
     ap.add_argument("--attention", choices=["identity", "fp8_sdpa"], default="identity",
                     help="tp_stack: attention core between the QKV and O linears: the V-slice stand-in of the linear stack "
                          "(default, the configuration the metric is quoted on) or causal FP8 attention over the 1024-token sequences")
+    ap.add_argument("--gate-up-fused", type=int, default=1, dest="gate_up_fused",
+                    help="tp_stack: 1 = silu(gate) * up in the epilogue of the gate/up GEMM, 0 = in its own kernel (A/B runs)")
+    ap.add_argument("--call-times", type=int, default=0, dest="call_times",
+                    help="tp_stack on one GPU: 1 = one extra forward with CUDA events around every library call; "
+                         "per-call totals are added to the line as `call_times`")
     ap.add_argument("--slabs", type=int, default=1, help="row slabs per row-parallel linear (all-reduce overlap) in tp_stack")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -247,6 +247,57 @@ def collective_stage_times(capi, stack, cfg, world, rows, iters=20):
     return out
 
 
+def call_times(capi, stack, h, mb, sharded):
+    """One forward with CUDA events around every call into the library (the C-ABI wrappers of `capi`): ms per
+    call kind, summed over the forward, with the call count; GEMMs are keyed by their (M, N, K)."""
+    import collections
+
+    import tensorrt_b200.stack as st
+
+    names = ("fp8_gemm", "fp8_gemm_silu_mul", "nvfp4_gemm", "add_rms_norm_fp8_quantize", "silu_mul_fp8_quantize", "silu_mul", "rms_norm",
+             "expand_heads", "fp8_quantize", "nvfp4_quantize", "amax", "add")
+    records, saved = [], {}
+
+    def wrap(name):
+        orig = getattr(capi, name)
+
+        def timed_call(*a, **k):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = orig(*a, **k)
+            e1.record()
+            key = name
+            if name.startswith("fp8_gemm"):
+                key = f"{name}({a[0].shape[0]}, {a[2].shape[0]}, {a[0].shape[1]})"
+            records.append((key, e0, e1))
+            return r
+
+        saved[name] = (orig, st.CudaBackend.__dict__.get(name))
+        setattr(capi, name, timed_call)
+        if name in st.CudaBackend.__dict__:
+            setattr(st.CudaBackend, name, staticmethod(timed_call))
+
+    for n in names:
+        wrap(n)
+    try:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        stack.forward(h, mb, sharded)
+        e1.record()
+        torch.cuda.synchronize()
+    finally:
+        for n, (orig, static) in saved.items():
+            setattr(capi, n, orig)
+            if static is not None:
+                setattr(st.CudaBackend, n, static)
+    agg = collections.defaultdict(lambda: [0, 0.0])
+    for key, a, b in records:
+        agg[key][0] += 1
+        agg[key][1] += a.elapsed_time(b)
+    return {"forward_ms": e0.elapsed_time(e1),
+            "calls": {k: {"n": v[0], "ms_total": v[1], "ms_each": v[1] / v[0]} for k, v in sorted(agg.items(), key=lambda kv: -kv[1][1])}}
+
+
 def run(args):
     from tensorrt_b200 import capi
     from tensorrt_b200.stack import DecoderStack, random_layer_weights
@@ -276,7 +327,10 @@ def run(args):
             raise SystemExit(3)
 
     t0 = time.time()
+    from tensorrt_b200.stack import CudaBackend
+
     stack = DecoderStack(cfg, random_layer_weights(cfg, seed, device=dev), rank=rank, world=world,
+                         backend=CudaBackend(cfg.mode, fuse_gate_up=bool(getattr(args, "gate_up_fused", 1))),
                          slabs=args.slabs if world > 1 else 1, fused_rows=tokens if fused else 0, pull_rows=64 if pull else 0)
     torch.cuda.synchronize()
     build_s = time.time() - t0
@@ -402,6 +456,8 @@ def run(args):
                      "traffic": None, "kernel": "gemm_pair_kernel<fp8>" if cfg.mode == "fp8" else "gemm_nvf4_pair_kernel",
                      "algorithmic_flops_per_step_per_gpu": flops / world},
     }
+    if getattr(args, "call_times", 0) and world == 1 and phase != "decode":
+        line["call_times"] = call_times(capi, stack, h, mb, sharded)
     if parity is not None:
         line["parity"] = parity
     if breakdown is not None:

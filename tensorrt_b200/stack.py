@@ -100,8 +100,9 @@ def shard_layer_weights(layer: dict, cfg: StackConfig, rank: int, world: int) ->
 class CudaBackend:
     """b200q kernels through the C ABI."""
 
-    def __init__(self, mode: str):
-        self.mode = mode
+    def __init__(self, mode: str, fuse_gate_up: bool = True):
+        """`fuse_gate_up` False keeps silu(gate) * up in its own kernel after the gate/up GEMM (A/B measurements)."""
+        self.mode, self.fuse_gate_up = mode, fuse_gate_up
 
     def prepare_weight(self, w: torch.Tensor):
         if self.mode == "fp8":
@@ -128,7 +129,7 @@ class CudaBackend:
         """Quantized input of the down projection straight from the gate/up GEMM: silu(gate) * up is applied
         in the GEMM's epilogue (the [T, 2F] bf16 tensor is never written), then quantized per token.  FP8 with
         at least 256 tokens and F a multiple of 128; None otherwise (the caller takes the unfused kernels)."""
-        if self.mode != "fp8" or xq[0].shape[0] < 256 or qw[0].shape[0] % 256:
+        if not self.fuse_gate_up or self.mode != "fp8" or xq[0].shape[0] < 256 or qw[0].shape[0] % 256:
             return None
         return capi.fp8_quantize(capi.fp8_gemm_silu_mul(xq[0], xq[1], qw[0], qw[1], None), None)
 
