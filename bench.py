@@ -17,7 +17,8 @@ metric), and the CPU baseline.
 
 One JSON line is printed by rank 0.  `--impl reference` times the CPU restatement of the
 reference's eager semantics (oracle/) on the host cores for the same metric and workload.
-Other workloads: `nvfp4_stack`, `nvfp4_quantize`, `fp8_quantize`, `fp8_gemm`, `nvfp4_gemm`.
+Other workloads: `nvfp4_stack`, `nvfp4_quantize`, `fp8_quantize`, `fp8_gemm`, `nvfp4_gemm`; `small_cases` launches the
+element-wise and attention kernels twice on small inputs (for profiler captures, nothing timed).
 """
 from __future__ import annotations
 
@@ -36,7 +37,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="tp_stack",
-                    choices=["tp_stack", "nvfp4_stack", "nvfp4_quantize", "fp8_quantize", "fp8_gemm", "nvfp4_gemm"])
+                    choices=["tp_stack", "nvfp4_stack", "nvfp4_quantize", "fp8_quantize", "fp8_gemm", "nvfp4_gemm", "small_cases"])
     ap.add_argument("--no-extras", action="store_true", help="tp_stack on one GPU: skip the quantize / GEMM sweep and the CPU baseline")
     ap.add_argument("--shape", default="", help="M,N,K for the GEMM workloads (default: the whole sweep)")
     ap.add_argument("--micro-batches", type=int, default=0, dest="micro_batches",

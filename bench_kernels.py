@@ -466,7 +466,37 @@ def run_quantize(args, which):
         "kernels": suite}))
 
 
+def run_small_cases(args):
+    """`--workload small_cases`: a few launches of the element-wise kernels and of the attention kernel on inputs
+    of a few hundred MB (larger than L2), for `ncu` captures that end by themselves.  Nothing is timed."""
+    from tensorrt_b200 import capi
+
+    torch.cuda.set_device(0)
+    tokens, hidden, ffn = 4096, 8192, 28672
+    gu = torch.randn(tokens, 2 * ffn, device="cuda", dtype=torch.bfloat16)
+    act = torch.randn(tokens, ffn, device="cuda", dtype=torch.bfloat16)
+    h = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
+    d = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(hidden, device="cuda", dtype=torch.bfloat16)
+    B, Hq, Hkv, S, D = 2, 64, 8, 1024, 128
+    q = torch.randn(B, Hq, S, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(B, Hkv, S, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(B, Hkv, S, D, device="cuda", dtype=torch.bfloat16)
+    am = torch.tensor([4.0], device="cuda")
+    for _ in range(2):
+        capi.silu_mul_fp8_quantize(gu)
+        capi.add_rms_norm_fp8_quantize(h, d, w)
+        capi.fp8_quantize(act, None)
+        capi.fp8_sdpa(q, k, v, am, am, am, True)
+    torch.cuda.synchronize()
+    print(json.dumps({"workload": "small_cases", "device_status": capi.device_status(),
+                      "cases": {"silu_mul_fp8_quantize": [tokens, 2 * ffn], "add_rms_norm_fp8_quantize": [tokens, hidden],
+                                "fp8_quantize": [tokens, ffn], "fp8_sdpa": [B, Hq, Hkv, S, D]}, "launches_each": 2}))
+
+
 def run(args):
+    if args.workload == "small_cases":
+        return run_small_cases(args)
     if args.workload == "fp8_gemm":
         run_gemm(args, "fp8")
     elif args.workload == "nvfp4_gemm":
