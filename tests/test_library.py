@@ -301,3 +301,24 @@ def test_comm_context_argument_validation():
     assert lib.b200q_comm_create(0, 1, null_cb, None, None) == -1
     assert lib.b200q_comm_alloc(None, 16, (ctypes.c_void_p * 8)()) == -1
     assert lib.b200q_comm_destroy(None) == 0
+
+
+def test_validation_of_the_fused_gate_up_gemm_without_a_device(b200):
+    """b200q_fp8_gemm_silu_mul[_quantize]: argument errors are reported before anything touches a device."""
+    from tensorrt_b200 import _lib
+
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(8192)
+    p = (ctypes.addressof(buf) + 255) & ~255
+    f, g = lib.b200q_fp8_gemm_silu_mul, lib.b200q_fp8_gemm_silu_mul_quantize
+    assert f(None, p, 1, p, p, 1, None, p, 256, 256, 64, None, None) == -1           # null operand
+    assert f(p, p, 1, p, p, 1, None, p, 256, 384, 64, None, None) == -1              # N = 2F with F not a multiple of 128
+    assert f(p, p, 1, p, p, 1, None, p, 256, 256, 72, None, None) == -1              # K % 16
+    assert f(p, p, 7, p, p, 1, None, p, 256, 256, 64, None, None) == -1              # activation scales: 1 or M
+    assert f(p + 4, p, 1, p, p, 1, None, p, 256, 256, 64, None, None) == -2          # misaligned codes
+    cfg = _lib.Cfg()
+    cfg.tile_n = 128
+    assert f(p, p, 1, p, p, 1, None, p, 256, 256, 64, None, ctypes.byref(cfg)) == -1  # one kernel serves this entry: no tile choice
+    assert g(p, p, 1, p, p, 1, None, None, p, p, 256, 256, 64, None, None) == -1     # the static amax is required
+    assert g(p, p, 1, p, p, 1, None, p, None, p, 256, 256, 64, None, None) == -1     # so is the code buffer
+    assert g(p, p, 1, p, p, 1, None, p, p, None, 256, 384, 64, None, None) == -1     # F not a multiple of 128
