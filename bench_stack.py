@@ -255,7 +255,7 @@ def call_times(capi, stack, h, mb, sharded):
     import tensorrt_b200.stack as st
 
     names = ("fp8_gemm", "fp8_gemm_silu_mul", "nvfp4_gemm", "add_rms_norm_fp8_quantize", "silu_mul_fp8_quantize", "silu_mul", "rms_norm",
-             "expand_heads", "fp8_quantize", "nvfp4_quantize", "amax", "add")
+             "expand_heads", "expand_heads_fp8_quantize", "fp8_quantize", "nvfp4_quantize", "amax", "add")
     records, saved = [], {}
 
     def wrap(name):
@@ -424,10 +424,10 @@ def run(args):
                      "limiter": "gemm" if gemm_ms >= 0.8 * per_layer_ms else "exchange + glue not hidden under the GEMMs"}
         if sharded and fused:
             breakdown["collective_stages"] = collective_stage_times(capi, stack, cfg, world, tokens // mb)
-    # launches of this library per layer and micro-batch: norm + quantize, QKV GEMM, head expansion, quantize, O GEMM,
+    # launches of this library per layer and micro-batch: norm + quantize, QKV GEMM, head expansion + quantize, O GEMM,
     # norm + quantize, gate/up GEMM (activation in its epilogue), quantize, down GEMM; the token-sharded form replaces
     # the two norm kernels by a flag exchange + reduce / norm / quantize / gather pair each
-    kernels_per_layer = 11 if (world > 1 and sharded and fused) else 9
+    kernels_per_layer = 10 if (world > 1 and sharded and fused) else 8
     launches = steps * (cfg.layers * kernels_per_layer * (mb if world > 1 else 1) + 2)
     line = {
         "metric": "tp_decoder_stack_prefill_throughput" if tp else "nvfp4_decoder_stack_prefill_throughput",

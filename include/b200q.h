@@ -385,6 +385,12 @@ int b200q_silu_mul_fp8_quantize(const void* gate_up, uint8_t* codes_out, float* 
 int b200q_add(const void* a, const void* b, void* out, int64_t n, b200q_stream_t stream);
 int b200q_expand_heads(const void* src, int64_t src_stride, int64_t src_col0, void* out, int64_t rows,
                        int heads_out, int rep, int head_dim, b200q_stream_t stream);
+/* b200q_expand_heads followed by b200q_fp8_quantize (dynamic per-row amax) in one pass: codes
+ * [rows, heads_out * head_dim] and scales [rows] equal those of the two separate calls; the kv slice of a
+ * token ((heads_out / rep) * head_dim elements) may hold at most 2048 elements. */
+int b200q_expand_heads_fp8_quantize(const void* src, int64_t src_stride, int64_t src_col0, uint8_t* codes_out,
+                                    float* scales_out, int64_t rows, int heads_out, int rep, int head_dim,
+                                    b200q_stream_t stream);
 
 /* The GEMM kernels bound every device-side wait; a wait that gives up records it in a
  * device status word instead of hanging.  This call synchronises with the device, returns

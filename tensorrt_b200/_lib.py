@@ -55,6 +55,7 @@ SIGNATURES = {
     "b200q_silu_mul_fp8_quantize": (_c.c_int, [_p, _p, _p, _i64, _i64, _p]),
     "b200q_add": (_c.c_int, [_p, _p, _p, _i64, _p]),
     "b200q_expand_heads": (_c.c_int, [_p, _i64, _i64, _p, _i64, _c.c_int, _c.c_int, _c.c_int, _p]),
+    "b200q_expand_heads_fp8_quantize": (_c.c_int, [_p, _i64, _i64, _p, _p, _i64, _c.c_int, _c.c_int, _c.c_int, _p]),
     "b200q_device_status": (_c.c_int, [_c.c_int]),
 }
 

@@ -403,6 +403,21 @@ def expand_heads(src: torch.Tensor, col0: int, heads_out: int, rep: int, head_di
     return out
 
 
+def expand_heads_fp8_quantize(src: torch.Tensor, col0: int, heads_out: int, rep: int, head_dim: int):
+    """`expand_heads` followed by `fp8_quantize(.., None)` in one pass -> (codes [.., heads_out*head_dim], scales [rows]),
+    the same bits; the kv slice of a token may hold at most 2048 elements."""
+    _need_cuda(src)
+    _bf16(src)
+    src = src.contiguous()
+    rows, width = _rows_cols(src)
+    codes = torch.empty(*src.shape[:-1], heads_out * head_dim, dtype=torch.uint8, device=src.device)
+    scales = torch.empty(rows, dtype=torch.float32, device=src.device)
+    with torch.cuda.device(src.device):
+        check(load().b200q_expand_heads_fp8_quantize(src.data_ptr(), width, col0, codes.data_ptr(), scales.data_ptr(), rows, heads_out, rep,
+                                                     head_dim, _stream(src)), "b200q_expand_heads_fp8_quantize")
+    return codes, scales
+
+
 def device_status(reset: bool = True) -> int:
     """0, or B200Q_ERR_TIMEOUT (-6) when a GEMM's bounded device-side wait gave up."""
     return load().b200q_device_status(1 if reset else 0)

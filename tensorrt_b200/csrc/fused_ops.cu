@@ -564,6 +564,54 @@ expand_heads_kernel(const __nv_bfloat16* __restrict__ src, int64_t src_stride, i
   }
 }
 
+// expand_heads followed by the per-token FP8 quantize, in one pass over the kv slice: a repeated head does
+// not change the token's abs-max, so the token is quantized once (one warp per token, its slice in
+// registers) and every code group is stored `rep` times.  The same codes and scales as
+// b200q_expand_heads + b200q_fp8_quantize with dynamic per-row amax; the expanded bf16 tensor is never written.
+template <int ITEMS>
+__global__ void __launch_bounds__(kThreads)
+expand_heads_quant_kernel(const __nv_bfloat16* __restrict__ src, int64_t src_stride, int64_t src_col0, uint8_t* __restrict__ codes,
+                          float* __restrict__ scales, int64_t rows, int heads_out, int rep, int head_dim) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t row = blockIdx.x * (int64_t)(kThreads / 32) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int kv_heads = heads_out / rep;
+  const int groups = (kv_heads * head_dim) >> 3;            // groups of 8 elements in the token's kv slice
+  const int64_t out_cols = static_cast<int64_t>(heads_out) * head_dim;
+  float v[ITEMS][8];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int g = lane + i * 32;
+    if (g < groups) {
+      Elem<__nv_bfloat16>::load8(src + row * src_stride + src_col0 + (int64_t)g * 8, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+    }
+  }
+  amax = warp_max(amax);
+  const float scale = fp8_scale_from_amax(amax);
+  if (lane == 0) scales[row] = scale;
+  const float y = b200q_rcp_rn(scale);
+  const bool fast = b200q_div_fast_ok(scale);
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const int g = lane + i * 32;
+    if (g < groups) {
+      float q[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q[j] = fast ? b200q_div_by_shared(v[i][j], scale, y) : __fdiv_rn(v[i][j], scale);
+      const uint2 packed = make_uint2(f32x2_to_e4m3x2(q[0], q[1]) | (f32x2_to_e4m3x2(q[2], q[3]) << 16),
+                                      f32x2_to_e4m3x2(q[4], q[5]) | (f32x2_to_e4m3x2(q[6], q[7]) << 16));
+      const int e = g * 8, kvh = e / head_dim, d = e - kvh * head_dim;
+      uint8_t* dst = codes + row * out_cols + static_cast<int64_t>(kvh) * rep * head_dim + d;
+      for (int r = 0; r < rep; ++r) *reinterpret_cast<uint2*>(dst + static_cast<int64_t>(r) * head_dim) = packed;
+    }
+  }
+}
+
 int grid_for(int64_t work_items) {
   int64_t ctas = (work_items + kThreads - 1) / kThreads;
   const int64_t cap = (int64_t)sm_count() * 16;
@@ -813,6 +861,30 @@ int b200q_expand_heads(const void* src, int64_t src_stride, int64_t src_col0, vo
   if (int rc = check_arch()) return rc;
   launch_pdl(expand_heads_kernel, dim3(grid_for(rows * heads_out * (head_dim >> 3))), dim3(kThreads), 0, static_cast<cudaStream_t>(stream),
              static_cast<const __nv_bfloat16*>(src), src_stride, src_col0, static_cast<__nv_bfloat16*>(out), rows, heads_out, rep, head_dim);
+  return check_launch();
+}
+
+int b200q_expand_heads_fp8_quantize(const void* src, int64_t src_stride, int64_t src_col0, uint8_t* codes_out, float* scales_out,
+                                    int64_t rows, int heads_out, int rep, int head_dim, b200q_stream_t stream) {
+  if (rows < 0 || heads_out <= 0 || rep <= 0 || head_dim <= 0 || head_dim % 8 != 0 || heads_out % rep != 0 || src_stride % 8 != 0 ||
+      src_col0 % 8 != 0 || rows > 0x7fffffffLL)
+    return B200Q_ERR_INVALID;
+  const int64_t kv_width = static_cast<int64_t>(heads_out / rep) * head_dim;
+  if (kv_width > 32 * 8 * 8) return B200Q_ERR_INVALID;       // the slice of a token stays in one warp's registers
+  if (rows == 0) return B200Q_OK;
+  if (src == nullptr || codes_out == nullptr || scales_out == nullptr) return B200Q_ERR_INVALID;
+  if (!aligned(src, 16) || !aligned(codes_out, 8)) return B200Q_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  const int items = static_cast<int>(((kv_width >> 3) + 31) / 32);
+  const dim3 grid(static_cast<unsigned>((rows + kThreads / 32 - 1) / (kThreads / 32)));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const auto* sp = static_cast<const __nv_bfloat16*>(src);
+#define B200Q_EHQ(I) launch_pdl(expand_heads_quant_kernel<I>, grid, dim3(kThreads), 0, st, sp, src_stride, src_col0, codes_out, scales_out, rows, heads_out, rep, head_dim)
+  if (items <= 1) B200Q_EHQ(1);
+  else if (items <= 2) B200Q_EHQ(2);
+  else if (items <= 4) B200Q_EHQ(4);
+  else B200Q_EHQ(8);
+#undef B200Q_EHQ
   return check_launch();
 }
 

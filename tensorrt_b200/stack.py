@@ -133,6 +133,13 @@ class CudaBackend:
             return None
         return capi.fp8_quantize(capi.fp8_gemm_silu_mul(xq[0], xq[1], qw[0], qw[1], None), None)
 
+    def expand_heads_quantize(self, src, col0, heads_out, rep, head_dim):
+        """The repeated-head stand-in for attention together with the per-token quantize in front of the O
+        projection (FP8; the kv slice of a token must fit one warp's registers), else None."""
+        if self.mode != "fp8" or (heads_out // rep) * head_dim > 2048:
+            return None
+        return capi.expand_heads_fp8_quantize(src, col0, heads_out, rep, head_dim)
+
     def silu_mul_quantize(self, gate_up: torch.Tensor):
         """silu(gate) * up as the quantized operand of the down projection (one kernel), or None
         when the mode has no fused form (NVFP4 block quantize needs the tensor amax first)."""
@@ -307,7 +314,12 @@ class DecoderLayer:
         if cfg.attention == "fp8_sdpa" and qkv.shape[0] >= cfg.seq_len:
             raise ValueError(f"{qkv.shape[0]} tokens are not whole sequences of {cfg.seq_len}")
         # fewer tokens than a sequence (a decode step has no key cache here) and the linear-stack form
-        return be.expand_heads(qkv, (cfg.q_width + cfg.kv_width) // w, cfg.n_q // w, cfg.n_q // cfg.n_kv, cfg.head_dim)
+        col0, heads, rep = (cfg.q_width + cfg.kv_width) // w, cfg.n_q // w, cfg.n_q // cfg.n_kv
+        if hasattr(be, "expand_heads_quantize") and not self.calibrating:
+            xq = be.expand_heads_quantize(qkv, col0, heads, rep, cfg.head_dim)    # quantized input of the O projection in one pass
+            if xq is not None:
+                return xq
+        return be.expand_heads(qkv, col0, heads, rep, cfg.head_dim)
 
     def _ffn_act(self, xq):
         """gate/up linear + silu(gate) * up -> input of the down projection (quantized when the

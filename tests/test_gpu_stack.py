@@ -54,6 +54,24 @@ def test_glue_kernels(b200):
     assert torch.equal(out, v)
 
 
+@pytest.mark.parametrize("rows,kv_heads,rep,hd,q_cols", [(9, 2, 2, 64, 384), (300, 8, 8, 128, 8192), (1000, 1, 8, 128, 1024),
+                                                         (33, 4, 1, 32, 0), (5, 16, 2, 128, 256)])
+def test_expand_heads_with_fused_quantize_is_bit_identical(b200, rows, kv_heads, rep, hd, q_cols):
+    """The repeated-head expansion and the per-token FP8 quantize in front of the O projection in one kernel:
+    codes and scales equal those of the two separate kernels (an all-zero token included)."""
+    capi = b200.capi
+    g = torch.Generator().manual_seed(rows + hd)
+    width = q_cols + 2 * kv_heads * hd                  # [q | k | v] columns of a QKV output
+    src = (torch.randn(rows, width, generator=g) * 2).bfloat16()
+    src[rows // 2] = 0
+    col0 = q_cols + kv_heads * hd
+    codes, scales = capi.expand_heads_fp8_quantize(src.cuda(), col0, kv_heads * rep, rep, hd)
+    c_ref, s_ref = capi.fp8_quantize(capi.expand_heads(src.cuda(), col0, kv_heads * rep, rep, hd), None)
+    assert codes.shape == (rows, kv_heads * rep * hd) and torch.equal(codes, c_ref) and torch.equal(scales, s_ref)
+    with pytest.raises(b200.B200QError):
+        capi.expand_heads_fp8_quantize(torch.zeros(2, 4096, dtype=torch.bfloat16, device="cuda"), 0, 32, 1, 128)   # kv slice beyond 2048
+
+
 # from 8 rows per SM and 4096 columns on: persistent CTAs fed by a ring of 4096-column chunks (1, 2 with a ragged
 # second, 4 ragged, 7 and 8 chunks per row; CTAs that walk 4 and 5 rows)
 @pytest.mark.parametrize("rows,f", [(1, 16), (33, 528), (64, 3584), (17, 14336), (5, 28672), (3, 32768),
